@@ -1,0 +1,5 @@
+"""Drop-in alias: `import flashnn` resolves to the B200-native operators, so code
+written against the reference's quantized-GEMM API (flashnn/__init__.py:7,10)
+runs unchanged."""
+from flashnn_b200 import (DynamicQuantize, GemmA8W8, GemmWeightOnly,  # noqa: F401
+                          set_autotune_triton_kernels, set_use_triton)

@@ -1,0 +1,8 @@
+"""B200-native implementation of FLASHNN's quantized-GEMM operators
+(DynamicQuantize, GemmA8W8, GemmWeightOnly) behind the reference's module API."""
+from .kernel_backend import (get_autotune_triton_kernels, get_use_triton,
+                             set_autotune_triton_kernels, set_use_triton)
+from .quant_gemm import DynamicQuantize, GemmA8W8, GemmWeightOnly
+
+__all__ = ["DynamicQuantize", "GemmA8W8", "GemmWeightOnly", "set_use_triton",
+           "set_autotune_triton_kernels", "get_use_triton", "get_autotune_triton_kernels"]

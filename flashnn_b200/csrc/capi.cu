@@ -1,0 +1,99 @@
+// Status plumbing shared by every entry point of the C ABI: per-thread error
+// text, the per-device status word that kernels write when a bounded wait runs
+// out, and cached device properties.
+#include <cstdarg>
+#include <cstdio>
+#include <mutex>
+
+#include "common.cuh"
+
+namespace fnn {
+namespace {
+
+thread_local char g_error[512] = "";
+
+// One status word per device that loads the library; kernels reach it through
+// the address handed to them, host code through cudaMemcpyFromSymbol.
+__device__ int g_device_status = 0;
+
+constexpr int kMaxDevices = 64;
+int* g_status_addr[kMaxDevices];
+int g_sm_count[kMaxDevices];
+std::once_flag g_once[kMaxDevices];
+
+void init_device(int dev) {
+  void* p = nullptr;
+  if (cudaGetSymbolAddress(&p, g_device_status) == cudaSuccess) g_status_addr[dev] = static_cast<int*>(p);
+  int n = 0;
+  if (cudaDeviceGetAttribute(&n, cudaDevAttrMultiProcessorCount, dev) == cudaSuccess) g_sm_count[dev] = n;
+}
+
+int current_device() {
+  int dev = 0;
+  if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= kMaxDevices) return -1;
+  std::call_once(g_once[dev], init_device, dev);
+  return dev;
+}
+
+}  // namespace
+
+int fail(int status, const char* fmt, ...) {
+  va_list ap;
+  va_start(ap, fmt);
+  vsnprintf(g_error, sizeof(g_error), fmt, ap);
+  va_end(ap);
+  return status;
+}
+
+int check_cuda(cudaError_t e, const char* what) {
+  if (e == cudaSuccess) return FNN_OK;
+  return fail(FNN_ERR_CUDA, "%s: %s", what, cudaGetErrorString(e));
+}
+
+int* device_status_word() {
+  const int dev = current_device();
+  return dev < 0 ? nullptr : g_status_addr[dev];
+}
+
+int sm_count() {
+  const int dev = current_device();
+  return (dev < 0 || g_sm_count[dev] <= 0) ? 148 : g_sm_count[dev];
+}
+
+}  // namespace fnn
+
+extern "C" int fnn_version(void) { return FNN_VERSION; }
+
+extern "C" const char* fnn_last_error_string(void) { return fnn::g_error; }
+
+extern "C" const char* fnn_status_string(int status) {
+  switch (status) {
+    case FNN_OK: return "ok";
+    case FNN_ERR_NULL_POINTER: return "null pointer";
+    case FNN_ERR_DTYPE: return "unsupported dtype";
+    case FNN_ERR_SHAPE: return "bad shape";
+    case FNN_ERR_ALIGNMENT: return "bad alignment";
+    case FNN_ERR_UNSUPPORTED: return "unsupported combination";
+    case FNN_ERR_WORKSPACE: return "workspace too small";
+    case FNN_ERR_CUDA: return "CUDA error";
+    case FNN_ERR_DEVICE_TIMEOUT: return "device-side wait timed out";
+    default: return "unknown status";
+  }
+}
+
+extern "C" int fnn_device_status(int* device_code) {
+  using namespace fnn;
+  if (!device_code) return fail(FNN_ERR_NULL_POINTER, "device_status: null output pointer");
+  int* word = device_status_word();
+  if (!word) return fail(FNN_ERR_CUDA, "device_status: no current CUDA device");
+  if (int e = check_cuda(cudaDeviceSynchronize(), "device_status: synchronize")) return e;
+  int code = 0;
+  if (int e = check_cuda(cudaMemcpy(&code, word, sizeof(int), cudaMemcpyDeviceToHost), "device_status: read")) return e;
+  if (code != 0) {
+    const int zero = 0;
+    if (int e = check_cuda(cudaMemcpy(word, &zero, sizeof(int), cudaMemcpyHostToDevice), "device_status: clear")) return e;
+  }
+  *device_code = code;
+  if (code != 0) return fail(FNN_ERR_DEVICE_TIMEOUT, "a kernel gave up on a bounded wait (device code %d)", code);
+  return FNN_OK;
+}

@@ -1,0 +1,161 @@
+// Per-token dynamic int8 quantisation (the prologue of the A8W8 GEMM).
+//
+// One CTA owns one row.  The row is read from HBM once: every thread keeps its
+// 16-byte chunks in registers between the absmax reduction and the quantise
+// pass, so the traffic is 2 bytes in + 1 byte out per element.
+//
+// Arithmetic reproduces DynamicQuantize._torch_impl of the reference
+// (flashnn/quant_gemm.py:53-57), which works in the input dtype T:
+//     s = T(absmax / 127)            q = rint(T(x / s))          scale_out = half(s)
+// with IEEE division in fp32 followed by one rounding to T, exactly what the CPU
+// computes for 16-bit tensors.  The int8 cast saturates.
+#include "common.cuh"
+
+namespace fnn {
+namespace {
+
+constexpr int kDqThreads = 256;
+
+template <typename T> __device__ __forceinline__ float round_to(float v) {
+  return to_f32(from_f32<T>(v));
+}
+
+template <typename T> __device__ __forceinline__ int quantise_one(float x, float s) {
+  const float r = rintf(round_to<T>(__fdiv_rn(x, s)));
+  if (r != r) return 0;  // 0/0 on an all-zero row
+  return static_cast<int>(fminf(fmaxf(r, -128.f), 127.f));
+}
+
+__device__ __forceinline__ float block_max(float v, float* red) {
+#pragma unroll
+  for (int o = 16; o > 0; o >>= 1) v = fmaxf(v, __shfl_xor_sync(0xffffffffu, v, o));
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, nwarp = (blockDim.x + 31) >> 5;
+  if (lane == 0) red[warp] = v;
+  __syncthreads();
+  v = (lane < nwarp) ? red[lane] : 0.f;
+#pragma unroll
+  for (int o = 16; o > 0; o >>= 1) v = fmaxf(v, __shfl_xor_sync(0xffffffffu, v, o));
+  return v;
+}
+
+template <typename T> __device__ __forceinline__ float abs2max(uint32_t w) {
+  // two packed T values -> max(|lo|, |hi|) as fp32
+  T lo, hi;
+  const uint16_t l = static_cast<uint16_t>(w & 0x7fffu), h = static_cast<uint16_t>((w >> 16) & 0x7fffu);
+  lo = *reinterpret_cast<const T*>(&l);
+  hi = *reinterpret_cast<const T*>(&h);
+  return fmaxf(to_f32(lo), to_f32(hi));
+}
+
+template <typename T> __device__ __forceinline__ float lo_of(uint32_t w) {
+  const uint16_t l = static_cast<uint16_t>(w & 0xffffu);
+  return to_f32(*reinterpret_cast<const T*>(&l));
+}
+template <typename T> __device__ __forceinline__ float hi_of(uint32_t w) {
+  const uint16_t h = static_cast<uint16_t>(w >> 16);
+  return to_f32(*reinterpret_cast<const T*>(&h));
+}
+
+// Vector path: K % 8 == 0, 16-byte aligned rows in, 8-byte aligned rows out.
+// NCHUNK = 16-byte chunks per thread (row held in registers).
+template <typename T, int NCHUNK>
+__global__ void __launch_bounds__(kDqThreads)
+dq_row_vec_kernel(const T* __restrict__ x, int64_t ldx, int8_t* __restrict__ q, int64_t ldq,
+                  __half* __restrict__ scale, int K) {
+  __shared__ float red[32];
+  const int64_t row = blockIdx.x;
+  const uint4* xr = reinterpret_cast<const uint4*>(x + row * ldx);
+  const int nvec = K >> 3;
+  uint4 v[NCHUNK];
+  float amax = 0.f;
+#pragma unroll
+  for (int c = 0; c < NCHUNK; ++c) {
+    const int i = c * blockDim.x + threadIdx.x;
+    v[c] = (i < nvec) ? __ldcs(xr + i) : make_uint4(0, 0, 0, 0);
+    amax = fmaxf(amax, fmaxf(fmaxf(abs2max<T>(v[c].x), abs2max<T>(v[c].y)),
+                             fmaxf(abs2max<T>(v[c].z), abs2max<T>(v[c].w))));
+  }
+  amax = block_max(amax, red);
+  const float s = round_to<T>(__fdiv_rn(amax, 127.0f));
+  if (threadIdx.x == 0) scale[row] = __float2half_rn(s);
+  uint2* qr = reinterpret_cast<uint2*>(q + row * ldq);
+#pragma unroll
+  for (int c = 0; c < NCHUNK; ++c) {
+    const int i = c * blockDim.x + threadIdx.x;
+    if (i < nvec) {
+      const uint32_t w[4] = {v[c].x, v[c].y, v[c].z, v[c].w};
+      uint32_t o[2];
+#pragma unroll
+      for (int h = 0; h < 2; ++h) {
+        const int q0 = quantise_one<T>(lo_of<T>(w[2 * h]), s);
+        const int q1 = quantise_one<T>(hi_of<T>(w[2 * h]), s);
+        const int q2 = quantise_one<T>(lo_of<T>(w[2 * h + 1]), s);
+        const int q3 = quantise_one<T>(hi_of<T>(w[2 * h + 1]), s);
+        o[h] = (q0 & 0xff) | ((q1 & 0xff) << 8) | ((q2 & 0xff) << 16) | ((q3 & 0xff) << 24);
+      }
+      __stcs(qr + i, make_uint2(o[0], o[1]));
+    }
+  }
+}
+
+// Any K, any alignment, any row length: two passes over the row (the second
+// one is served by L2).
+template <typename T>
+__global__ void __launch_bounds__(kDqThreads)
+dq_row_generic_kernel(const T* __restrict__ x, int64_t ldx, int8_t* __restrict__ q, int64_t ldq,
+                      __half* __restrict__ scale, int K) {
+  __shared__ float red[32];
+  const int64_t row = blockIdx.x;
+  const T* xr = x + row * ldx;
+  float amax = 0.f;
+  for (int i = threadIdx.x; i < K; i += blockDim.x) amax = fmaxf(amax, fabsf(to_f32(xr[i])));
+  amax = block_max(amax, red);
+  const float s = round_to<T>(__fdiv_rn(amax, 127.0f));
+  if (threadIdx.x == 0) scale[row] = __float2half_rn(s);
+  int8_t* qr = q + row * ldq;
+  for (int i = threadIdx.x; i < K; i += blockDim.x)
+    qr[i] = static_cast<int8_t>(quantise_one<T>(to_f32(xr[i]), s));
+}
+
+template <typename T>
+int launch_dq(const T* x, int64_t M, int64_t K, int64_t ldx, int8_t* q, int64_t ldq, __half* scale,
+              cudaStream_t st) {
+  const bool vec = (K % 8 == 0) && (ldx % 8 == 0) && (ldq % 8 == 0) &&
+                   (reinterpret_cast<uintptr_t>(x) % 16 == 0) &&
+                   (reinterpret_cast<uintptr_t>(q) % 8 == 0) && (K <= int64_t(kDqThreads) * 8 * 16);
+  const dim3 grid(static_cast<unsigned>(M));
+  if (!vec) {
+    dq_row_generic_kernel<T><<<grid, kDqThreads, 0, st>>>(x, ldx, q, ldq, scale, int(K));
+    return check_cuda(cudaGetLastError(), "dynamic_quant (generic) launch");
+  }
+  const int nvec = int(K / 8);
+  int threads = ((nvec + 31) / 32) * 32;
+  if (threads > kDqThreads) threads = kDqThreads;
+  const int nchunk = (nvec + threads - 1) / threads;
+#define FNN_DQ_CASE(N)                                                                     \
+  dq_row_vec_kernel<T, N><<<grid, threads, 0, st>>>(x, ldx, q, ldq, scale, int(K))
+  if (nchunk <= 1) FNN_DQ_CASE(1);
+  else if (nchunk <= 2) FNN_DQ_CASE(2);
+  else if (nchunk <= 4) FNN_DQ_CASE(4);
+  else if (nchunk <= 8) FNN_DQ_CASE(8);
+  else FNN_DQ_CASE(16);
+#undef FNN_DQ_CASE
+  return check_cuda(cudaGetLastError(), "dynamic_quant launch");
+}
+
+}  // namespace
+}  // namespace fnn
+
+extern "C" int fnn_dynamic_quant(const void* x, int x_dtype, int64_t M, int64_t K, int64_t ldx,
+                                 int8_t* q, int64_t ldq, void* scale_f16, void* stream) {
+  using namespace fnn;
+  if (M < 0 || K < 0 || ldx < K || ldq < K) return fail(FNN_ERR_SHAPE, "dynamic_quant: M=%lld K=%lld ldx=%lld ldq=%lld", (long long)M, (long long)K, (long long)ldx, (long long)ldq);
+  if (x_dtype != FNN_F16 && x_dtype != FNN_BF16) return fail(FNN_ERR_DTYPE, "dynamic_quant: input must be f16 or bf16 (got dtype code %d)", x_dtype);
+  if (M == 0) return FNN_OK;
+  if (!x || !q || !scale_f16) return fail(FNN_ERR_NULL_POINTER, "dynamic_quant: null tensor pointer");
+  if (K == 0 || K > INT32_MAX || M > INT32_MAX) return fail(FNN_ERR_SHAPE, "dynamic_quant: K must be in [1, 2^31), M below 2^31");
+  cudaStream_t st = static_cast<cudaStream_t>(stream);
+  if (x_dtype == FNN_F16)
+    return launch_dq<__half>(static_cast<const __half*>(x), M, K, ldx, q, ldq, static_cast<__half*>(scale_f16), st);
+  return launch_dq<__nv_bfloat16>(static_cast<const __nv_bfloat16*>(x), M, K, ldx, q, ldq, static_cast<__half*>(scale_f16), st);
+}

@@ -1,0 +1,419 @@
+// A8W8 GEMM for sm_100a: int8 x int8 -> int32 on the 5th-generation tensor
+// cores (tcgen05.mma kind::i8), operands staged by TMA, accumulators in TMEM,
+// per-token x per-channel scaling fused into the epilogue.
+//
+// One persistent CTA per SM, six warps:
+//   warp 0      TMA producer   (one elected lane issues the bulk tensor loads)
+//   warp 1      MMA issuer     (one elected lane issues tcgen05.mma / commit; owns TMEM)
+//   warps 2-5   epilogue       (tcgen05.ld -> scale -> 16-bit store), one TMEM lane
+//                               quarter each (quarter = warp id % 4)
+// Shared memory holds a STAGES-deep ring of {A 128x128 B, B BNx128 B} tiles in
+// the 128-byte-swizzled K-major layout that both the TMA tensor map and the
+// UMMA shared-memory descriptor name.  TMEM holds two BN-column accumulators so
+// the epilogue of tile i overlaps the main loop of tile i+1.
+//
+// Every wait is bounded: a role that runs out of time records a code in the
+// device status word, raises the CTA's abort flag, and all roles fall through to
+// a common teardown that drains outstanding copies and MMAs and frees TMEM.
+#include <mutex>
+
+#include "common.cuh"
+
+namespace fnn {
+namespace {
+
+constexpr int kBM = 128;       // rows of A per tile (UMMA M)
+constexpr int kBK = 128;       // K bytes per stage = one 128-byte swizzle row
+constexpr int kUmmaK = 32;     // K per tcgen05.mma for 8-bit operands
+constexpr int kThreads = 192;  // 6 warps
+constexpr int kGroupM = 16;    // tiles along M that share a wave (L2 reuse of B)
+
+struct A8W8Params {
+  const void* alpha_row;
+  const void* alpha_col;
+  void* out;
+  int32_t* acc_out;
+  int64_t ldo, ldacc;
+  int row_dtype, col_dtype;
+  int M, N, K;
+  int tiles_m, tiles_n, k_blocks;
+  int* status;  // device status word
+};
+
+template <int BN, int STAGES> struct SmemLayout {
+  static constexpr int kABytes = kBM * kBK;
+  static constexpr int kBBytes = BN * kBK;
+  static constexpr int kStageBytes = kABytes + kBBytes;
+  static constexpr int kColScaleOff = STAGES * kStageBytes;         // [4][BN] float
+  static constexpr int kBarOff = kColScaleOff + 4 * BN * 4;          // barriers
+  static constexpr int kNumBars = 2 * STAGES + 4 + 1;                // full, empty, tmem full/empty x2, drain
+  static constexpr int kTmemSlotOff = kBarOff + kNumBars * 8;
+  static constexpr int kAbortOff = kTmemSlotOff + 8;
+  static constexpr int kTotal = kAbortOff + 8;
+  static constexpr int kDynamicBytes = kTotal + 1024;  // slack for manual 1024-byte alignment
+};
+
+__device__ __forceinline__ void tile_coords(int t, int tiles_m, int tiles_n, int& mb, int& nb) {
+  const int group_sz = kGroupM * tiles_n;
+  const int gid = t / group_sz;
+  const int first_m = gid * kGroupM;
+  const int gm = min(tiles_m - first_m, kGroupM);
+  const int r = t - gid * group_sz;
+  mb = first_m + r % gm;
+  nb = r / gm;
+}
+
+__device__ __forceinline__ void report(int* status, volatile int* abort_flag, int code) {
+  *abort_flag = code;
+  if (status) atomicCAS(status, 0, code);
+}
+
+template <typename OutT, int BN, int STAGES>
+__global__ void __launch_bounds__(kThreads, 1)
+a8w8_umma_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ CUtensorMap tmap_b,
+                 const A8W8Params p) {
+  using L = SmemLayout<BN, STAGES>;
+  extern __shared__ uint8_t smem_raw[];
+  uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
+  float* col_scale_smem = reinterpret_cast<float*>(smem + L::kColScaleOff);
+  uint64_t* bars = reinterpret_cast<uint64_t*>(smem + L::kBarOff);
+  uint64_t* full_bar = bars;
+  uint64_t* empty_bar = bars + STAGES;
+  uint64_t* tmem_full_bar = bars + 2 * STAGES;
+  uint64_t* tmem_empty_bar = bars + 2 * STAGES + 2;
+  uint64_t* drain_bar = bars + 2 * STAGES + 4;
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(smem + L::kTmemSlotOff);
+  volatile int* abort_flag = reinterpret_cast<volatile int*>(smem + L::kAbortOff);
+
+  const int warp = threadIdx.x >> 5;
+  const int lane = threadIdx.x & 31;
+  const int num_tiles = p.tiles_m * p.tiles_n;
+  constexpr uint32_t kTmemCols = 2 * BN;
+
+  if (threadIdx.x == 0) {
+    *abort_flag = 0;
+    for (int s = 0; s < STAGES; ++s) {
+      mbar_init(&full_bar[s], 1);
+      mbar_init(&empty_bar[s], 1);
+    }
+    for (int b = 0; b < 2; ++b) {
+      mbar_init(&tmem_full_bar[b], 1);
+      mbar_init(&tmem_empty_bar[b], 4);
+    }
+    mbar_init(drain_bar, 1);
+    mbar_fence_init();
+    tma_prefetch_desc(&tmap_a);
+    tma_prefetch_desc(&tmap_b);
+  }
+  if (warp == 1) {
+    tmem_alloc(tmem_slot, kTmemCols);
+    tmem_relinquish();
+  }
+  tc_fence_before();
+  __syncthreads();
+  tc_fence_after();
+  const uint32_t tmem_base = *tmem_slot;
+
+  if (warp == 0) {
+    // ------------------------------ TMA producer ------------------------------
+    const bool leader = elect_one();
+    int stage = 0;
+    uint32_t phase = 0;
+    long long issued = 0;
+    bool ok = true;
+    for (int t = blockIdx.x; t < num_tiles && ok; t += gridDim.x) {
+      int mb, nb;
+      tile_coords(t, p.tiles_m, p.tiles_n, mb, nb);
+      for (int kb = 0; kb < p.k_blocks; ++kb) {
+        ok = mbar_wait_bounded(&empty_bar[stage], phase ^ 1, abort_flag);
+        ok = __all_sync(0xffffffffu, ok);
+        if (!ok) {
+          if (leader) report(p.status, abort_flag, DEV_TIMEOUT_PRODUCER);
+          break;
+        }
+        if (leader) {
+          uint8_t* sa = smem + stage * L::kStageBytes;
+          mbar_expect_tx(&full_bar[stage], L::kStageBytes);
+          tma_load_2d(sa, &tmap_a, &full_bar[stage], kb * kBK, mb * kBM);
+          tma_load_2d(sa + L::kABytes, &tmap_b, &full_bar[stage], kb * kBK, nb * BN);
+          ++issued;
+        }
+        __syncwarp();
+        if (++stage == STAGES) { stage = 0; phase ^= 1; }
+      }
+    }
+    // Wait (bounded) until the last copies issued have landed, so that nothing
+    // writes this CTA's shared memory after it has exited, even after an abort.
+    if (leader) {
+      int none = 0;
+      const long long first = issued > STAGES ? issued - STAGES : 0;
+      for (long long i = first; i < issued; ++i)
+        if (!mbar_wait_bounded(&full_bar[i % STAGES], uint32_t((i / STAGES) & 1), &none)) {
+          report(p.status, abort_flag, DEV_TIMEOUT_DRAIN);
+          break;
+        }
+    }
+  } else if (warp == 1) {
+    // ------------------------------- MMA issuer -------------------------------
+    const bool leader = elect_one();
+    constexpr uint32_t idesc = umma_idesc(/*s32*/ 2, /*signed 8-bit*/ 1, kBM, BN);
+    int stage = 0;
+    uint32_t phase = 0;
+    int local = 0;
+    bool ok = true;
+    bool issued_any = false;
+    for (int t = blockIdx.x; t < num_tiles && ok; t += gridDim.x, ++local) {
+      const int buf = local & 1;
+      const uint32_t acc_phase = (local >> 1) & 1;
+      ok = mbar_wait_bounded(&tmem_empty_bar[buf], acc_phase ^ 1, abort_flag);
+      ok = __all_sync(0xffffffffu, ok);
+      if (!ok) {
+        if (leader) report(p.status, abort_flag, DEV_TIMEOUT_MMA);
+        break;
+      }
+      tc_fence_after();
+      const uint32_t tmem_d = tmem_base + buf * BN;
+      for (int kb = 0; kb < p.k_blocks; ++kb) {
+        ok = mbar_wait_bounded(&full_bar[stage], phase, abort_flag);
+        ok = __all_sync(0xffffffffu, ok);
+        if (!ok) {
+          if (leader) report(p.status, abort_flag, DEV_TIMEOUT_MMA);
+          break;
+        }
+        tc_fence_after();
+        if (leader) {
+          const uint32_t sa = smem_u32(smem + stage * L::kStageBytes);
+          const uint32_t sb = sa + L::kABytes;
+#pragma unroll
+          for (int k = 0; k < kBK / kUmmaK; ++k)
+            umma_i8(tmem_d, umma_desc_k_sw128(sa + k * kUmmaK), umma_desc_k_sw128(sb + k * kUmmaK),
+                    idesc, (kb | k) != 0 ? 1u : 0u);
+          tc_commit(&empty_bar[stage]);  // frees the smem stage once these MMAs have read it
+          issued_any = true;
+        }
+        __syncwarp();
+        if (++stage == STAGES) { stage = 0; phase ^= 1; }
+      }
+      if (ok && leader) tc_commit(&tmem_full_bar[buf]);  // accumulator complete
+      __syncwarp();
+    }
+    // Wait (bounded) for every MMA issued before TMEM is freed, even after an abort.
+    if (leader && issued_any) {
+      int none = 0;
+      tc_commit(drain_bar);
+      if (!mbar_wait_bounded(drain_bar, 0, &none)) report(p.status, abort_flag, DEV_TIMEOUT_DRAIN);
+    }
+  } else {
+    // -------------------------------- epilogue --------------------------------
+    const int quarter = warp & 3;
+    float* cs = col_scale_smem + quarter * BN;  // this warp's private copy
+    const bool same16 = (p.row_dtype == p.col_dtype) && (p.row_dtype != FNN_F32);
+    OutT* out = reinterpret_cast<OutT*>(p.out);
+    const bool vec_ok = (p.ldo % 8 == 0) && (reinterpret_cast<uintptr_t>(out) % 16 == 0);
+    const bool acc_vec_ok = p.acc_out && (p.ldacc % 4 == 0) && (reinterpret_cast<uintptr_t>(p.acc_out) % 16 == 0);
+    int local = 0;
+    bool ok = true;
+    for (int t = blockIdx.x; t < num_tiles && ok; t += gridDim.x, ++local) {
+      int mb, nb;
+      tile_coords(t, p.tiles_m, p.tiles_n, mb, nb);
+      const int buf = local & 1;
+      const uint32_t acc_phase = (local >> 1) & 1;
+      const int row = mb * kBM + quarter * 32 + lane;
+      const int n0 = nb * BN;
+      // column scales of this tile -> this warp's smem copy (fp32); row scale -> register
+      for (int j = lane; j < BN; j += 32)
+        cs[j] = (n0 + j < p.N) ? load_as_f32(p.alpha_col, p.col_dtype, n0 + j) : 0.f;
+      const float rs = (row < p.M) ? load_as_f32(p.alpha_row, p.row_dtype, row) : 0.f;
+      __syncwarp();
+
+      ok = mbar_wait_bounded(&tmem_full_bar[buf], acc_phase, abort_flag);
+      ok = __all_sync(0xffffffffu, ok);
+      if (!ok) {
+        if (lane == 0) report(p.status, abort_flag, DEV_TIMEOUT_EPILOGUE);
+        break;
+      }
+      tc_fence_after();
+      const uint32_t taddr = tmem_base + (uint32_t(quarter * 32) << 16) + buf * BN;
+#pragma unroll 1
+      for (int c = 0; c < BN / 32; ++c) {
+        uint32_t r[32];
+        tmem_ld_32x32(taddr + c * 32, r);
+        tc_wait_ld();
+        const int col0 = n0 + c * 32;
+        if (row < p.M && col0 < p.N) {
+          const bool full = col0 + 32 <= p.N;
+          if (p.acc_out) {
+            int32_t* arow = p.acc_out + int64_t(row) * p.ldacc + col0;
+            if (full && acc_vec_ok) {
+#pragma unroll
+              for (int j = 0; j < 32; j += 4)
+                *reinterpret_cast<uint4*>(arow + j) = make_uint4(r[j], r[j + 1], r[j + 2], r[j + 3]);
+            } else {
+#pragma unroll
+              for (int j = 0; j < 32; ++j)
+                if (col0 + j < p.N) arow[j] = int32_t(r[j]);
+            }
+          }
+          float v[32];
+#pragma unroll
+          for (int j = 0; j < 32; ++j) {
+            float s = __fmul_rn(rs, cs[c * 32 + j]);
+            if (same16) s = round_through(s, p.row_dtype);
+            v[j] = __fmul_rn(float(int32_t(r[j])), s);
+          }
+          OutT* orow = out + int64_t(row) * p.ldo + col0;
+          if (full && vec_ok) {
+#pragma unroll
+            for (int j = 0; j < 32; j += 8)
+              *reinterpret_cast<uint4*>(orow + j) =
+                  make_uint4(pack2<OutT>(v[j], v[j + 1]), pack2<OutT>(v[j + 2], v[j + 3]),
+                             pack2<OutT>(v[j + 4], v[j + 5]), pack2<OutT>(v[j + 6], v[j + 7]));
+          } else {
+#pragma unroll
+            for (int j = 0; j < 32; ++j)
+              if (col0 + j < p.N) orow[j] = from_f32<OutT>(v[j]);
+          }
+        }
+      }
+      tc_fence_before();
+      __syncwarp();
+      if (lane == 0) mbar_arrive(&tmem_empty_bar[buf]);
+    }
+  }
+
+  // -------------------------------- teardown --------------------------------
+  tc_fence_before();
+  __syncthreads();
+  if (warp == 1) {
+    tc_fence_after();
+    tmem_dealloc(tmem_base, kTmemCols);
+  }
+}
+
+// Any alignment, any strides: one thread per output element (correctness path
+// for operands the TMA path cannot address; also covers K == 0).
+template <typename OutT>
+__global__ void a8w8_generic_kernel(const int8_t* __restrict__ a, int64_t lda, const int8_t* __restrict__ b,
+                                    int64_t ldb, const A8W8Params p) {
+  const int64_t idx = int64_t(blockIdx.x) * blockDim.x + threadIdx.x;
+  if (idx >= int64_t(p.M) * p.N) return;
+  const int m = int(idx / p.N), n = int(idx % p.N);
+  const int8_t* ar = a + m * lda;
+  const int8_t* br = b + n * ldb;
+  int acc = 0;
+  for (int k = 0; k < p.K; ++k) acc += int(ar[k]) * int(br[k]);
+  if (p.acc_out) p.acc_out[m * p.ldacc + n] = acc;
+  const bool same16 = (p.row_dtype == p.col_dtype) && (p.row_dtype != FNN_F32);
+  float s = __fmul_rn(load_as_f32(p.alpha_row, p.row_dtype, m), load_as_f32(p.alpha_col, p.col_dtype, n));
+  if (same16) s = round_through(s, p.row_dtype);
+  reinterpret_cast<OutT*>(p.out)[m * p.ldo + n] = from_f32<OutT>(__fmul_rn(float(acc), s));
+}
+
+// ---------------------------------------------------------------------------
+// host side
+// ---------------------------------------------------------------------------
+using EncodeTiledFn = CUresult (*)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*,
+                                   const cuuint64_t*, const cuuint32_t*, const cuuint32_t*,
+                                   CUtensorMapInterleave, CUtensorMapSwizzle, CUtensorMapL2promotion,
+                                   CUtensorMapFloatOOBfill);
+
+EncodeTiledFn encode_tiled_fn() {
+  static EncodeTiledFn fn = nullptr;
+  static std::once_flag once;
+  std::call_once(once, [] {
+    void* sym = nullptr;
+    cudaDriverEntryPointQueryResult q;
+    if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &sym, cudaEnableDefault, &q) == cudaSuccess &&
+        q == cudaDriverEntryPointSuccess)
+      fn = reinterpret_cast<EncodeTiledFn>(sym);
+  });
+  return fn;
+}
+
+// int8 [rows, K] row-major (pitch `ld` bytes) -> tensor map with a {128 B, box_rows} box, 128-byte swizzle
+int make_tmap_i8(CUtensorMap* m, const void* base, int64_t rows, int64_t K, int64_t ld, int box_rows) {
+  EncodeTiledFn enc = encode_tiled_fn();
+  if (!enc) return fail(FNN_ERR_CUDA, "cuTensorMapEncodeTiled is not available from this driver");
+  const cuuint64_t dims[2] = {cuuint64_t(K), cuuint64_t(rows)};
+  const cuuint64_t strides[1] = {cuuint64_t(ld)};
+  const cuuint32_t box[2] = {cuuint32_t(kBK), cuuint32_t(box_rows)};
+  const cuuint32_t estr[2] = {1, 1};
+  const CUresult r = enc(m, CU_TENSOR_MAP_DATA_TYPE_UINT8, 2, const_cast<void*>(base), dims, strides, box, estr,
+                         CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B,
+                         CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+  if (r != CUDA_SUCCESS) return fail(FNN_ERR_CUDA, "cuTensorMapEncodeTiled failed with CUresult %d", int(r));
+  return FNN_OK;
+}
+
+template <typename OutT, int BN, int STAGES>
+int launch_umma(const int8_t* a, int64_t lda, const int8_t* b, int64_t ldb, A8W8Params p, cudaStream_t st) {
+  using L = SmemLayout<BN, STAGES>;
+  static_assert(L::kDynamicBytes <= 227 * 1024, "shared memory budget");
+  auto kern = a8w8_umma_kernel<OutT, BN, STAGES>;
+  static std::once_flag once[64];
+  int dev = 0;
+  cudaGetDevice(&dev);
+  cudaError_t attr_err = cudaSuccess;
+  std::call_once(once[dev & 63], [&] {
+    attr_err = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, L::kDynamicBytes);
+  });
+  if (attr_err != cudaSuccess) return check_cuda(attr_err, "cudaFuncSetAttribute(a8w8)");
+  CUtensorMap ta, tb;
+  if (int e = make_tmap_i8(&ta, a, p.M, p.K, lda, kBM)) return e;
+  if (int e = make_tmap_i8(&tb, b, p.N, p.K, ldb, BN)) return e;
+  p.tiles_m = (p.M + kBM - 1) / kBM;
+  p.tiles_n = (p.N + BN - 1) / BN;
+  p.k_blocks = (p.K + kBK - 1) / kBK;
+  const int tiles = p.tiles_m * p.tiles_n;
+  const int grid = tiles < sm_count() ? tiles : sm_count();
+  kern<<<grid, kThreads, L::kDynamicBytes, st>>>(ta, tb, p);
+  return check_cuda(cudaGetLastError(), "a8w8 tcgen05 launch");
+}
+
+template <typename OutT>
+int dispatch(const int8_t* a, int64_t lda, const int8_t* b, int64_t ldb, const A8W8Params& p, cudaStream_t st) {
+  const bool tma_ok = p.K > 0 && (reinterpret_cast<uintptr_t>(a) % 16 == 0) && (reinterpret_cast<uintptr_t>(b) % 16 == 0) &&
+                      (lda % 16 == 0) && (ldb % 16 == 0);
+  if (!tma_ok) {
+    const int64_t total = int64_t(p.M) * p.N;
+    a8w8_generic_kernel<OutT><<<unsigned((total + 255) / 256), 256, 0, st>>>(a, lda, b, ldb, p);
+    return check_cuda(cudaGetLastError(), "a8w8 generic launch");
+  }
+  // Tile width: the widest tile that still gives every SM work.
+  const int sms = sm_count();
+  const int tiles_m = (p.M + kBM - 1) / kBM;
+  if (tiles_m * ((p.N + 255) / 256) >= sms) return launch_umma<OutT, 256, 4>(a, lda, b, ldb, p, st);
+  if (tiles_m * ((p.N + 127) / 128) >= sms) return launch_umma<OutT, 128, 6>(a, lda, b, ldb, p, st);
+  return launch_umma<OutT, 64, 8>(a, lda, b, ldb, p, st);
+}
+
+}  // namespace
+}  // namespace fnn
+
+extern "C" size_t fnn_gemm_a8w8_workspace_bytes(int64_t, int64_t, int64_t) { return 0; }
+
+extern "C" int fnn_gemm_a8w8(const int8_t* a, int64_t lda, const int8_t* b, int64_t ldb, const void* alpha_row,
+                             int row_dtype, const void* alpha_col, int col_dtype, void* out, int out_dtype,
+                             int64_t ldo, int64_t M, int64_t N, int64_t K, int32_t* acc_out, int64_t ldacc,
+                             void* workspace, size_t workspace_bytes, void* stream) {
+  using namespace fnn;
+  (void)workspace;
+  (void)workspace_bytes;
+  if (M < 0 || N < 0 || K < 0 || lda < K || ldb < K || ldo < N || (acc_out && ldacc < N))
+    return fail(FNN_ERR_SHAPE, "gemm_a8w8: M=%lld N=%lld K=%lld lda=%lld ldb=%lld ldo=%lld", (long long)M,
+                (long long)N, (long long)K, (long long)lda, (long long)ldb, (long long)ldo);
+  if (M > INT32_MAX || N > INT32_MAX || K > INT32_MAX) return fail(FNN_ERR_SHAPE, "gemm_a8w8: sizes must be below 2^31");
+  if (out_dtype != FNN_F16 && out_dtype != FNN_BF16) return fail(FNN_ERR_DTYPE, "gemm_a8w8: output must be f16 or bf16 (got dtype code %d)", out_dtype);
+  if (row_dtype < FNN_F16 || row_dtype > FNN_F32 || col_dtype < FNN_F16 || col_dtype > FNN_F32)
+    return fail(FNN_ERR_DTYPE, "gemm_a8w8: scales must be f16, bf16 or f32 (got dtype codes %d, %d)", row_dtype, col_dtype);
+  if (M == 0 || N == 0) return FNN_OK;
+  if (!a || !b || !alpha_row || !alpha_col || !out) return fail(FNN_ERR_NULL_POINTER, "gemm_a8w8: null tensor pointer");
+  A8W8Params p{};
+  p.alpha_row = alpha_row; p.alpha_col = alpha_col; p.out = out; p.acc_out = acc_out;
+  p.ldo = ldo; p.ldacc = ldacc; p.row_dtype = row_dtype; p.col_dtype = col_dtype;
+  p.M = int(M); p.N = int(N); p.K = int(K);
+  p.status = device_status_word();
+  cudaStream_t st = static_cast<cudaStream_t>(stream);
+  if (out_dtype == FNN_F16) return dispatch<__half>(a, lda, b, ldb, p, st);
+  return dispatch<__nv_bfloat16>(a, lda, b, ldb, p, st);
+}

@@ -1,0 +1,148 @@
+/*
+ * flashnn_b200 -- C ABI of the B200 (sm_100a) quantized-GEMM kernels.
+ *
+ * The reference project has no FFI: its kernels are reached through Python
+ * launcher functions that take caller-allocated tensors
+ * (`triton_dynamic_quantize`, `triton_gemm_a8w8_forward`,
+ * `triton_gemm_a16w8_forward`, `triton_gemm_a16w4_forward`).  Each entry point
+ * below replaces one of those launchers and is cited beside it (paths are
+ * inside the reference project).  Conventions, all entry points:
+ *
+ *   - every pointer is a device pointer unless stated otherwise; the caller
+ *     owns all memory, the library allocates nothing on these paths;
+ *   - sizes are in elements, leading dimensions (`ld*`) in elements of the
+ *     tensor they belong to, row-major;
+ *   - work is enqueued on `stream` (a cudaStream_t passed as void*; NULL is the
+ *     default stream) and the call returns without synchronising;
+ *   - the return value is an `fnn_status`; nothing is thrown, nothing exits,
+ *     and on any non-zero status no kernel has been launched;
+ *   - the library is re-entrant; `fnn_last_error_string` is per host thread.
+ */
+#ifndef FLASHNN_B200_H
+#define FLASHNN_B200_H
+
+#include <stddef.h>
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+#define FNN_VERSION 100 /* major*10000 + minor*100 + patch */
+
+typedef enum fnn_status {
+  FNN_OK = 0,
+  FNN_ERR_NULL_POINTER = 1,  /* a required pointer is NULL */
+  FNN_ERR_DTYPE = 2,         /* dtype code not accepted for that argument */
+  FNN_ERR_SHAPE = 3,         /* negative/inconsistent sizes, ld smaller than the row */
+  FNN_ERR_ALIGNMENT = 4,     /* pointer or pitch breaks a documented alignment rule */
+  FNN_ERR_UNSUPPORTED = 5,   /* combination not implemented */
+  FNN_ERR_WORKSPACE = 6,     /* workspace missing or smaller than *_workspace_bytes says */
+  FNN_ERR_CUDA = 7,          /* a CUDA runtime/driver call failed; see fnn_last_error_string */
+  FNN_ERR_DEVICE_TIMEOUT = 8 /* a kernel gave up on a bounded wait (reported by fnn_device_status) */
+} fnn_status;
+
+typedef enum fnn_dtype {
+  FNN_F16 = 0,
+  FNN_BF16 = 1,
+  FNN_F32 = 2
+} fnn_dtype;
+
+/* Library version (FNN_VERSION of the build). */
+int fnn_version(void);
+
+/* Text of the last non-zero status returned on this host thread ("" if none). */
+const char* fnn_last_error_string(void);
+
+/* Name of a status code. */
+const char* fnn_status_string(int status);
+
+/*
+ * Reads and clears the current device's kernel status word.  Kernels never trap:
+ * a wait on an mbarrier that runs out of time records a code there, releases what
+ * the CTA holds and returns.  *device_code receives 0 when every kernel since the
+ * last call completed normally.  Synchronises the device.  Returns FNN_OK,
+ * FNN_ERR_DEVICE_TIMEOUT (with the code in *device_code) or FNN_ERR_CUDA.
+ */
+int fnn_device_status(int* device_code);
+
+/*
+ * Per-token dynamic int8 quantisation.
+ * Replaces `triton_dynamic_quantize(out, input, scale)`
+ * (flashnn/triton_kernels/dynamic_quant.py:73-97); arithmetic follows
+ * `DynamicQuantize._torch_impl` (flashnn/quant_gemm.py:53-57): absmax, scale =
+ * absmax/127 and x/scale are each rounded to the input dtype, the quotient is
+ * rounded half-to-even, and the int8 cast saturates (+128 becomes +127; the
+ * reference's cast wraps it to -128).  A row of zeros gives q = 0, scale = 0.
+ *
+ *   x      [M, K]  f16 or bf16 (x_dtype), leading dimension ldx
+ *   q      [M, K]  int8, leading dimension ldq
+ *   scale  [M]     f16
+ */
+int fnn_dynamic_quant(const void* x, int x_dtype, int64_t M, int64_t K, int64_t ldx,
+                      int8_t* q, int64_t ldq, void* scale_f16, void* stream);
+
+/*
+ * A8W8 GEMM:  out[m,n] = (sum_k a[m,k] * b[n,k]) * s(m,n)  cast to out_dtype.
+ * Replaces `triton_gemm_a8w8_forward(out, a, b, alpha_row, alpha_col)`
+ * (flashnn/triton_kernels/gemm_a8w8.py:182-221); the scale follows
+ * `GemmA8W8._torch_impl` (flashnn/quant_gemm.py:96-104): when both scales have
+ * the same 16-bit dtype, s = row*col rounded to that dtype; otherwise
+ * s = fl32(row*col); then out = fl32(float(acc) * s) rounded once to out_dtype.
+ * The accumulator is exact int32.
+ *
+ *   a          [M, K]  int8, lda      b          [N, K]  int8, ldb
+ *   alpha_row  [M]     row_dtype      alpha_col  [N]     col_dtype  (f16/bf16/f32)
+ *   out        [M, N]  f16 or bf16 (out_dtype), ldo
+ *   acc_out    optional [M, N] int32 (ldacc): when not NULL the raw accumulator is
+ *              written there as well (parity checks)
+ *   workspace  scratch of at least fnn_gemm_a8w8_workspace_bytes(M, N, K) bytes,
+ *              256-byte aligned; may be NULL when that function returns 0
+ *
+ * Fast path (TMA + tcgen05): a, b 16-byte aligned and lda, ldb multiples of 16.
+ * Anything else runs a slower generic kernel with the same results.
+ */
+int fnn_gemm_a8w8(const int8_t* a, int64_t lda, const int8_t* b, int64_t ldb,
+                  const void* alpha_row, int row_dtype, const void* alpha_col, int col_dtype,
+                  void* out, int out_dtype, int64_t ldo, int64_t M, int64_t N, int64_t K,
+                  int32_t* acc_out, int64_t ldacc, void* workspace, size_t workspace_bytes,
+                  void* stream);
+
+/* Scratch bytes fnn_gemm_a8w8 needs for this problem size on the current device. */
+size_t fnn_gemm_a8w8_workspace_bytes(int64_t M, int64_t N, int64_t K);
+
+/*
+ * Weight-only GEMM / GEMV:  out = act . dequant(W)^T (+ bias), W int8 or packed int4.
+ * Replaces `triton_gemm_a16w8_forward` (flashnn/triton_kernels/gemm_a16w8.py:275-338)
+ * and `triton_gemm_a16w4_forward` (flashnn/triton_kernels/gemm_a16w4.py:336-406).
+ * dequant(W)[n,k] = (W[n,k] - zp) * scale with zp, scale per channel n
+ * (group_size == 0) or per (k / group_size, n).  Products and sums are fp32, the
+ * dequantised weight is never rounded to 16 bits, the bias is added in fp32 and
+ * the result is rounded once to out_dtype.
+ *
+ *   act          [M, K]   f16 or bf16 (act_dtype), lda
+ *   qweight      weight_bits == 8: int8 [N, K]
+ *                weight_bits == 4: bytes [N/2, K]; byte (j,k) holds channel 2j in its
+ *                low nibble and channel 2j+1 in its high nibble, two's complement
+ *                (flashnn/quant_gemm.py:175-190).  Row pitch is K bytes in both cases.
+ *   scale        [N] (group_size == 0) or [K/group_size, N]; dtype scale_dtype
+ *   zero_points  NULL or same shape and dtype as scale
+ *   bias         NULL or [N] of dtype bias_dtype
+ *   out          [M, N]  out_dtype (f16 or bf16), ldo
+ *   workspace    scratch of at least fnn_gemm_weight_only_workspace_bytes(...) bytes,
+ *                256-byte aligned; may be NULL when that function returns 0
+ */
+int fnn_gemm_weight_only(const void* act, int act_dtype, int64_t lda, const void* qweight,
+                         int weight_bits, const void* scale, const void* zero_points,
+                         int scale_dtype, int64_t group_size, const void* bias, int bias_dtype,
+                         void* out, int out_dtype, int64_t ldo, int64_t M, int64_t N, int64_t K,
+                         void* workspace, size_t workspace_bytes, void* stream);
+
+/* Scratch bytes fnn_gemm_weight_only needs for this problem on the current device. */
+size_t fnn_gemm_weight_only_workspace_bytes(int64_t M, int64_t N, int64_t K, int weight_bits,
+                                            int64_t group_size);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* FLASHNN_B200_H */

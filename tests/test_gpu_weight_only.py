@@ -1,0 +1,118 @@
+"""GemmWeightOnly on the GPU (through the C ABI) against the fp32 dequant-matmul
+oracle (bound: |d| <= 1e-3 + 1e-2 |ref|) and the golden vectors of the reference."""
+import pytest
+import torch
+
+from oracle import quant_oracle as O
+from tests import golden_io as G
+
+pytestmark = pytest.mark.gpu
+WO = G.load("gemm_weight_only.npz")
+RTOL, ATOL = 1e-2, 1e-3  # the bound on weight-only outputs versus fp32 dequant-matmul
+
+
+def run(act, qw, scale, bias=None, zp=None):
+    import flashnn_b200
+    from flashnn_b200 import _lib
+    dev = lambda t: None if t is None else t.cuda()
+    out = flashnn_b200.GemmWeightOnly(act.dtype)(dev(act), dev(qw), dev(scale), dev(bias), dev(zp))
+    torch.cuda.synchronize()
+    assert _lib.device_status() == 0
+    return out.cpu()
+
+
+def assert_within_bound(out, act, qw, scale, bias, zp):
+    ref = O.gemm_weight_only_fp32(act, qw, scale, bias, zp)
+    # the kernel rounds once to the 16-bit output; allow that rounding on top of the stated bound
+    err = (out.float() - ref).abs()
+    bound = ATOL + RTOL * ref.abs()
+    assert bool((err <= bound).all()), f"max excess {(err - bound).max():.3e}"
+    # and it is at least as close as one final rounding of the fp32 result almost everywhere
+    exact = ref.to(out.dtype)
+    assert float((out != exact).float().mean()) < 0.02
+
+
+@pytest.mark.parametrize("name", sorted(WO))
+def test_golden_cases(name):
+    c = WO[name]
+    dt = G.dtype_of(c["dtype"])
+    act, qw, scale = G.tensor(c["act"], dt), G.tensor(c["qw"]), G.tensor(c["scale"], dt)
+    bias = G.tensor(c["bias"], dt) if "bias" in c else None
+    zp = G.tensor(c["zp"], dt) if "zp" in c else None
+    out = run(act, qw, scale, bias, zp)
+    assert_within_bound(out, act, qw, scale, bias, zp)
+    # against the reference's own output: it rounds w*s to 16 bits, so only a coarse bound holds
+    ref = G.tensor(c["out"], dt).float()
+    assert float((out.float() - ref).abs().max()) <= 0.02 * float(ref.abs().max())
+
+
+def make(kind, m, n, k, dt, group, use_bias, use_zp, seed):
+    g = torch.Generator().manual_seed(seed)
+    act = torch.randn(m, k, generator=g).to(dt)
+    if kind == 8:
+        qw = torch.randint(-127, 128, (n, k), generator=g, dtype=torch.int8)
+    else:
+        qw = O.pack_int4(torch.randint(-8, 8, (n, k), generator=g, dtype=torch.int8))
+    sshape = (n,) if group == 0 else (k // group, n)
+    scale = (torch.rand(*sshape, generator=g) * 0.045 + 0.005).to(dt)
+    bias = torch.randn(n, generator=g).to(dt) if use_bias else None
+    zp = torch.randint(-3, 4, sshape, generator=g).to(dt) if use_zp else None
+    return act, qw, scale, bias, zp
+
+
+# the reference's test shape (3, 1024, 4096) with group 64, all eight option combinations, int8
+# (tests/quant_gemm/test_gemm_weight_only.py:160-181), plus the same sweep for packed int4
+@pytest.mark.parametrize("kind", [8, 4])
+@pytest.mark.parametrize("use_bias", [False, True])
+@pytest.mark.parametrize("group", [0, 64])
+@pytest.mark.parametrize("use_zp", [False, True])
+def test_reference_test_shape(kind, use_bias, group, use_zp):
+    act, qw, scale, bias, zp = make(kind, 3, 1024, 4096, torch.float16, group, use_bias, use_zp, seed=kind + group)
+    out = run(act, qw, scale, bias, zp)
+    assert_within_bound(out, act, qw, scale, bias, zp)
+
+
+@pytest.mark.parametrize("kind,dt,group", [(4, torch.bfloat16, 128), (4, torch.float16, 128), (8, torch.bfloat16, 0),
+                                           (8, torch.float16, 128), (4, torch.bfloat16, 0), (8, torch.bfloat16, 256)])
+@pytest.mark.parametrize("m", [1, 2, 8, 9, 16])
+def test_decode_shapes(kind, dt, group, m):
+    act, qw, scale, bias, zp = make(kind, m, 272, 1024, dt, group, True, m % 2 == 0, seed=m)
+    out = run(act, qw, scale, bias, zp)
+    assert_within_bound(out, act, qw, scale, bias, zp)
+
+
+@pytest.mark.parametrize("kind,m,n,k,group", [(4, 17, 64, 256, 64), (8, 40, 50, 200, 0), (4, 3, 30, 96, 32),
+                                              (8, 2, 7, 33, 0), (4, 130, 128, 512, 128)])
+def test_generic_path_shapes(kind, m, n, k, group):
+    act, qw, scale, bias, zp = make(kind, m, n, k, torch.float16, group, True, True, seed=k)
+    out = run(act, qw, scale, bias, zp)
+    assert_within_bound(out, act, qw, scale, bias, zp)
+
+
+@pytest.mark.parametrize("m", [1, 4, 16])
+def test_a16w4_decode_config(m):
+    """A16W4 decode GEMV at N=28672, K=8192, group 128 (bf16)."""
+    from flashnn_b200 import workloads as W
+    w = W.a16w4_decode(m)
+    out = run(w["x"], w["qw"], w["scale"])
+    assert_within_bound(out, w["x"], w["qw"], w["scale"], None, None)
+
+
+def test_linearity_in_the_activations():
+    # size-independent property: f(2x) == 2 f(x) exactly (scaling by a power of two commutes with every rounding)
+    from flashnn_b200 import workloads as W
+    w = W.a16w4_decode(4, n=4096, k=4096)
+    o1 = run(w["x"], w["qw"], w["scale"])
+    o2 = run(w["x"] * 2, w["qw"], w["scale"])
+    assert torch.equal(o2.float(), o1.float() * 2)
+
+
+def test_weight_kind_is_inferred_from_shapes():
+    import flashnn_b200
+    act = torch.randn(2, 128, dtype=torch.float16).cuda()
+    qw = torch.zeros(24, 128, dtype=torch.int8).cuda()
+    with pytest.raises(AssertionError, match="only support int8 or int4x2"):
+        flashnn_b200.GemmWeightOnly()(act, qw, torch.ones(100, dtype=torch.float16).cuda())
+    with pytest.raises(AssertionError, match="Matrix B must be transposed"):
+        flashnn_b200.GemmWeightOnly()(act, torch.zeros(24, 64, dtype=torch.int8).cuda(),
+                                      torch.ones(24, dtype=torch.float16).cuda())
