@@ -123,17 +123,20 @@ __device__ __forceinline__ bool mbar_try_wait(uint64_t* bar, uint32_t parity) {
 constexpr uint64_t kWaitLimitNs = 2000000000ull;
 
 // Bounded wait: returns false when the limit ran out or another role already
-// reported a failure through *abort_flag (shared memory).
+// reported a failure through *abort_flag (shared memory).  Each try_wait may
+// suspend the thread in hardware for up to the hinted time, so a waiting warp
+// does not compete for issue slots.
 __device__ __forceinline__ bool mbar_wait_bounded(uint64_t* bar, uint32_t parity,
                                                   volatile int* abort_flag) {
   uint32_t done;
   const uint32_t addr = smem_u32(bar);
+  const uint32_t hint_ns = 200000u;
   asm volatile(
       "{\n\t.reg .pred p;\n\t"
-      "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
+      "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2, %3;\n\t"
       "selp.u32 %0, 1, 0, p;\n\t}\n"
       : "=r"(done)
-      : "r"(addr), "r"(parity)
+      : "r"(addr), "r"(parity), "r"(hint_ns)
       : "memory");
   if (done) return true;
   const uint64_t t0 = global_timer_ns();
@@ -141,13 +144,13 @@ __device__ __forceinline__ bool mbar_wait_bounded(uint64_t* bar, uint32_t parity
   while (true) {
     asm volatile(
         "{\n\t.reg .pred p;\n\t"
-        "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
+        "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2, %3;\n\t"
         "selp.u32 %0, 1, 0, p;\n\t}\n"
         : "=r"(done)
-        : "r"(addr), "r"(parity)
+        : "r"(addr), "r"(parity), "r"(hint_ns)
         : "memory");
     if (done) return true;
-    if ((++spins & 0x3ff) == 0) {
+    if ((++spins & 0xf) == 0) {
       if (*abort_flag != 0) return false;
       if (global_timer_ns() - t0 > kWaitLimitNs) return false;
     }

@@ -9,12 +9,19 @@
 //     s = T(absmax / 127)            q = rint(T(x / s))          scale_out = half(s)
 // with IEEE division in fp32 followed by one rounding to T, exactly what the CPU
 // computes for 16-bit tensors.  The int8 cast saturates.
+//
+// The per-element division is replaced by a multiplication with 1/s plus a check:
+// x * (1/s) is within 2 ulp of the true quotient, so rounding it to T gives the
+// same value unless it lies within a few ulp of a midpoint between two T values;
+// only those rare elements take the exact division.  rint and the int8 cast are
+// one magic-number addition (no conversion instructions).
 #include "common.cuh"
 
 namespace fnn {
 namespace {
 
-constexpr int kDqThreads = 256;
+constexpr int kDqThreads = 256;     // block size of the generic kernel
+constexpr int kDqMaxThreads = 1024;  // largest block of the vector kernel
 
 template <typename T> __device__ __forceinline__ float round_to(float v) {
   return to_f32(from_f32<T>(v));
@@ -24,6 +31,22 @@ template <typename T> __device__ __forceinline__ int quantise_one(float x, float
   const float r = rintf(round_to<T>(__fdiv_rn(x, s)));
   if (r != r) return 0;  // 0/0 on an all-zero row
   return static_cast<int>(fminf(fmaxf(r, -128.f), 127.f));
+}
+
+// Bits of fp32 that a conversion to T drops, and the midpoint pattern among them.
+template <typename T> struct DropBits;
+template <> struct DropBits<__nv_bfloat16> { static constexpr uint32_t mask = 0xFFFFu, mid = 0x8000u; };
+template <> struct DropBits<__half> { static constexpr uint32_t mask = 0x1FFFu, mid = 0x1000u; };
+
+// Same result as quantise_one for s > 0, returned in the low byte (two's complement).
+template <typename T> __device__ __forceinline__ uint32_t quantise_fast(float x, float s, float inv_s) {
+  float r = __fmul_rn(x, inv_s);
+  // ambiguous when the dropped bits are within 3 ulp of the rounding midpoint
+  const uint32_t d = (__float_as_uint(r) & DropBits<T>::mask) - (DropBits<T>::mid - 3u);
+  if (d <= 6u) r = __fdiv_rn(x, s);
+  const float t = fminf(round_to<T>(r), 127.f);  // |t| <= 128; only +128 needs the clamp
+  // 1.5 * 2^23 + t rounds t half-to-even and leaves the integer in the low mantissa bits
+  return __float_as_uint(__fadd_rn(t, 12582912.f));
 }
 
 __device__ __forceinline__ float block_max(float v, float* red) {
@@ -59,7 +82,7 @@ template <typename T> __device__ __forceinline__ float hi_of(uint32_t w) {
 // Vector path: K % 8 == 0, 16-byte aligned rows in, 8-byte aligned rows out.
 // NCHUNK = 16-byte chunks per thread (row held in registers).
 template <typename T, int NCHUNK>
-__global__ void __launch_bounds__(kDqThreads)
+__global__ void __launch_bounds__(kDqMaxThreads)
 dq_row_vec_kernel(const T* __restrict__ x, int64_t ldx, int8_t* __restrict__ q, int64_t ldq,
                   __half* __restrict__ scale, int K) {
   __shared__ float red[32];
@@ -79,6 +102,28 @@ dq_row_vec_kernel(const T* __restrict__ x, int64_t ldx, int8_t* __restrict__ q, 
   const float s = round_to<T>(__fdiv_rn(amax, 127.0f));
   if (threadIdx.x == 0) scale[row] = __float2half_rn(s);
   uint2* qr = reinterpret_cast<uint2*>(q + row * ldq);
+  if (!(s > 0.f)) {
+    // all-zero row (or a scale that underflowed to zero in T): fall back to the plain form
+#pragma unroll
+    for (int c = 0; c < NCHUNK; ++c) {
+      const int i = c * blockDim.x + threadIdx.x;
+      if (i < nvec) {
+        const uint32_t w[4] = {v[c].x, v[c].y, v[c].z, v[c].w};
+        uint32_t o[2];
+#pragma unroll
+        for (int h = 0; h < 2; ++h) {
+          const int q0 = quantise_one<T>(lo_of<T>(w[2 * h]), s);
+          const int q1 = quantise_one<T>(hi_of<T>(w[2 * h]), s);
+          const int q2 = quantise_one<T>(lo_of<T>(w[2 * h + 1]), s);
+          const int q3 = quantise_one<T>(hi_of<T>(w[2 * h + 1]), s);
+          o[h] = (q0 & 0xff) | ((q1 & 0xff) << 8) | ((q2 & 0xff) << 16) | ((q3 & 0xff) << 24);
+        }
+        __stcs(qr + i, make_uint2(o[0], o[1]));
+      }
+    }
+    return;
+  }
+  const float inv_s = __frcp_rn(s);
 #pragma unroll
   for (int c = 0; c < NCHUNK; ++c) {
     const int i = c * blockDim.x + threadIdx.x;
@@ -87,11 +132,12 @@ dq_row_vec_kernel(const T* __restrict__ x, int64_t ldx, int8_t* __restrict__ q, 
       uint32_t o[2];
 #pragma unroll
       for (int h = 0; h < 2; ++h) {
-        const int q0 = quantise_one<T>(lo_of<T>(w[2 * h]), s);
-        const int q1 = quantise_one<T>(hi_of<T>(w[2 * h]), s);
-        const int q2 = quantise_one<T>(lo_of<T>(w[2 * h + 1]), s);
-        const int q3 = quantise_one<T>(hi_of<T>(w[2 * h + 1]), s);
-        o[h] = (q0 & 0xff) | ((q1 & 0xff) << 8) | ((q2 & 0xff) << 16) | ((q3 & 0xff) << 24);
+        const uint32_t q0 = quantise_fast<T>(lo_of<T>(w[2 * h]), s, inv_s);
+        const uint32_t q1 = quantise_fast<T>(hi_of<T>(w[2 * h]), s, inv_s);
+        const uint32_t q2 = quantise_fast<T>(lo_of<T>(w[2 * h + 1]), s, inv_s);
+        const uint32_t q3 = quantise_fast<T>(hi_of<T>(w[2 * h + 1]), s, inv_s);
+        // gather the four low bytes
+        o[h] = __byte_perm(__byte_perm(q0, q1, 0x0040), __byte_perm(q2, q3, 0x0040), 0x5410);
       }
       __stcs(qr + i, make_uint2(o[0], o[1]));
     }
@@ -122,23 +168,23 @@ int launch_dq(const T* x, int64_t M, int64_t K, int64_t ldx, int8_t* q, int64_t 
               cudaStream_t st) {
   const bool vec = (K % 8 == 0) && (ldx % 8 == 0) && (ldq % 8 == 0) &&
                    (reinterpret_cast<uintptr_t>(x) % 16 == 0) &&
-                   (reinterpret_cast<uintptr_t>(q) % 8 == 0) && (K <= int64_t(kDqThreads) * 8 * 16);
+                   (reinterpret_cast<uintptr_t>(q) % 8 == 0) && (K <= int64_t(kDqMaxThreads) * 8 * 8);
   const dim3 grid(static_cast<unsigned>(M));
   if (!vec) {
     dq_row_generic_kernel<T><<<grid, kDqThreads, 0, st>>>(x, ldx, q, ldq, scale, int(K));
     return check_cuda(cudaGetLastError(), "dynamic_quant (generic) launch");
   }
+  // block size: the smallest of 256 / 512 / 1024 that keeps a thread at <= 4 chunks, if any does
   const int nvec = int(K / 8);
   int threads = ((nvec + 31) / 32) * 32;
-  if (threads > kDqThreads) threads = kDqThreads;
+  if (threads > 256) threads = (nvec <= 256 * 4) ? 256 : (nvec <= 512 * 4) ? 512 : kDqMaxThreads;
   const int nchunk = (nvec + threads - 1) / threads;
 #define FNN_DQ_CASE(N)                                                                     \
   dq_row_vec_kernel<T, N><<<grid, threads, 0, st>>>(x, ldx, q, ldq, scale, int(K))
   if (nchunk <= 1) FNN_DQ_CASE(1);
   else if (nchunk <= 2) FNN_DQ_CASE(2);
   else if (nchunk <= 4) FNN_DQ_CASE(4);
-  else if (nchunk <= 8) FNN_DQ_CASE(8);
-  else FNN_DQ_CASE(16);
+  else FNN_DQ_CASE(8);
 #undef FNN_DQ_CASE
   return check_cuda(cudaGetLastError(), "dynamic_quant launch");
 }

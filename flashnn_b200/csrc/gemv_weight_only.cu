@@ -2,10 +2,10 @@
 // activations x int8 or packed-int4 weights, per-channel or group-wise scales.
 //
 // The op is HBM-bound (every weight byte is read exactly once), so the kernel is
-// built around 128-bit weight loads that go straight into registers:
+// built around 16-byte-per-lane asynchronous weight copies and register-level expansion:
 //   - a CTA owns 16 output channels (8 packed rows for int4, 16 rows for int8)
 //     and its 8 warps split K;
-//   - each lane expands its weight bytes to exact 16-bit integers with
+//   - each lane expands its weight bytes to 16-bit floats with
 //     PRMT/LOP3 bit tricks (no int->float conversions) and uses them as the
 //     16 x 16 operand of mma.sync.m16n8k16; the activations are the narrow
 //     16 x 8 operand, so one weight fragment serves up to 8 tokens (two MMAs
@@ -15,17 +15,19 @@
 //     rounded to 16 bits;
 //   - partial sums of the 8 warps meet in shared memory; bias is added in fp32
 //     and the result is rounded once.
-// Zero-points are applied as  -zp * s * sum_k x  per group, with the per-group
-// activation sums produced by a small prologue kernel in caller-provided scratch.
+// The int4 fragments carry a constant offset (and zero-points add another): both are
+// removed per group as  -(offset + zp) * s * sum_k x, with sum_k x produced in the
+// accumulator layout by a second MMA against an all-ones operand.
+#include <type_traits>
+
 #include "common.cuh"
 
 namespace fnn {
+constexpr int kStepK = 64;   // K covered by one warp-wide 128-bit load per row (4 lanes x 16 B)
 namespace {
 
 constexpr int kGemvWarps = 8;
 constexpr int kGemvThreads = kGemvWarps * 32;
-constexpr int kStepK = 64;   // K covered by one warp-wide 128-bit load per row (4 lanes x 16 B)
-constexpr int kBatch = 4;    // loads in flight per lane
 
 struct WoParams {
   const void* act;      // [M, K] T
@@ -33,17 +35,22 @@ struct WoParams {
   const void* scale;    // [N] or [G, N]
   const void* zp;       // nullptr or like scale
   const void* bias;     // nullptr or [N]
-  const float* xsum;    // [M, G] activation sums per group (only with zero-points)
   void* out;
   int64_t lda, ldo;
   int scale_dtype, bias_dtype;
   int M, N, K;
   int group;  // 0 = per channel
-  int G;      // number of groups along K (1 when per channel)
+  int* status;  // device status word
 };
 
 template <typename T> struct Mma;
 template <> struct Mma<__half> {
+  // d = a * b (no accumulator input)
+  static __device__ __forceinline__ void run0(float (&d)[4], const uint32_t (&a)[4], uint32_t b0, uint32_t b1) {
+    asm volatile("mma.sync.aligned.m16n8k16.row.col.f32.f16.f16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%10,%10,%10,%10};"
+                 : "=f"(d[0]), "=f"(d[1]), "=f"(d[2]), "=f"(d[3])
+                 : "r"(a[0]), "r"(a[1]), "r"(a[2]), "r"(a[3]), "r"(b0), "r"(b1), "f"(0.f));
+  }
   static __device__ __forceinline__ void run(float (&d)[4], const uint32_t (&a)[4], uint32_t b0, uint32_t b1) {
     asm volatile("mma.sync.aligned.m16n8k16.row.col.f32.f16.f16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};"
                  : "+f"(d[0]), "+f"(d[1]), "+f"(d[2]), "+f"(d[3])
@@ -51,6 +58,11 @@ template <> struct Mma<__half> {
   }
 };
 template <> struct Mma<__nv_bfloat16> {
+  static __device__ __forceinline__ void run0(float (&d)[4], const uint32_t (&a)[4], uint32_t b0, uint32_t b1) {
+    asm volatile("mma.sync.aligned.m16n8k16.row.col.f32.bf16.bf16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%10,%10,%10,%10};"
+                 : "=f"(d[0]), "=f"(d[1]), "=f"(d[2]), "=f"(d[3])
+                 : "r"(a[0]), "r"(a[1]), "r"(a[2]), "r"(a[3]), "r"(b0), "r"(b1), "f"(0.f));
+  }
   static __device__ __forceinline__ void run(float (&d)[4], const uint32_t (&a)[4], uint32_t b0, uint32_t b1) {
     asm volatile("mma.sync.aligned.m16n8k16.row.col.f32.bf16.bf16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};"
                  : "+f"(d[0]), "+f"(d[1]), "+f"(d[2]), "+f"(d[3])
@@ -67,36 +79,40 @@ __device__ __forceinline__ uint32_t sub2(uint32_t a, uint32_t b, __half) {
   __half2 r = __hsub2(*reinterpret_cast<__half2*>(&a), *reinterpret_cast<__half2*>(&b));
   return *reinterpret_cast<uint32_t*>(&r);
 }
-__device__ __forceinline__ uint32_t sub2(uint32_t a, uint32_t b, __nv_bfloat16) {
-  __nv_bfloat162 r = __hsub2(*reinterpret_cast<__nv_bfloat162*>(&a), *reinterpret_cast<__nv_bfloat162*>(&b));
-  return *reinterpret_cast<uint32_t*>(&r);
-}
 
 // Four packed bytes (4 consecutive k of one packed row) -> the MMA A fragment:
 //   a[0] = low nibbles  (channel 2j)   at k0, k0+1      a[1] = high nibbles (channel 2j+1) at k0, k0+1
 //   a[2] = low nibbles  (channel 2j)   at k0+2, k0+3    a[3] = high nibbles (channel 2j+1) at k0+2, k0+3
-// each as an exact signed integer in T.
-template <typename T> __device__ __forceinline__ void dequant_int4(uint32_t w, uint32_t (&a)[4]);
-template <> __device__ __forceinline__ void dequant_int4<__nv_bfloat16>(uint32_t w, uint32_t (&a)[4]) {
-  // byte = 0x80 | ((n ^ 8) << 3) under a 0x41 high byte is the bf16 value 16 + (n ^ 8) = n_signed + 24
-  const uint32_t lo = ((w << 3) & 0x78787878u) ^ 0xC0C0C0C0u;
-  const uint32_t hi = ((w >> 1) & 0x78787878u) ^ 0xC0C0C0C0u;
-  const uint32_t m = 0x41414141u, off = 0x41C041C0u;  // 24.0 twice
-  a[0] = sub2(prmt(lo, m, 0x4140), off, __nv_bfloat16());
-  a[1] = sub2(prmt(hi, m, 0x4140), off, __nv_bfloat16());
-  a[2] = sub2(prmt(lo, m, 0x4342), off, __nv_bfloat16());
-  a[3] = sub2(prmt(hi, m, 0x4342), off, __nv_bfloat16());
-}
-template <> __device__ __forceinline__ void dequant_int4<__half>(uint32_t w, uint32_t (&a)[4]) {
-  // byte = n ^ 8 under a 0x64 high byte is the fp16 value 1024 + (n ^ 8) = n_signed + 1032
-  const uint32_t lo = (w & 0x0F0F0F0Fu) ^ 0x08080808u;
-  const uint32_t hi = ((w >> 4) & 0x0F0F0F0Fu) ^ 0x08080808u;
-  const uint32_t m = 0x64646464u, off = 0x64086408u;  // 1032.0 twice
-  a[0] = sub2(prmt(lo, m, 0x4140), off, __half());
-  a[1] = sub2(prmt(hi, m, 0x4140), off, __half());
-  a[2] = sub2(prmt(lo, m, 0x4342), off, __half());
-  a[3] = sub2(prmt(hi, m, 0x4342), off, __half());
-}
+// The fragment holds kAlpha * (n + kOffset) for the signed nibble n, exactly, built with logic ops and
+// byte permutes only: no conversion and no subtraction per element.  The constant part is taken out
+// once per scale group:  sum_k n_k x_k = (sum_k a_k x_k) / kAlpha - kOffset * sum_k x_k.
+template <typename T> struct Ones;  // two packed 1.0 values
+template <> struct Ones<__nv_bfloat16> { static constexpr uint32_t v = 0x3F803F80u; };
+template <> struct Ones<__half> { static constexpr uint32_t v = 0x3C003C00u; };
+
+template <typename T> struct Int4Frag;
+template <> struct Int4Frag<__nv_bfloat16> {
+  // byte (n ^ 8) under a 0x43 high byte is the bf16 value 128 + (n ^ 8) = n + 136
+  static constexpr float kInvAlpha = 1.f, kOffset = 136.f;
+  static __device__ __forceinline__ void make(uint32_t w, uint32_t (&a)[4]) {
+    const uint32_t lo = (w & 0x0F0F0F0Fu) ^ 0x08080808u;
+    const uint32_t hi = ((w >> 4) & 0x0F0F0F0Fu) ^ 0x08080808u;
+    const uint32_t m = 0x43434343u;
+    a[0] = prmt(lo, m, 0x4140); a[1] = prmt(hi, m, 0x4140);
+    a[2] = prmt(lo, m, 0x4342); a[3] = prmt(hi, m, 0x4342);
+  }
+};
+template <> struct Int4Frag<__half> {
+  // byte ((n ^ 8) << 4) under a 0x64 high byte is the fp16 value 1024 + 16 (n ^ 8) = 16 (n + 72)
+  static constexpr float kInvAlpha = 0.0625f, kOffset = 72.f;
+  static __device__ __forceinline__ void make(uint32_t w, uint32_t (&a)[4]) {
+    const uint32_t lo = ((w << 4) & 0xF0F0F0F0u) ^ 0x80808080u;
+    const uint32_t hi = (w & 0xF0F0F0F0u) ^ 0x80808080u;
+    const uint32_t m = 0x64646464u;
+    a[0] = prmt(lo, m, 0x4140); a[1] = prmt(hi, m, 0x4140);
+    a[2] = prmt(lo, m, 0x4342); a[3] = prmt(hi, m, 0x4342);
+  }
+};
 
 // Four int8 (4 consecutive k of one weight row) -> two fragment registers (k0,k0+1), (k0+2,k0+3).
 template <typename T> __device__ __forceinline__ void dequant_int8(uint32_t w, uint32_t& r01, uint32_t& r23);
@@ -118,124 +134,216 @@ template <> __device__ __forceinline__ void dequant_int8<__nv_bfloat16>(uint32_t
   r23 = pack2<__nv_bfloat16>(f2, f3);
 }
 
-template <typename T, int BITS, int NT>
-__global__ void __launch_bounds__(kGemvThreads)
+template <typename T> __device__ __forceinline__ float lo16_f32(uint32_t v);
+template <typename T> __device__ __forceinline__ float hi16_f32(uint32_t v);
+template <> __device__ __forceinline__ float lo16_f32<__nv_bfloat16>(uint32_t v) { return __uint_as_float(v << 16); }
+template <> __device__ __forceinline__ float hi16_f32<__nv_bfloat16>(uint32_t v) { return __uint_as_float(v & 0xFFFF0000u); }
+template <> __device__ __forceinline__ float lo16_f32<__half>(uint32_t v) { return __low2float(*reinterpret_cast<__half2*>(&v)); }
+template <> __device__ __forceinline__ float hi16_f32<__half>(uint32_t v) { return __high2float(*reinterpret_cast<__half2*>(&v)); }
+
+constexpr int kRing = 8;  // steps (of 64 k) a lane keeps in flight in its shared-memory FIFO
+
+template <int BITS> struct GemvSmem {
+  static constexpr int kLaneBytes = (BITS == 4) ? 16 : 32;    // bytes per lane per step
+  static constexpr int kSlotBytes = 32 * kLaneBytes;          // one step of one warp
+  static constexpr int kWarpBytes = kRing * kSlotBytes;       // [slot][lane]
+  static constexpr int kBytes = kGemvWarps * kWarpBytes;
+};
+
+__device__ __forceinline__ void cp_async16(uint32_t smem_dst, const void* gsrc) {
+  asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"(smem_dst), "l"(gsrc) : "memory");
+}
+__device__ __forceinline__ void cp_async_commit() { asm volatile("cp.async.commit_group;" ::: "memory"); }
+template <int N> __device__ __forceinline__ void cp_async_wait() {
+  asm volatile("cp.async.wait_group %0;" ::"n"(N) : "memory");
+}
+__device__ __forceinline__ uint4 lds128(uint32_t addr) {
+  uint4 v;
+  asm volatile("ld.shared.v4.u32 {%0, %1, %2, %3}, [%4];" : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w) : "r"(addr));
+  return v;
+}
+
+// One CTA per row group (16 output channels); its 8 warps split K into equal slices.  Every lane
+// streams exactly the weight bytes its own MMA fragments need: 16 bytes per step (64 k) of one
+// packed row, copied asynchronously from HBM into the lane's private slot of a shared-memory FIFO
+// (cp.async, kRing steps deep, no registers held, no cross-lane traffic, waits stall in hardware
+// rather than spin), then read back with one 128-bit shared load.
+//   SPU    steps (of 64 k) per partial-sum flush: the scale group for group-wise scales (64, 128 or
+//          256), a pseudo-group of 64 or 128 for per-channel scales.  At every flush the fp32 MMA
+//          accumulator is corrected for the fragment offset / zero-point, scaled, and added to the
+//          running total; partial sums therefore stay small.  The correction needs sum_k x over the
+//          group: a second MMA per fragment with an all-ones operand produces it in the accumulator
+//          layout, on the otherwise idle tensor pipe.
+//   PERCH  per-channel scales: the flush uses scale 1 and the channel scale is applied at the end.
+// Host guarantees: K % 512 == 0, the warp slice K/8 is a whole number of flush groups, scale dtype == T
+// for group-wise scales.  Tokens beyond M are computed from a clamped (duplicate) row and never stored.
+template <typename T, int BITS, int NT, int SPU, bool PERCH>
+__global__ void __launch_bounds__(kGemvThreads, (BITS == 4 && NT == 1) ? 4 : 2)
 gemv_mma_kernel(const WoParams p) {
+  using S = GemvSmem<BITS>;
+  extern __shared__ __align__(128) uint8_t smem[];
   __shared__ float red[kGemvWarps][NT][4][32];
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int g = lane >> 2, tig = lane & 3;
-  const int ch_base = blockIdx.x * 16;
-  // channels behind accumulator registers {0,1} and {2,3}
-  const int ch_a = (BITS == 4) ? ch_base + 2 * g : ch_base + g;
+  const int rg = blockIdx.x;
+  // channels behind accumulator registers {0,1} (ch_a) and {2,3} (ch_b)
+  const int ch_a = (BITS == 4) ? rg * 16 + 2 * g : rg * 16 + g;
   const int ch_b = (BITS == 4) ? ch_a + 1 : ch_a + 8;
-  // weight rows this lane streams (clamped; out-of-range channels are never stored)
   const int64_t last_row = (BITS == 4 ? p.N / 2 : p.N) - 1;
-  const int64_t row_a = min(int64_t(BITS == 4 ? ch_base / 2 + g : ch_a), last_row);
-  const int64_t row_b = min(int64_t(ch_b), last_row);  // int8 only
-  const uint8_t* wa = p.qw + row_a * p.K + tig * 16;
-  const uint8_t* wb = p.qw + row_b * p.K + tig * 16;
-  const T* act = reinterpret_cast<const T*>(p.act);
+  const int steps_w = p.K / (kStepK * kGemvWarps);
+  const int k_begin = warp * steps_w * kStepK;
+  const uint8_t* wp = p.qw + min(int64_t(BITS == 4 ? rg * 8 + g : ch_a), last_row) * p.K + k_begin + tig * 16;
+  const uint8_t* wp2 = p.qw + min(int64_t(ch_b), last_row) * p.K + k_begin + tig * 16;  // int8 only
+  const uint32_t fifo = smem_u32(smem) + warp * S::kWarpBytes + lane * S::kLaneBytes;
 
-  // K range of this warp, in units of one scale group (or of 64 when per channel)
-  const int unit = p.group > 0 ? p.group : kStepK;
-  const int units = p.K / unit;
-  const int u0 = int(int64_t(units) * warp / kGemvWarps), u1 = int(int64_t(units) * (warp + 1) / kGemvWarps);
-  const int steps_per_unit = unit / kStepK;
+  // copy of step (base + J) into FIFO slot J; pointers are advanced by the caller, offsets are immediates
+  auto issue = [&](int slot, const uint8_t* w, const uint8_t* w2) {
+    cp_async16(fifo + slot * S::kSlotBytes, w);
+    if (BITS == 8) cp_async16(fifo + slot * S::kSlotBytes + 16, w2);
+  };
+  // prologue: the first kRing steps (every step commits a group, real or empty, so counts stay constant)
+#pragma unroll
+  for (int j = 0; j < kRing; ++j) {
+    if (j < steps_w) issue(j, wp + j * kStepK, wp2 + j * kStepK);
+    cp_async_commit();
+  }
 
-  float tot[NT][4], acc[NT][4];
+  const uint8_t* xp[NT];  // activations of token g (and g+8), 16 consecutive k per step starting at tig*16
+#pragma unroll
+  for (int t = 0; t < NT; ++t)
+    xp[t] = reinterpret_cast<const uint8_t*>(reinterpret_cast<const T*>(p.act) + int64_t(min(g + 8 * t, p.M - 1)) * p.lda + k_begin + tig * 16);
+  // scale pairs: for int4 the two channels are adjacent (one aligned 32-bit load)
+  const int sa_i = (BITS == 4) ? min(ch_a, p.N - 2) : min(ch_a, p.N - 1);
+  const int sb_i = (BITS == 4) ? sa_i + 1 : min(ch_b, p.N - 1);
+  const int64_t group_pitch = int64_t(p.N) * int64_t(sizeof(T));
+  const uint8_t* sp = reinterpret_cast<const uint8_t*>(reinterpret_cast<const T*>(p.scale) + int64_t(warp) * (steps_w / SPU) * p.N);
+  const uint8_t* zpp = p.zp ? reinterpret_cast<const uint8_t*>(p.zp) + (sp - reinterpret_cast<const uint8_t*>(p.scale)) : nullptr;
+
+  // constant part of the int4 fragment encoding (none for int8, which is expanded exactly)
+  constexpr float kInvAlpha = (BITS == 4) ? Int4Frag<T>::kInvAlpha : 1.f;
+  constexpr float kOffset = (BITS == 4) ? Int4Frag<T>::kOffset : 0.f;
+  constexpr bool kOnes = (BITS == 4);        // always track sum_k x
+  const bool ones = kOnes || p.zp != nullptr;  // int8: only when zero-points are given
+  const uint32_t one2[4] = {Ones<T>::v, Ones<T>::v, Ones<T>::v, Ones<T>::v};
+
+  float tot[NT][4], acc[NT][4], xsum[NT][4];
 #pragma unroll
   for (int t = 0; t < NT; ++t)
 #pragma unroll
-    for (int i = 0; i < 4; ++i) tot[t][i] = acc[t][i] = 0.f;
+    for (int i = 0; i < 4; ++i) tot[t][i] = acc[t][i] = xsum[t][i] = 0.f;
 
-  const bool tok_ok[2] = {g < p.M, g + 8 < p.M};
-  const int total_steps = (u1 - u0) * steps_per_unit;
-  int k = u0 * unit;
-  int step_in_unit = 0;
-  int grp = u0;
+  auto load_pair = [&](const uint8_t* base) -> uint32_t {
+    const T* s = reinterpret_cast<const T*>(base);
+    if (BITS == 4) return __ldg(reinterpret_cast<const uint32_t*>(s + sa_i));
+    return uint32_t(__ldg(reinterpret_cast<const uint16_t*>(s + sa_i))) |
+           (uint32_t(__ldg(reinterpret_cast<const uint16_t*>(s + sb_i))) << 16);
+  };
+  // per-channel zero-points are constant along K; group-wise ones are read at each flush
+  float za = kOffset / kInvAlpha, zb = kOffset / kInvAlpha;
+  if (PERCH && p.zp) {
+    za += load_as_f32(p.zp, p.scale_dtype, sa_i) / kInvAlpha;
+    zb += load_as_f32(p.zp, p.scale_dtype, sb_i) / kInvAlpha;
+  }
 
-  // scale / zero-point of the current group for the two channels of this lane
-  auto finish_group = [&](int gi) {
-    float sa = 1.f, sb = 1.f, za = 0.f, zb = 0.f;
-    if (p.group > 0) {
-      const int64_t o = int64_t(gi) * p.N;
-      if (ch_a < p.N) { sa = load_as_f32(p.scale, p.scale_dtype, o + ch_a); if (p.zp) za = load_as_f32(p.zp, p.scale_dtype, o + ch_a); }
-      if (ch_b < p.N) { sb = load_as_f32(p.scale, p.scale_dtype, o + ch_b); if (p.zp) zb = load_as_f32(p.zp, p.scale_dtype, o + ch_b); }
+  // one step: fragments of 64 k; `first` starts a new flush group (accumulators are overwritten)
+  auto compute_step = [&](const uint4& wv, const uint4& w2v, const uint8_t* xstep, bool first) {
+    uint32_t xw[NT][8];
+#pragma unroll
+    for (int t = 0; t < NT; ++t) {
+      const uint4* x4 = reinterpret_cast<const uint4*>(xstep + (xp[t] - xp[0]));
+      const uint4 x0 = __ldg(x4), x1 = __ldg(x4 + 1);
+      xw[t][0] = x0.x; xw[t][1] = x0.y; xw[t][2] = x0.z; xw[t][3] = x0.w;
+      xw[t][4] = x1.x; xw[t][5] = x1.y; xw[t][6] = x1.z; xw[t][7] = x1.w;
+    }
+    const uint32_t ww[4] = {wv.x, wv.y, wv.z, wv.w};
+    const uint32_t ww2[4] = {w2v.x, w2v.y, w2v.z, w2v.w};
+#pragma unroll
+    for (int q = 0; q < 4; ++q) {
+      uint32_t a[4];
+      if (BITS == 4) {
+        Int4Frag<T>::make(ww[q], a);
+      } else {
+        dequant_int8<T>(ww[q], a[0], a[2]);
+        dequant_int8<T>(ww2[q], a[1], a[3]);
+      }
+#pragma unroll
+      for (int t = 0; t < NT; ++t) {
+        if (first && q == 0) {
+          Mma<T>::run0(acc[t], a, xw[t][0], xw[t][1]);
+          if (ones) Mma<T>::run0(xsum[t], one2, xw[t][0], xw[t][1]);
+        } else {
+          Mma<T>::run(acc[t], a, xw[t][2 * q], xw[t][2 * q + 1]);
+          if (ones) Mma<T>::run(xsum[t], one2, xw[t][2 * q], xw[t][2 * q + 1]);
+        }
+      }
+    }
+  };
+  auto flush = [&](uint32_t sc, const uint8_t* zp_group) {
+    float sa = kInvAlpha, sb = kInvAlpha;
+    if (!PERCH) { sa *= lo16_f32<T>(sc); sb *= hi16_f32<T>(sc); }
+    if (ones) {
+      float fa = za, fb = zb;
+      if (!PERCH && p.zp) {
+        fa += load_as_f32(zp_group, p.scale_dtype, sa_i) / kInvAlpha;
+        fb += load_as_f32(zp_group, p.scale_dtype, sb_i) / kInvAlpha;
+      }
+#pragma unroll
+      for (int t = 0; t < NT; ++t) {
+        acc[t][0] = fmaf(-fa, xsum[t][0], acc[t][0]); acc[t][1] = fmaf(-fa, xsum[t][1], acc[t][1]);
+        acc[t][2] = fmaf(-fb, xsum[t][0], acc[t][2]); acc[t][3] = fmaf(-fb, xsum[t][1], acc[t][3]);
+      }
     }
 #pragma unroll
     for (int t = 0; t < NT; ++t) {
-      float x0 = 0.f, x1 = 0.f;
-      if (p.group > 0 && p.zp) {
-        const int m0 = t * 8 + 2 * tig;
-        if (m0 < p.M) x0 = p.xsum[int64_t(m0) * p.G + gi];
-        if (m0 + 1 < p.M) x1 = p.xsum[int64_t(m0 + 1) * p.G + gi];
-      }
-      tot[t][0] += sa * (acc[t][0] - za * x0);
-      tot[t][1] += sa * (acc[t][1] - za * x1);
-      tot[t][2] += sb * (acc[t][2] - zb * x0);
-      tot[t][3] += sb * (acc[t][3] - zb * x1);
-#pragma unroll
-      for (int i = 0; i < 4; ++i) acc[t][i] = 0.f;
+      tot[t][0] = fmaf(sa, acc[t][0], tot[t][0]);
+      tot[t][1] = fmaf(sa, acc[t][1], tot[t][1]);
+      tot[t][2] = fmaf(sb, acc[t][2], tot[t][2]);
+      tot[t][3] = fmaf(sb, acc[t][3], tot[t][3]);
     }
   };
 
-  for (int s0 = 0; s0 < total_steps; s0 += kBatch) {
-    const int nb = min(kBatch, total_steps - s0);
-    uint4 wq[kBatch], wq2[kBatch];
+  // main loop: kRing steps per iteration, every shared / global offset an immediate
+  const int full = steps_w / kRing * kRing;
+  const uint8_t* xq = xp[0];
+  for (int s0 = 0; s0 < full; s0 += kRing) {
+    uint32_t sc[kRing / SPU];
+    if (!PERCH) {
 #pragma unroll
-    for (int i = 0; i < kBatch; ++i)
-      if (i < nb) {
-        wq[i] = __ldcs(reinterpret_cast<const uint4*>(wa + k + i * kStepK));
-        if (BITS == 8) wq2[i] = __ldcs(reinterpret_cast<const uint4*>(wb + k + i * kStepK));
-      }
+      for (int i = 0; i < kRing / SPU; ++i) sc[i] = load_pair(sp + i * group_pitch);
+    }
+    const bool refill = s0 + 2 * kRing <= steps_w;  // the next-but-one block of steps is complete
 #pragma unroll
-    for (int i = 0; i < kBatch; ++i)
-      if (i < nb) {
-        // activations of token g (and g+8): 16 consecutive k starting at k + tig*16
-        uint4 xv[NT][2];
-#pragma unroll
-        for (int t = 0; t < NT; ++t) {
-          if (tok_ok[t]) {
-            const uint4* xp = reinterpret_cast<const uint4*>(act + int64_t(g + 8 * t) * p.lda + k + i * kStepK + tig * 16);
-            xv[t][0] = __ldg(xp);
-            xv[t][1] = __ldg(xp + 1);
-          } else {
-            xv[t][0] = xv[t][1] = make_uint4(0, 0, 0, 0);
-          }
-        }
-        const uint32_t ww[4] = {wq[i].x, wq[i].y, wq[i].z, wq[i].w};
-        const uint32_t ww2[4] = {wq2[i].x, wq2[i].y, wq2[i].z, wq2[i].w};
-#pragma unroll
-        for (int j = 0; j < 4; ++j) {
-          uint32_t a[4];
-          if (BITS == 4) {
-            dequant_int4<T>(ww[j], a);
-          } else {
-            dequant_int8<T>(ww[j], a[0], a[2]);
-            dequant_int8<T>(ww2[j], a[1], a[3]);
-          }
-#pragma unroll
-          for (int t = 0; t < NT; ++t) {
-            const uint32_t xw[8] = {xv[t][0].x, xv[t][0].y, xv[t][0].z, xv[t][0].w,
-                                    xv[t][1].x, xv[t][1].y, xv[t][1].z, xv[t][1].w};
-            Mma<T>::run(acc[t], a, xw[2 * j], xw[2 * j + 1]);
-          }
-        }
-        if (++step_in_unit == steps_per_unit) {
-          step_in_unit = 0;
-          if (p.group > 0) finish_group(grp);
-          ++grp;
-        }
-      }
-    k += nb * kStepK;
+    for (int j = 0; j < kRing; ++j) {
+      cp_async_wait<kRing - 1>();  // step s0+j has landed (at most kRing-1 newer groups pending)
+      const uint4 wv = lds128(fifo + j * S::kSlotBytes);
+      uint4 w2v = wv;
+      if (BITS == 8) w2v = lds128(fifo + j * S::kSlotBytes + 16);
+      compute_step(wv, w2v, xq + j * (kStepK * int(sizeof(T))), j % SPU == 0);
+      if (refill) issue(j, wp + (kRing + j) * kStepK, wp2 + (kRing + j) * kStepK);
+      else if (s0 + kRing + j < steps_w) issue(j, wp + (kRing + j) * kStepK, wp2 + (kRing + j) * kStepK);
+      cp_async_commit();
+      if ((j + 1) % SPU == 0) flush(PERCH ? 0u : sc[j / SPU], zpp ? zpp + (j / SPU) * group_pitch : nullptr);
+    }
+    wp += kRing * kStepK;
+    wp2 += kRing * kStepK;
+    xq += kRing * kStepK * int(sizeof(T));
+    sp += (kRing / SPU) * group_pitch;
+    if (zpp) zpp += (kRing / SPU) * group_pitch;
   }
-  if (p.group == 0) {
-    // per-channel: the whole K range is one group; scale and zero-point are applied after the reduction
-#pragma unroll
-    for (int t = 0; t < NT; ++t)
-#pragma unroll
-      for (int i = 0; i < 4; ++i) tot[t][i] = acc[t][i];
+  // remainder: fewer than kRing steps, already requested by the block before (or by the prologue)
+  for (int s = full; s < steps_w; ++s) {
+    const int j = s - full;
+    cp_async_wait<0>();
+    const uint4 wv = lds128(fifo + j * S::kSlotBytes);
+    uint4 w2v = wv;
+    if (BITS == 8) w2v = lds128(fifo + j * S::kSlotBytes + 16);
+    compute_step(wv, w2v, xq + j * (kStepK * int(sizeof(T))), j % SPU == 0);
+    if ((j + 1) % SPU == 0) {
+      const int gi = j / SPU;
+      flush(PERCH ? 0u : load_pair(sp + gi * group_pitch), zpp ? zpp + gi * group_pitch : nullptr);
+    }
   }
+  cp_async_wait<0>();
 
 #pragma unroll
   for (int t = 0; t < NT; ++t)
@@ -254,32 +362,12 @@ gemv_mma_kernel(const WoParams p) {
         const int ch = (i < 2) ? ch_a : ch_b;
         const int m = t * 8 + 2 * tig + (i & 1);
         if (ch < p.N && m < p.M) {
-          if (p.group == 0) {
-            const float s = load_as_f32(p.scale, p.scale_dtype, ch);
-            if (p.zp) v -= load_as_f32(p.zp, p.scale_dtype, ch) * p.xsum[m];
-            v *= s;
-          }
+          if (PERCH) v *= load_as_f32(p.scale, p.scale_dtype, ch);
           if (p.bias) v += load_as_f32(p.bias, p.bias_dtype, ch);
           out[int64_t(m) * p.ldo + ch] = from_f32<T>(v);
         }
       }
   }
-}
-
-// sum of x over each scale group: xsum[m, gi] = sum_{k in group gi} x[m, k]   (one warp per (m, gi))
-template <typename T>
-__global__ void group_sum_kernel(const T* __restrict__ act, int64_t lda, float* __restrict__ xsum, int M, int K, int G) {
-  const int64_t w = (int64_t(blockIdx.x) * blockDim.x + threadIdx.x) >> 5;
-  const int lane = threadIdx.x & 31;
-  if (w >= int64_t(M) * G) return;
-  const int m = int(w / G), gi = int(w % G);
-  const int len = K / G;
-  const T* x = act + int64_t(m) * lda + int64_t(gi) * len;
-  float s = 0.f;
-  for (int i = lane; i < len; i += 32) s += to_f32(x[i]);
-#pragma unroll
-  for (int o = 16; o > 0; o >>= 1) s += __shfl_xor_sync(0xffffffffu, s, o);
-  if (lane == 0) xsum[w] = s;
 }
 
 // Correctness path for everything the fast kernels do not cover (any M, K, group size):
@@ -318,48 +406,72 @@ __global__ void wo_generic_kernel(const WoParams p) {
   reinterpret_cast<T*>(p.out)[int64_t(m) * p.ldo + n] = from_f32<T>(total);
 }
 
-bool gemv_path_ok(const WoParams& p, int bits) {
-  if (p.M > 16) return false;
-  if (p.K % kStepK != 0) return false;
-  if (p.group > 0 && (p.group % kStepK != 0 || p.K % p.group != 0)) return false;
-  if (reinterpret_cast<uintptr_t>(p.qw) % 16 != 0) return false;
-  if (reinterpret_cast<uintptr_t>(p.act) % 16 != 0 || p.lda % 8 != 0) return false;
-  if (bits == 4 && p.N % 2 != 0) return false;
-  return true;
+// Steps (of 64 k) per partial-sum flush of the fast kernel, or -1 when the fast kernel does not apply.
+int gemv_spu(const WoParams& p, int bits, int act_dtype) {
+  if (p.M > 16) return -1;
+  if (p.K % (kStepK * kGemvWarps) != 0) return -1;
+  if (reinterpret_cast<uintptr_t>(p.qw) % 16 != 0) return -1;
+  if (reinterpret_cast<uintptr_t>(p.act) % 16 != 0 || p.lda % 8 != 0) return -1;
+  if (bits == 4 && (p.N % 2 != 0 || p.N < 2)) return -1;
+  const int slice = p.K / kGemvWarps;
+  if (p.group == 0) return (slice % (2 * kStepK) == 0) ? 2 : 1;  // pseudo-groups of 128 or 64
+  if (p.scale_dtype != act_dtype) return -1;  // group scales are read as packed pairs of T
+  if (reinterpret_cast<uintptr_t>(p.scale) % 4 != 0) return -1;
+  if (slice % p.group != 0) return -1;  // a warp's K slice must be whole groups
+  const int spu = p.group / kStepK;
+  if (p.group % kStepK != 0 || (spu != 1 && spu != 2 && spu != 4)) return -1;
+  return spu;
 }
 
 template <typename T, int BITS>
 int launch_wo(WoParams p, void* workspace, size_t workspace_bytes, cudaStream_t st) {
-  if (!gemv_path_ok(p, BITS)) {
+  const int spu = gemv_spu(p, BITS, std::is_same<T, __half>::value ? FNN_F16 : FNN_BF16);
+  if (spu < 0) {
     const int64_t total = int64_t(p.M) * p.N;
     wo_generic_kernel<T, BITS><<<unsigned((total + 255) / 256), 256, 0, st>>>(p);
     return check_cuda(cudaGetLastError(), "weight-only generic launch");
   }
-  if (p.zp) {
-    const size_t need = size_t(p.M) * p.G * sizeof(float);
-    if (!workspace || workspace_bytes < need)
-      return fail(FNN_ERR_WORKSPACE, "gemm_weight_only: zero-points need %zu bytes of workspace, got %zu", need, workspace_bytes);
-    if (reinterpret_cast<uintptr_t>(workspace) % 256 != 0) return fail(FNN_ERR_ALIGNMENT, "gemm_weight_only: workspace must be 256-byte aligned");
-    float* xsum = static_cast<float*>(workspace);
-    const int64_t warps = int64_t(p.M) * p.G;
-    group_sum_kernel<T><<<unsigned((warps * 32 + 255) / 256), 256, 0, st>>>(reinterpret_cast<const T*>(p.act), p.lda, xsum, p.M, p.K, p.G);
-    if (int e = check_cuda(cudaGetLastError(), "group_sum launch")) return e;
-    p.xsum = xsum;
-  }
+  const bool perch = p.group == 0;
+  (void)workspace;
+  (void)workspace_bytes;
+  p.status = device_status_word();
+  const int nt = p.M <= 8 ? 1 : 2;
   const unsigned grid = unsigned((p.N + 15) / 16);
-  if (p.M <= 8) gemv_mma_kernel<T, BITS, 1><<<grid, kGemvThreads, 0, st>>>(p);
-  else gemv_mma_kernel<T, BITS, 2><<<grid, kGemvThreads, 0, st>>>(p);
-  return check_cuda(cudaGetLastError(), "weight-only gemv launch");
+  const size_t smem_bytes = GemvSmem<BITS>::kBytes;
+  cudaError_t err;
+#define FNN_GEMV_CASE(NT, SPU, PC)                                                                          \
+  do {                                                                                                      \
+    static bool configured[64] = {};                                                                        \
+    int dev = 0;                                                                                            \
+    cudaGetDevice(&dev);                                                                                    \
+    err = cudaSuccess;                                                                                      \
+    if (!configured[dev & 63]) {                                                                            \
+      err = cudaFuncSetAttribute(gemv_mma_kernel<T, BITS, NT, SPU, PC>,                                     \
+                                 cudaFuncAttributeMaxDynamicSharedMemorySize, int(smem_bytes));             \
+      configured[dev & 63] = (err == cudaSuccess);                                                          \
+    }                                                                                                       \
+    if (err == cudaSuccess) {                                                                               \
+      gemv_mma_kernel<T, BITS, NT, SPU, PC><<<grid, kGemvThreads, smem_bytes, st>>>(p);                     \
+      err = cudaGetLastError();                                                                             \
+    }                                                                                                       \
+  } while (0)
+#define FNN_GEMV_NT(NT)                                        \
+  if (perch) { if (spu == 1) FNN_GEMV_CASE(NT, 1, true); else FNN_GEMV_CASE(NT, 2, true); } \
+  else if (spu == 1) FNN_GEMV_CASE(NT, 1, false);              \
+  else if (spu == 2) FNN_GEMV_CASE(NT, 2, false);              \
+  else FNN_GEMV_CASE(NT, 4, false)
+  if (nt == 1) { FNN_GEMV_NT(1); } else { FNN_GEMV_NT(2); }
+#undef FNN_GEMV_NT
+#undef FNN_GEMV_CASE
+  return check_cuda(err, "weight-only gemv launch");
 }
 
 }  // namespace
 }  // namespace fnn
 
 extern "C" size_t fnn_gemm_weight_only_workspace_bytes(int64_t M, int64_t N, int64_t K, int weight_bits, int64_t group_size) {
-  (void)N; (void)weight_bits;
-  if (M <= 0 || K <= 0) return 0;
-  const int64_t G = group_size > 0 ? (K + group_size - 1) / group_size : 1;
-  return size_t(M) * size_t(G) * sizeof(float);  // activation sums per group (used with zero-points)
+  (void)M; (void)N; (void)K; (void)weight_bits; (void)group_size;
+  return 0;  // neither the decode kernel nor the generic kernel uses scratch
 }
 
 extern "C" int fnn_gemm_weight_only(const void* act, int act_dtype, int64_t lda, const void* qweight, int weight_bits,
@@ -383,8 +495,8 @@ extern "C" int fnn_gemm_weight_only(const void* act, int act_dtype, int64_t lda,
   if (K == 0) return fail(FNN_ERR_SHAPE, "gemm_weight_only: K must be positive");
   WoParams p{};
   p.act = act; p.qw = static_cast<const uint8_t*>(qweight); p.scale = scale; p.zp = zero_points; p.bias = bias;
-  p.xsum = nullptr; p.out = out; p.lda = lda; p.ldo = ldo; p.scale_dtype = scale_dtype; p.bias_dtype = bias_dtype;
-  p.M = int(M); p.N = int(N); p.K = int(K); p.group = int(group_size); p.G = group_size > 0 ? int(K / group_size) : 1;
+  p.out = out; p.lda = lda; p.ldo = ldo; p.scale_dtype = scale_dtype; p.bias_dtype = bias_dtype;
+  p.M = int(M); p.N = int(N); p.K = int(K); p.group = int(group_size);
   cudaStream_t st = static_cast<cudaStream_t>(stream);
   if (act_dtype == FNN_F16)
     return weight_bits == 4 ? launch_wo<__half, 4>(p, workspace, workspace_bytes, st) : launch_wo<__half, 8>(p, workspace, workspace_bytes, st);
