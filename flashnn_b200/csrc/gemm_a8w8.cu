@@ -68,6 +68,47 @@ __device__ __forceinline__ void report(int* status, volatile int* abort_flag, in
   if (status) atomicCAS(status, 0, code);
 }
 
+// Epilogue of 32 accumulator columns of one output row: optional raw int32 copy, then
+// out = fl32(float(acc) * s) with s = row scale * column scale (rounded to the scales' dtype when
+// both scales share a 16-bit dtype), rounded once to OutT.
+template <typename OutT>
+__device__ __forceinline__ void store_chunk(const uint32_t (&r)[32], int row, int col0, float rs, const float* cs,
+                                            bool same16, const A8W8Params& p, bool vec_ok, bool acc_vec_ok) {
+  if (row >= p.M || col0 >= p.N) return;
+  const bool full = col0 + 32 <= p.N;
+  if (p.acc_out) {
+    int32_t* arow = p.acc_out + int64_t(row) * p.ldacc + col0;
+    if (full && acc_vec_ok) {
+#pragma unroll
+      for (int j = 0; j < 32; j += 4)
+        *reinterpret_cast<uint4*>(arow + j) = make_uint4(r[j], r[j + 1], r[j + 2], r[j + 3]);
+    } else {
+#pragma unroll
+      for (int j = 0; j < 32; ++j)
+        if (col0 + j < p.N) arow[j] = int32_t(r[j]);
+    }
+  }
+  float v[32];
+#pragma unroll
+  for (int j = 0; j < 32; ++j) {
+    float s = __fmul_rn(rs, cs[j]);
+    if (same16) s = round_through(s, p.row_dtype);
+    v[j] = __fmul_rn(float(int32_t(r[j])), s);
+  }
+  OutT* orow = reinterpret_cast<OutT*>(p.out) + int64_t(row) * p.ldo + col0;
+  if (full && vec_ok) {
+#pragma unroll
+    for (int j = 0; j < 32; j += 8)
+      *reinterpret_cast<uint4*>(orow + j) =
+          make_uint4(pack2<OutT>(v[j], v[j + 1]), pack2<OutT>(v[j + 2], v[j + 3]),
+                     pack2<OutT>(v[j + 4], v[j + 5]), pack2<OutT>(v[j + 6], v[j + 7]));
+  } else {
+#pragma unroll
+    for (int j = 0; j < 32; ++j)
+      if (col0 + j < p.N) orow[j] = from_f32<OutT>(v[j]);
+  }
+}
+
 template <typename OutT, int BN, int STAGES>
 __global__ void __launch_bounds__(kThreads, 1)
 a8w8_umma_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ CUtensorMap tmap_b,
@@ -208,8 +249,7 @@ a8w8_umma_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_consta
     const int quarter = warp & 3;
     float* cs = col_scale_smem + quarter * BN;  // this warp's private copy
     const bool same16 = (p.row_dtype == p.col_dtype) && (p.row_dtype != FNN_F32);
-    OutT* out = reinterpret_cast<OutT*>(p.out);
-    const bool vec_ok = (p.ldo % 8 == 0) && (reinterpret_cast<uintptr_t>(out) % 16 == 0);
+    const bool vec_ok = (p.ldo % 8 == 0) && (reinterpret_cast<uintptr_t>(p.out) % 16 == 0);
     const bool acc_vec_ok = p.acc_out && (p.ldacc % 4 == 0) && (reinterpret_cast<uintptr_t>(p.acc_out) % 16 == 0);
     int local = 0;
     bool ok = true;
@@ -239,41 +279,7 @@ a8w8_umma_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_consta
         uint32_t r[32];
         tmem_ld_32x32(taddr + c * 32, r);
         tc_wait_ld();
-        const int col0 = n0 + c * 32;
-        if (row < p.M && col0 < p.N) {
-          const bool full = col0 + 32 <= p.N;
-          if (p.acc_out) {
-            int32_t* arow = p.acc_out + int64_t(row) * p.ldacc + col0;
-            if (full && acc_vec_ok) {
-#pragma unroll
-              for (int j = 0; j < 32; j += 4)
-                *reinterpret_cast<uint4*>(arow + j) = make_uint4(r[j], r[j + 1], r[j + 2], r[j + 3]);
-            } else {
-#pragma unroll
-              for (int j = 0; j < 32; ++j)
-                if (col0 + j < p.N) arow[j] = int32_t(r[j]);
-            }
-          }
-          float v[32];
-#pragma unroll
-          for (int j = 0; j < 32; ++j) {
-            float s = __fmul_rn(rs, cs[c * 32 + j]);
-            if (same16) s = round_through(s, p.row_dtype);
-            v[j] = __fmul_rn(float(int32_t(r[j])), s);
-          }
-          OutT* orow = out + int64_t(row) * p.ldo + col0;
-          if (full && vec_ok) {
-#pragma unroll
-            for (int j = 0; j < 32; j += 8)
-              *reinterpret_cast<uint4*>(orow + j) =
-                  make_uint4(pack2<OutT>(v[j], v[j + 1]), pack2<OutT>(v[j + 2], v[j + 3]),
-                             pack2<OutT>(v[j + 4], v[j + 5]), pack2<OutT>(v[j + 6], v[j + 7]));
-          } else {
-#pragma unroll
-            for (int j = 0; j < 32; ++j)
-              if (col0 + j < p.N) orow[j] = from_f32<OutT>(v[j]);
-          }
-        }
+        store_chunk<OutT>(r, row, n0 + c * 32, rs, cs + c * 32, same16, p, vec_ok, acc_vec_ok);
       }
       tc_fence_before();
       __syncwarp();
@@ -287,6 +293,225 @@ a8w8_umma_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_consta
   if (warp == 1) {
     tc_fence_after();
     tmem_dealloc(tmem_base, kTmemCols);
+  }
+}
+
+// ---------------------------------------------------------------------------
+// CTA-pair variant (cluster of 2, tcgen05 cta_group::2): one 256 x 256 output tile per pair.
+// CTA r of the pair loads rows [128 r, 128 r + 128) of the A tile and of the B tile (no multicast:
+// every CTA fetches exactly the bytes that end up in its own shared memory), so each stage is
+// 32 KB per CTA for the same MMA work that takes 48 KB in the single-CTA kernel: a third less
+// L2->SM traffic and a deeper ring in the same shared memory.  The leader CTA (rank 0) issues
+// the MMAs for both; each CTA's TMEM holds its own 128 accumulator rows and each CTA runs its
+// own epilogue.  Barriers:
+//   full[s]        in the leader; the leader's producer expects the bytes of both CTAs, both CTAs'
+//                  TMA loads complete on it
+//   empty[s]       in each CTA; signalled by the leader's tcgen05.commit with a two-CTA mask
+//   tmem_full[b]   in each CTA; signalled the same way when a tile's accumulator is complete
+//   tmem_empty[b]  in the leader; 8 arrivals (4 epilogue warps of each CTA, the peer's remotely)
+// ---------------------------------------------------------------------------
+template <int STAGES> struct PairSmem {
+  static constexpr int kBN = 256;
+  static constexpr int kABytes = kBM * kBK;             // this CTA's 128 rows of A
+  static constexpr int kBBytes = (kBN / 2) * kBK;       // this CTA's 128 rows of B
+  static constexpr int kStageBytes = kABytes + kBBytes;
+  static constexpr int kColScaleOff = STAGES * kStageBytes;  // [4][kBN] float
+  static constexpr int kBarOff = kColScaleOff + 4 * kBN * 4;
+  static constexpr int kNumBars = 2 * STAGES + 4 + 1;
+  static constexpr int kTmemSlotOff = kBarOff + kNumBars * 8;
+  static constexpr int kAbortOff = kTmemSlotOff + 8;
+  static constexpr int kTotal = kAbortOff + 8;
+  static constexpr int kDynamicBytes = kTotal + 1024;
+};
+
+template <typename OutT, int STAGES>
+__global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(kThreads, 1)
+a8w8_umma_pair_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ CUtensorMap tmap_b,
+                      const A8W8Params p) {
+  using L = PairSmem<STAGES>;
+  constexpr int BN = L::kBN;
+  extern __shared__ uint8_t smem_raw[];
+  uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
+  float* col_scale_smem = reinterpret_cast<float*>(smem + L::kColScaleOff);
+  uint64_t* bars = reinterpret_cast<uint64_t*>(smem + L::kBarOff);
+  uint64_t* full_bar = bars;
+  uint64_t* empty_bar = bars + STAGES;
+  uint64_t* tmem_full_bar = bars + 2 * STAGES;
+  uint64_t* tmem_empty_bar = bars + 2 * STAGES + 2;
+  uint64_t* drain_bar = bars + 2 * STAGES + 4;
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(smem + L::kTmemSlotOff);
+  volatile int* abort_flag = reinterpret_cast<volatile int*>(smem + L::kAbortOff);
+
+  const int warp = threadIdx.x >> 5;
+  const int lane = threadIdx.x & 31;
+  const uint32_t rank = cluster_ctarank();  // 0 = leader
+  const int pair_id = blockIdx.x >> 1;
+  const int num_pairs = gridDim.x >> 1;
+  const int num_tiles = p.tiles_m * p.tiles_n;  // 256 x 256 tiles
+  constexpr uint32_t kTmemCols = 2 * BN;
+
+  if (threadIdx.x == 0) {
+    *abort_flag = 0;
+    for (int s = 0; s < STAGES; ++s) {
+      mbar_init(&full_bar[s], 1);
+      mbar_init(&empty_bar[s], 1);
+    }
+    for (int b = 0; b < 2; ++b) {
+      mbar_init(&tmem_full_bar[b], 1);
+      mbar_init(&tmem_empty_bar[b], 8);
+    }
+    mbar_init(drain_bar, 1);
+    mbar_fence_init();
+    tma_prefetch_desc(&tmap_a);
+    tma_prefetch_desc(&tmap_b);
+  }
+  if (warp == 1) {
+    tmem_alloc_pair(tmem_slot, kTmemCols);
+    tmem_relinquish_pair();
+  }
+  tc_fence_before();
+  __syncthreads();
+  cluster_sync_all();  // both CTAs' barriers exist before anything crosses the pair
+  tc_fence_after();
+  const uint32_t tmem_base = *tmem_slot;
+
+  if (warp == 0) {
+    // ------------------------------ TMA producer (both CTAs) ------------------------------
+    const bool leader_lane = elect_one();
+    int stage = 0;
+    uint32_t phase = 0;
+    long long issued = 0;
+    bool ok = true;
+    for (int t = pair_id; t < num_tiles && ok; t += num_pairs) {
+      int mb, nb;
+      tile_coords(t, p.tiles_m, p.tiles_n, mb, nb);
+      for (int kb = 0; kb < p.k_blocks; ++kb) {
+        ok = mbar_wait_bounded(&empty_bar[stage], phase ^ 1, abort_flag);
+        ok = __all_sync(0xffffffffu, ok);
+        if (!ok) {
+          if (leader_lane) report(p.status, abort_flag, DEV_TIMEOUT_PRODUCER);
+          break;
+        }
+        if (leader_lane) {
+          uint8_t* sa = smem + stage * L::kStageBytes;
+          const uint32_t full_in_leader = map_to_cta(smem_u32(&full_bar[stage]), 0);
+          if (rank == 0) mbar_expect_tx(&full_bar[stage], 2 * L::kStageBytes);
+          tma_load_2d_pair(sa, &tmap_a, full_in_leader, kb * kBK, mb * 256 + int(rank) * 128);
+          tma_load_2d_pair(sa + L::kABytes, &tmap_b, full_in_leader, kb * kBK, nb * BN + int(rank) * 128);
+          ++issued;
+        }
+        __syncwarp();
+        if (++stage == STAGES) { stage = 0; phase ^= 1; }
+      }
+    }
+    // Wait (bounded, cut short by an abort) until the MMAs have consumed the last stages issued:
+    // nothing is still being written into this CTA's shared memory when it exits.
+    if (leader_lane) {
+      const long long first = issued > STAGES ? issued - STAGES : 0;
+      for (long long i = first; i < issued; ++i)
+        if (!mbar_wait_bounded(&empty_bar[i % STAGES], uint32_t((i / STAGES) & 1), abort_flag)) break;
+    }
+  } else if (warp == 1) {
+    // ------------------------------- MMA issuer (leader only) -------------------------------
+    const bool leader_lane = elect_one();
+    if (rank == 0) {
+      constexpr uint32_t idesc = umma_idesc(/*s32*/ 2, /*signed 8-bit*/ 1, 256, BN);
+      int stage = 0;
+      uint32_t phase = 0;
+      int local = 0;
+      bool ok = true;
+      bool issued_any = false;
+      for (int t = pair_id; t < num_tiles && ok; t += num_pairs, ++local) {
+        const int buf = local & 1;
+        const uint32_t acc_phase = (local >> 1) & 1;
+        ok = mbar_wait_bounded(&tmem_empty_bar[buf], acc_phase ^ 1, abort_flag);
+        ok = __all_sync(0xffffffffu, ok);
+        if (!ok) {
+          if (leader_lane) report(p.status, abort_flag, DEV_TIMEOUT_MMA);
+          break;
+        }
+        tc_fence_after();
+        const uint32_t tmem_d = tmem_base + buf * BN;
+        for (int kb = 0; kb < p.k_blocks; ++kb) {
+          ok = mbar_wait_bounded(&full_bar[stage], phase, abort_flag);
+          ok = __all_sync(0xffffffffu, ok);
+          if (!ok) {
+            if (leader_lane) report(p.status, abort_flag, DEV_TIMEOUT_MMA);
+            break;
+          }
+          tc_fence_after();
+          if (leader_lane) {
+            const uint32_t sa = smem_u32(smem + stage * L::kStageBytes);
+            const uint32_t sb = sa + L::kABytes;
+#pragma unroll
+            for (int k = 0; k < kBK / kUmmaK; ++k)
+              umma_i8_pair(tmem_d, umma_desc_k_sw128(sa + k * kUmmaK), umma_desc_k_sw128(sb + k * kUmmaK), idesc,
+                           (kb | k) != 0 ? 1u : 0u);
+            tc_commit_pair(&empty_bar[stage], 0x3);  // frees this stage in both CTAs
+            issued_any = true;
+          }
+          __syncwarp();
+          if (++stage == STAGES) { stage = 0; phase ^= 1; }
+        }
+        if (ok && leader_lane) tc_commit_pair(&tmem_full_bar[buf], 0x3);  // accumulator complete, both CTAs
+        __syncwarp();
+      }
+      // Wait (bounded) for every MMA issued before TMEM is freed, even after an abort.
+      if (leader_lane && issued_any) {
+        int none = 0;
+        tc_commit_pair(drain_bar, 0x1);
+        if (!mbar_wait_bounded(drain_bar, 0, &none)) report(p.status, abort_flag, DEV_TIMEOUT_DRAIN);
+      }
+    }
+  } else {
+    // -------------------------------- epilogue (both CTAs) --------------------------------
+    const int quarter = warp & 3;
+    float* cs = col_scale_smem + quarter * BN;  // this warp's private copy
+    const bool same16 = (p.row_dtype == p.col_dtype) && (p.row_dtype != FNN_F32);
+    const bool vec_ok = (p.ldo % 8 == 0) && (reinterpret_cast<uintptr_t>(p.out) % 16 == 0);
+    const bool acc_vec_ok = p.acc_out && (p.ldacc % 4 == 0) && (reinterpret_cast<uintptr_t>(p.acc_out) % 16 == 0);
+    int local = 0;
+    bool ok = true;
+    for (int t = pair_id; t < num_tiles && ok; t += num_pairs, ++local) {
+      int mb, nb;
+      tile_coords(t, p.tiles_m, p.tiles_n, mb, nb);
+      const int buf = local & 1;
+      const uint32_t acc_phase = (local >> 1) & 1;
+      const int row = mb * 256 + int(rank) * 128 + quarter * 32 + lane;
+      const int n0 = nb * BN;
+      for (int j = lane; j < BN; j += 32)
+        cs[j] = (n0 + j < p.N) ? load_as_f32(p.alpha_col, p.col_dtype, n0 + j) : 0.f;
+      const float rs = (row < p.M) ? load_as_f32(p.alpha_row, p.row_dtype, row) : 0.f;
+      __syncwarp();
+
+      ok = mbar_wait_bounded(&tmem_full_bar[buf], acc_phase, abort_flag);
+      ok = __all_sync(0xffffffffu, ok);
+      if (!ok) {
+        if (lane == 0) report(p.status, abort_flag, DEV_TIMEOUT_EPILOGUE);
+        break;
+      }
+      tc_fence_after();
+      const uint32_t taddr = tmem_base + (uint32_t(quarter * 32) << 16) + buf * BN;
+#pragma unroll 1
+      for (int c = 0; c < BN / 32; ++c) {
+        uint32_t r[32];
+        tmem_ld_32x32(taddr + c * 32, r);
+        tc_wait_ld();
+        store_chunk<OutT>(r, row, n0 + c * 32, rs, cs + c * 32, same16, p, vec_ok, acc_vec_ok);
+      }
+      tc_fence_before();
+      __syncwarp();
+      if (lane == 0) mbar_arrive_cluster(map_to_cta(smem_u32(&tmem_empty_bar[buf]), 0));
+    }
+  }
+
+  // -------------------------------- teardown --------------------------------
+  tc_fence_before();
+  __syncthreads();
+  cluster_sync_all();  // neither CTA leaves while the other may still touch its memory or barriers
+  if (warp == 1) {
+    tc_fence_after();
+    tmem_dealloc_pair(tmem_base, kTmemCols);
   }
 }
 
@@ -370,6 +595,31 @@ int launch_umma(const int8_t* a, int64_t lda, const int8_t* b, int64_t ldb, A8W8
   return check_cuda(cudaGetLastError(), "a8w8 tcgen05 launch");
 }
 
+template <typename OutT, int STAGES>
+int launch_pair(const int8_t* a, int64_t lda, const int8_t* b, int64_t ldb, A8W8Params p, cudaStream_t st) {
+  using L = PairSmem<STAGES>;
+  static_assert(L::kDynamicBytes <= 227 * 1024, "shared memory budget");
+  auto kern = a8w8_umma_pair_kernel<OutT, STAGES>;
+  static std::once_flag once[64];
+  int dev = 0;
+  cudaGetDevice(&dev);
+  cudaError_t attr_err = cudaSuccess;
+  std::call_once(once[dev & 63], [&] {
+    attr_err = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, L::kDynamicBytes);
+  });
+  if (attr_err != cudaSuccess) return check_cuda(attr_err, "cudaFuncSetAttribute(a8w8 pair)");
+  CUtensorMap ta, tb;
+  if (int e = make_tmap_i8(&ta, a, p.M, p.K, lda, kBM)) return e;
+  if (int e = make_tmap_i8(&tb, b, p.N, p.K, ldb, L::kBN / 2)) return e;
+  p.tiles_m = (p.M + 255) / 256;
+  p.tiles_n = (p.N + L::kBN - 1) / L::kBN;
+  p.k_blocks = (p.K + kBK - 1) / kBK;
+  const int tiles = p.tiles_m * p.tiles_n;
+  const int pairs = tiles < sm_count() / 2 ? tiles : sm_count() / 2;
+  kern<<<2 * pairs, kThreads, L::kDynamicBytes, st>>>(ta, tb, p);
+  return check_cuda(cudaGetLastError(), "a8w8 tcgen05 (CTA pair) launch");
+}
+
 template <typename OutT>
 int dispatch(const int8_t* a, int64_t lda, const int8_t* b, int64_t ldb, const A8W8Params& p, cudaStream_t st) {
   const bool tma_ok = p.K > 0 && (reinterpret_cast<uintptr_t>(a) % 16 == 0) && (reinterpret_cast<uintptr_t>(b) % 16 == 0) &&
@@ -379,8 +629,10 @@ int dispatch(const int8_t* a, int64_t lda, const int8_t* b, int64_t ldb, const A
     a8w8_generic_kernel<OutT><<<unsigned((total + 255) / 256), 256, 0, st>>>(a, lda, b, ldb, p);
     return check_cuda(cudaGetLastError(), "a8w8 generic launch");
   }
-  // Tile width: the widest tile that still gives every SM work.
+  // Large problems: one 256 x 256 tile per CTA pair.  Otherwise the widest single-CTA tile that
+  // still gives every SM work.
   const int sms = sm_count();
+  if (p.M > kBM && ((p.M + 255) / 256) * ((p.N + 255) / 256) >= sms / 2) return launch_pair<OutT, 6>(a, lda, b, ldb, p, st);
   const int tiles_m = (p.M + kBM - 1) / kBM;
   if (tiles_m * ((p.N + 255) / 256) >= sms) return launch_umma<OutT, 256, 4>(a, lda, b, ldb, p, st);
   if (tiles_m * ((p.N + 127) / 128) >= sms) return launch_umma<OutT, 128, 6>(a, lda, b, ldb, p, st);

@@ -46,11 +46,13 @@ def make(m, n, k, seed, scale_ty=torch.float32, lo=-127):
     return a, b, row, col
 
 
-# ragged M / N / K (tile multiples are 128 / 64..256 / 128), tiny sizes, K with a 16-byte but not
+# ragged M / N / K (tile multiples are 128 or 256 / 64..256 / 128; the last three shapes are large enough for
+# the CTA-pair kernel), tiny sizes, K with a 16-byte but not
 # 128-byte pitch (TMA zero fill), K not a multiple of 16 (generic kernel), -128 operands
 @pytest.mark.parametrize("m,n,k", [(1, 64, 128), (3, 200, 336), (17, 520, 1040), (129, 130, 144),
                                    (128, 128, 128), (256, 512, 4096), (300, 1000, 8896), (16, 4096, 4096),
-                                   (5, 48, 100), (33, 17, 7), (64, 8192, 1024), (1000, 264, 7392)])
+                                   (5, 48, 100), (33, 17, 7), (64, 8192, 1024), (1000, 264, 7392),
+                                   (2500, 2100, 1040), (2049, 2560, 144), (1290, 4200, 2064)])
 @pytest.mark.parametrize("out_ty", [torch.float16, torch.bfloat16])
 def test_shapes_exact(m, n, k, out_ty):
     a, b, row, col = make(m, n, k, seed=m + n + k, lo=-128)
