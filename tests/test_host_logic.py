@@ -1,0 +1,60 @@
+"""Host-side behaviour of the operator classes that needs no GPU: the reference's names are importable, the backend
+switches exist, and nothing falls back to a CPU computation."""
+import pytest
+import torch
+
+
+def test_reference_names_are_importable():
+    import flashnn
+    from flashnn import DynamicQuantize, GemmA8W8, GemmWeightOnly, set_use_triton  # noqa: F401
+    import flashnn_b200
+    assert flashnn.GemmA8W8 is flashnn_b200.GemmA8W8
+    assert isinstance(flashnn.DynamicQuantize(), torch.nn.Module)
+    assert flashnn.GemmA8W8().out_ty == torch.float16 and flashnn.GemmWeightOnly().out_ty == torch.float16
+    assert flashnn.GemmA8W8(torch.bfloat16).out_ty == torch.bfloat16
+
+
+def test_cpu_tensors_are_rejected_not_computed():
+    import flashnn_b200
+    x = torch.randn(4, 64).half()
+    with pytest.raises(RuntimeError, match="no CPU path"):
+        flashnn_b200.DynamicQuantize()(x)
+    a = torch.zeros(4, 64, dtype=torch.int8)
+    with pytest.raises(RuntimeError, match="no CPU path"):
+        flashnn_b200.GemmA8W8()(a, a, torch.ones(4), torch.ones(4))
+    with pytest.raises(RuntimeError, match="no CPU path"):
+        flashnn_b200.GemmWeightOnly()(x, a, torch.ones(4).half())
+
+
+def test_selecting_the_torch_backend_raises():
+    import flashnn_b200
+    from flashnn_b200 import kernel_backend as kb
+    assert kb.get_use_triton() is True
+    flashnn_b200.set_use_triton(False)
+    try:
+        with pytest.raises(ValueError, match="No valid backend found"):
+            flashnn_b200.DynamicQuantize()(torch.randn(2, 8).half())
+    finally:
+        flashnn_b200.set_use_triton(True)
+    flashnn_b200.set_autotune_triton_kernels(True)  # accepted, has no effect on these operators
+    assert kb.get_autotune_triton_kernels() is True
+    flashnn_b200.set_autotune_triton_kernels(False)
+
+
+def test_package_does_not_import_the_oracle():
+    import os
+    root = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+    for dirpath, _, files in os.walk(os.path.join(root, "flashnn_b200")):
+        for f in files:
+            if f.endswith((".py", ".cu", ".cuh")):
+                text = open(os.path.join(dirpath, f)).read()
+                assert "oracle" not in text.replace("the oracle", ""), f"{f} refers to the oracle package"
+
+
+def test_workload_byte_and_op_counts():
+    from flashnn_b200 import workloads as W
+    assert W.a8w8_ops(8192, 8192, 8192) == 2 * 8192 ** 3
+    assert W.a8w8_bytes(16, 4096, 4096) == 16990272
+    assert W.dynamic_quant_bytes(4096, 4096) == 50339840
+    assert W.a16w4_bytes(1, 28672, 8192, 128) == 121184256
+    assert W.a16w4_bytes(4, 28672, 8192, 128) == 121405440 and W.a16w4_bytes(16, 28672, 8192, 128) == 122290176
