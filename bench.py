@@ -439,6 +439,13 @@ def run_case(args):
         op = flashnn_b200.GemmWeightOnly(torch.bfloat16)
         fn = lambda: op(x, qw, sc)
         work, unit = W.a16w4_bytes(m, n, k, 128) / 1e9, "GB/s"
+    elif name == "wo":
+        m, n, k = args.m or 2048, args.n or 8192, args.k or 8192
+        w = W.a16w8_prefill(m, n, k)
+        x, qw, sc = w["x"].to(device), w["w"].to(device), w["scale"].to(device)
+        op = flashnn_b200.GemmWeightOnly(torch.float16)
+        fn = lambda: op(x, qw, sc)
+        work, unit = 2.0 * m * n * k / 1e12, "TFLOP/s"
     elif name == "dq":
         m, k = args.m or 4096, args.k or 8192
         x = W.rand_normal((m, k), 0, torch.bfloat16, outliers=True).to(device)
@@ -460,7 +467,7 @@ def main():
     ap.add_argument("--warmup", type=int, default=5)
     ap.add_argument("--impl", choices=["native", "reference"], default="native")
     ap.add_argument("--cpu-rows", type=int, default=256, help="tokens in the CPU-baseline sample")
-    ap.add_argument("--case", choices=["a8w8", "gemv", "dq"], help="run one kernel only (profiling / A-B timing)")
+    ap.add_argument("--case", choices=["a8w8", "gemv", "dq", "wo"], help="run one kernel only (profiling / A-B timing)")
     ap.add_argument("--m", type=int)
     ap.add_argument("--n", type=int)
     ap.add_argument("--k", type=int)

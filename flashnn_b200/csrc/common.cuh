@@ -19,7 +19,17 @@ int fail(int status, const char* fmt, ...);
 int check_cuda(cudaError_t e, const char* what);
 int* device_status_word();  // device address of this device's status word, or nullptr
 int sm_count();
+// 2-D tiled tensor map over a row-major [rows, cols] matrix of 1- or 2-byte elements (row pitch in bytes);
+// the box is box_cols x box_rows elements, out-of-range elements read as zero.
+int make_tmap_2d(CUtensorMap* m, int elem_bytes, const void* base, int64_t rows, int64_t cols, int64_t pitch_bytes,
+                 int box_cols, int box_rows, bool swizzle128);
 
+
+// Prefill-shaped weight-only GEMM with per-channel scales (gemm_weight_only.cu).  Returns an fnn_status, or -1
+// when the operands do not meet the TMA path's alignment rules.
+int weight_only_prefill(const void* act, int act_dtype, int64_t lda, const void* qweight, int bits, const void* scale,
+                        const void* zp, int scale_dtype, const void* bias, int bias_dtype, void* out, int64_t ldo,
+                        int M, int N, int K, void* workspace, size_t workspace_bytes, cudaStream_t st);
 
 // codes written to the device status word
 enum DeviceCode : int {
@@ -123,20 +133,17 @@ __device__ __forceinline__ bool mbar_try_wait(uint64_t* bar, uint32_t parity) {
 constexpr uint64_t kWaitLimitNs = 2000000000ull;
 
 // Bounded wait: returns false when the limit ran out or another role already
-// reported a failure through *abort_flag (shared memory).  Each try_wait may
-// suspend the thread in hardware for up to the hinted time, so a waiting warp
-// does not compete for issue slots.
+// reported a failure through *abort_flag (shared memory).
 __device__ __forceinline__ bool mbar_wait_bounded(uint64_t* bar, uint32_t parity,
                                                   volatile int* abort_flag) {
   uint32_t done;
   const uint32_t addr = smem_u32(bar);
-  const uint32_t hint_ns = 200000u;
   asm volatile(
       "{\n\t.reg .pred p;\n\t"
-      "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2, %3;\n\t"
+      "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
       "selp.u32 %0, 1, 0, p;\n\t}\n"
       : "=r"(done)
-      : "r"(addr), "r"(parity), "r"(hint_ns)
+      : "r"(addr), "r"(parity)
       : "memory");
   if (done) return true;
   const uint64_t t0 = global_timer_ns();
@@ -144,10 +151,33 @@ __device__ __forceinline__ bool mbar_wait_bounded(uint64_t* bar, uint32_t parity
   while (true) {
     asm volatile(
         "{\n\t.reg .pred p;\n\t"
-        "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2, %3;\n\t"
+        "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
         "selp.u32 %0, 1, 0, p;\n\t}\n"
         : "=r"(done)
-        : "r"(addr), "r"(parity), "r"(hint_ns)
+        : "r"(addr), "r"(parity)
+        : "memory");
+    if (done) return true;
+    if ((++spins & 0xff) == 0) {
+      if (*abort_flag != 0) return false;
+      if (global_timer_ns() - t0 > kWaitLimitNs) return false;
+    }
+  }
+}
+
+// Same as mbar_wait_bounded, with acquire semantics at cluster scope: for barriers that threads of the
+// peer CTA arrive on after writing data this CTA (or its tensor core) goes on to read.
+__device__ __forceinline__ bool mbar_wait_bounded_cluster(uint64_t* bar, uint32_t parity, volatile int* abort_flag) {
+  uint32_t done;
+  const uint32_t addr = smem_u32(bar);
+  const uint64_t t0 = global_timer_ns();
+  uint32_t spins = 0;
+  while (true) {
+    asm volatile(
+        "{\n\t.reg .pred p;\n\t"
+        "mbarrier.try_wait.parity.acquire.cluster.shared::cta.b64 p, [%1], %2;\n\t"
+        "selp.u32 %0, 1, 0, p;\n\t}\n"
+        : "=r"(done)
+        : "r"(addr), "r"(parity)
         : "memory");
     if (done) return true;
     if ((++spins & 0xf) == 0) {

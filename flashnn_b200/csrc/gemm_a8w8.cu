@@ -537,37 +537,9 @@ __global__ void a8w8_generic_kernel(const int8_t* __restrict__ a, int64_t lda, c
 // ---------------------------------------------------------------------------
 // host side
 // ---------------------------------------------------------------------------
-using EncodeTiledFn = CUresult (*)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*,
-                                   const cuuint64_t*, const cuuint32_t*, const cuuint32_t*,
-                                   CUtensorMapInterleave, CUtensorMapSwizzle, CUtensorMapL2promotion,
-                                   CUtensorMapFloatOOBfill);
-
-EncodeTiledFn encode_tiled_fn() {
-  static EncodeTiledFn fn = nullptr;
-  static std::once_flag once;
-  std::call_once(once, [] {
-    void* sym = nullptr;
-    cudaDriverEntryPointQueryResult q;
-    if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &sym, cudaEnableDefault, &q) == cudaSuccess &&
-        q == cudaDriverEntryPointSuccess)
-      fn = reinterpret_cast<EncodeTiledFn>(sym);
-  });
-  return fn;
-}
-
 // int8 [rows, K] row-major (pitch `ld` bytes) -> tensor map with a {128 B, box_rows} box, 128-byte swizzle
 int make_tmap_i8(CUtensorMap* m, const void* base, int64_t rows, int64_t K, int64_t ld, int box_rows) {
-  EncodeTiledFn enc = encode_tiled_fn();
-  if (!enc) return fail(FNN_ERR_CUDA, "cuTensorMapEncodeTiled is not available from this driver");
-  const cuuint64_t dims[2] = {cuuint64_t(K), cuuint64_t(rows)};
-  const cuuint64_t strides[1] = {cuuint64_t(ld)};
-  const cuuint32_t box[2] = {cuuint32_t(kBK), cuuint32_t(box_rows)};
-  const cuuint32_t estr[2] = {1, 1};
-  const CUresult r = enc(m, CU_TENSOR_MAP_DATA_TYPE_UINT8, 2, const_cast<void*>(base), dims, strides, box, estr,
-                         CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B,
-                         CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
-  if (r != CUDA_SUCCESS) return fail(FNN_ERR_CUDA, "cuTensorMapEncodeTiled failed with CUresult %d", int(r));
-  return FNN_OK;
+  return make_tmap_2d(m, /*elem_bytes=*/1, base, rows, K, ld, kBK, box_rows, /*swizzle128=*/true);
 }
 
 template <typename OutT, int BN, int STAGES>

@@ -470,7 +470,9 @@ int launch_wo(WoParams p, void* workspace, size_t workspace_bytes, cudaStream_t 
 }  // namespace fnn
 
 extern "C" size_t fnn_gemm_weight_only_workspace_bytes(int64_t M, int64_t N, int64_t K, int weight_bits, int64_t group_size) {
-  (void)M; (void)N; (void)K; (void)weight_bits; (void)group_size;
+  (void)N; (void)K; (void)weight_bits;
+  // prefill kernel (M > 16, per-channel scales): row sums of the activations, read when zero-points are given
+  if (M > 16 && group_size == 0) return (size_t(M) * sizeof(float) + 255) / 256 * 256;
   return 0;  // neither the decode kernel nor the generic kernel uses scratch
 }
 
@@ -498,6 +500,12 @@ extern "C" int fnn_gemm_weight_only(const void* act, int act_dtype, int64_t lda,
   p.out = out; p.lda = lda; p.ldo = ldo; p.scale_dtype = scale_dtype; p.bias_dtype = bias_dtype;
   p.M = int(M); p.N = int(N); p.K = int(K); p.group = int(group_size);
   cudaStream_t st = static_cast<cudaStream_t>(stream);
+  if (M > 16 && group_size == 0) {
+    // prefill shapes with per-channel scales: tensor-core kernel (falls through when TMA cannot address the operands)
+    const int r = weight_only_prefill(act, act_dtype, lda, qweight, weight_bits, scale, zero_points, scale_dtype, bias,
+                                      bias_dtype, out, ldo, int(M), int(N), int(K), workspace, workspace_bytes, st);
+    if (r >= 0) return r;
+  }
   if (act_dtype == FNN_F16)
     return weight_bits == 4 ? launch_wo<__half, 4>(p, workspace, workspace_bytes, st) : launch_wo<__half, 8>(p, workspace, workspace_bytes, st);
   return weight_bits == 4 ? launch_wo<__nv_bfloat16, 4>(p, workspace, workspace_bytes, st) : launch_wo<__nv_bfloat16, 8>(p, workspace, workspace_bytes, st);
