@@ -512,3 +512,69 @@ int weight_only_prefill(const void* act, int act_dtype, int64_t lda, const void*
 }
 
 }  // namespace fnn
+
+// ---------------------------------------------------------------------------
+// Entry point that allocates nothing: the row-sum scratch lives in the library image.
+// ---------------------------------------------------------------------------
+namespace fnn {
+namespace {
+
+constexpr int kStaticRows = 65536;  // most activation rows (tokens) one call may bring
+
+// Row sums of the activations for the zero-point term; 256 KB on every GPU that loads the library, for as
+// long as the process lives.  In host code this name is only a handle for the runtime, not a device address.
+static __device__ __align__(256) float g_static_row_sums[kStaticRows];
+
+float* g_static_row_sums_addr[64];
+std::once_flag g_static_once[64];
+cudaError_t g_static_err[64];
+
+}  // namespace
+}  // namespace fnn
+
+extern "C" int fnn_gemm_weight_only_prefill_static(const void* act, int act_dtype, int64_t lda, const void* qweight,
+                                                   int weight_bits, const void* scale, const void* zero_points,
+                                                   int scale_dtype, const void* bias, int bias_dtype, void* out,
+                                                   int out_dtype, int64_t ldo, int64_t M, int64_t N, int64_t K,
+                                                   void* stream) {
+  using namespace fnn;
+  if (M < 0 || N < 0 || K <= 0 || lda < K || ldo < N)
+    return fail(FNN_ERR_SHAPE, "gemm_weight_only_prefill_static: M=%lld N=%lld K=%lld lda=%lld ldo=%lld", (long long)M,
+                (long long)N, (long long)K, (long long)lda, (long long)ldo);
+  if (M > kStaticRows)
+    return fail(FNN_ERR_WORKSPACE, "gemm_weight_only_prefill_static: M=%lld exceeds the %d rows the built-in scratch holds; "
+                "use fnn_gemm_weight_only with a caller-provided workspace", (long long)M, kStaticRows);
+  if (N > INT32_MAX || K > INT32_MAX) return fail(FNN_ERR_SHAPE, "gemm_weight_only_prefill_static: sizes must be below 2^31");
+  if (weight_bits != 4 && weight_bits != 8) return fail(FNN_ERR_UNSUPPORTED, "gemm_weight_only_prefill_static: weight_bits must be 4 or 8 (got %d)", weight_bits);
+  if (weight_bits == 4 && (N % 2) != 0) return fail(FNN_ERR_SHAPE, "gemm_weight_only_prefill_static: packed int4 needs an even N");
+  if (act_dtype != FNN_F16 && act_dtype != FNN_BF16) return fail(FNN_ERR_DTYPE, "gemm_weight_only_prefill_static: activations must be f16 or bf16");
+  if (out_dtype != act_dtype) return fail(FNN_ERR_DTYPE, "gemm_weight_only_prefill_static: output dtype must equal the activation dtype");
+  if (scale_dtype < FNN_F16 || scale_dtype > FNN_F32) return fail(FNN_ERR_DTYPE, "gemm_weight_only_prefill_static: bad scale dtype code %d", scale_dtype);
+  if (bias && (bias_dtype < FNN_F16 || bias_dtype > FNN_F32)) return fail(FNN_ERR_DTYPE, "gemm_weight_only_prefill_static: bad bias dtype code %d", bias_dtype);
+  if (M == 0 || N == 0) return FNN_OK;
+  if (!act || !qweight || !scale || !out) return fail(FNN_ERR_NULL_POINTER, "gemm_weight_only_prefill_static: null tensor pointer");
+
+  // Set-up, once per device and with that device current: ask the runtime where this device's copy of the
+  // array lives.  (The array's name itself must never be handed to a kernel from host code.)
+  int dev = 0;
+  if (int e = check_cuda(cudaGetDevice(&dev), "cudaGetDevice")) return e;
+  if (dev < 0 || dev >= 64) return fail(FNN_ERR_UNSUPPORTED, "gemm_weight_only_prefill_static: device index %d is out of range", dev);
+  std::call_once(g_static_once[dev], [dev] {
+    float* ptr = nullptr;
+    g_static_err[dev] = cudaGetSymbolAddress(reinterpret_cast<void**>(&ptr), g_static_row_sums);
+    g_static_row_sums_addr[dev] = (g_static_err[dev] == cudaSuccess) ? ptr : nullptr;
+  });
+  if (g_static_err[dev] != cudaSuccess || !g_static_row_sums_addr[dev])
+    return check_cuda(g_static_err[dev] != cudaSuccess ? g_static_err[dev] : cudaErrorInvalidSymbol,
+                      "cudaGetSymbolAddress(row-sum scratch)");
+
+  // Every element the kernel reads (rows 0..M-1) is rewritten by the row-sum kernel of this same call, so nothing
+  // left over from an earlier call is ever used and nothing has to be cleared.
+  const int r = weight_only_prefill(act, act_dtype, lda, qweight, weight_bits, scale, zero_points, scale_dtype, bias,
+                                    bias_dtype, out, ldo, int(M), int(N), int(K), g_static_row_sums_addr[dev],
+                                    sizeof(float) * kStaticRows, static_cast<cudaStream_t>(stream));
+  if (r < 0)
+    return fail(FNN_ERR_ALIGNMENT, "gemm_weight_only_prefill_static: act and qweight must be 16-byte aligned, lda a multiple "
+                "of 8 elements and K a multiple of 16");
+  return r;
+}

@@ -142,6 +142,30 @@ int fnn_gemm_weight_only(const void* act, int act_dtype, int64_t lda, const void
 size_t fnn_gemm_weight_only_workspace_bytes(int64_t M, int64_t N, int64_t K, int weight_bits,
                                             int64_t group_size);
 
+/*
+ * Weight-only GEMM with per-channel scales that needs no workspace from the caller and allocates nothing.
+ * No counterpart in the reference; it exists for callers that cannot obtain device memory at call time:
+ * a plugin inside a host process that owns every allocation, a server whose memory pool was carved up at
+ * start-up, a latency-critical loop where a cudaMalloc (and the device-wide synchronisation it implies) is
+ * not acceptable.  Same tensor-core kernel and same results as fnn_gemm_weight_only for per-channel scales;
+ * the one piece of scratch that kernel uses (fp32 row sums of the activations, read when zero-points are
+ * given) lives in a 256 KB array inside the library image instead of a caller buffer.
+ *
+ *   - group_size is implicitly 0 (scale, zero_points are [N]); all other arguments as fnn_gemm_weight_only;
+ *   - M may not exceed 65536 rows: larger calls are refused with FNN_ERR_WORKSPACE (use fnn_gemm_weight_only);
+ *   - act and qweight 16-byte aligned, lda a multiple of 8, K a multiple of 16 (else FNN_ERR_ALIGNMENT);
+ *   - the first call on each device looks up the array's device address (cudaGetSymbolAddress); make that
+ *     first call outside any stream capture;
+ *   - every call on a device shares the one array: calls that can overlap on the GPU (different streams) race
+ *     on it and must be serialised by the caller.  Nothing in it has to be cleared between calls: each call
+ *     rewrites the rows it reads;
+ *   - every GPU that loads the library holds the 256 KB until the process exits.
+ */
+int fnn_gemm_weight_only_prefill_static(const void* act, int act_dtype, int64_t lda, const void* qweight,
+                                        int weight_bits, const void* scale, const void* zero_points,
+                                        int scale_dtype, const void* bias, int bias_dtype, void* out,
+                                        int out_dtype, int64_t ldo, int64_t M, int64_t N, int64_t K, void* stream);
+
 #ifdef __cplusplus
 }
 #endif
