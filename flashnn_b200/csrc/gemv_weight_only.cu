@@ -70,6 +70,13 @@ template <> struct Mma<__nv_bfloat16> {
   }
 };
 
+// (a & b) ^ c in one LOP3 (truth table 0x6A); b and c are register operands so the compiler cannot split it
+// into two immediate-operand instructions
+__device__ __forceinline__ uint32_t and_xor(uint32_t a, uint32_t b, uint32_t c) {
+  uint32_t r;
+  asm("lop3.b32 %0, %1, %2, %3, 0x6A;" : "=r"(r) : "r"(a), "r"(b), "r"(c));
+  return r;
+}
 __device__ __forceinline__ uint32_t prmt(uint32_t a, uint32_t b, uint32_t sel) {
   uint32_t r;
   asm("prmt.b32 %0, %1, %2, %3;" : "=r"(r) : "r"(a), "r"(b), "r"(sel));
@@ -95,8 +102,8 @@ template <> struct Int4Frag<__nv_bfloat16> {
   // byte (n ^ 8) under a 0x43 high byte is the bf16 value 128 + (n ^ 8) = n + 136
   static constexpr float kInvAlpha = 1.f, kOffset = 136.f;
   static __device__ __forceinline__ void make(uint32_t w, uint32_t (&a)[4]) {
-    const uint32_t lo = (w & 0x0F0F0F0Fu) ^ 0x08080808u;
-    const uint32_t hi = ((w >> 4) & 0x0F0F0F0Fu) ^ 0x08080808u;
+    const uint32_t lo = and_xor(w, 0x0F0F0F0Fu, 0x08080808u);
+    const uint32_t hi = and_xor(w >> 4, 0x0F0F0F0Fu, 0x08080808u);
     const uint32_t m = 0x43434343u;
     a[0] = prmt(lo, m, 0x4140); a[1] = prmt(hi, m, 0x4140);
     a[2] = prmt(lo, m, 0x4342); a[3] = prmt(hi, m, 0x4342);
@@ -106,8 +113,8 @@ template <> struct Int4Frag<__half> {
   // byte ((n ^ 8) << 4) under a 0x64 high byte is the fp16 value 1024 + 16 (n ^ 8) = 16 (n + 72)
   static constexpr float kInvAlpha = 0.0625f, kOffset = 72.f;
   static __device__ __forceinline__ void make(uint32_t w, uint32_t (&a)[4]) {
-    const uint32_t lo = ((w << 4) & 0xF0F0F0F0u) ^ 0x80808080u;
-    const uint32_t hi = (w & 0xF0F0F0F0u) ^ 0x80808080u;
+    const uint32_t lo = and_xor(w << 4, 0xF0F0F0F0u, 0x80808080u);
+    const uint32_t hi = and_xor(w, 0xF0F0F0F0u, 0x80808080u);
     const uint32_t m = 0x64646464u;
     a[0] = prmt(lo, m, 0x4140); a[1] = prmt(hi, m, 0x4140);
     a[2] = prmt(lo, m, 0x4342); a[3] = prmt(hi, m, 0x4342);
@@ -370,6 +377,244 @@ gemv_mma_kernel(const WoParams p) {
   }
 }
 
+// Persistent form of gemv_mma_kernel for the common case (N % 16 == 0, K % 4096 == 0): CTA b handles row
+// groups b, b + gridDim.x, ... with the same eight warps and the same K slices throughout, so the per-warp
+// set-up is paid once, and each lane's cp.async FIFO (16 steps deep here) runs on across row-group boundaries.
+// Activation fragments are fetched one step ahead of their use.  Per row group the only CTA-wide event is
+// one barrier for the cross-warp sum; the partial-sum buffer is double-buffered so no second barrier is needed.
+template <typename T, int BITS, int NT, int SPU, bool PERCH>
+__global__ void __launch_bounds__(kGemvThreads, 2)
+gemv_mma_persistent_kernel(const WoParams p, const int num_rg) {
+  using S = GemvSmem<BITS>;
+  constexpr int kDepth = 2 * kRing;  // FIFO slots per lane: two blocks of kRing steps
+  constexpr int kWarpFifo = kDepth * S::kSlotBytes;
+  extern __shared__ __align__(128) uint8_t smem[];
+  __shared__ float red[2][kGemvWarps][NT][4][32];
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int g = lane >> 2, tig = lane & 3;
+  constexpr int R = (BITS == 4) ? 8 : 16;  // weight rows per row group
+  const int steps_w = p.K / (kStepK * kGemvWarps);
+  const int k_begin = warp * steps_w * kStepK;
+  int rg = blockIdx.x;
+  const uint8_t* wp = p.qw + (int64_t(rg) * R + g) * p.K + k_begin + tig * 16;  // row of accumulators {0,1}
+  const int64_t row_b = int64_t(8) * p.K;                                        // int8: row of accumulators {2,3}
+  const int64_t rg_stride = int64_t(gridDim.x) * R * p.K;
+  const uint32_t fifo = smem_u32(smem) + warp * kWarpFifo + lane * S::kLaneBytes;
+  const int groups_w = steps_w / SPU;
+  float* xs = reinterpret_cast<float*>(smem + kGemvWarps * kWarpFifo) + warp * groups_w * (8 * NT);  // [group][token]
+  auto issue = [&](uint32_t slot_addr, const uint8_t* w) {
+    cp_async16(slot_addr, w);
+    if (BITS == 8) cp_async16(slot_addr + 16, w + row_b);
+  };
+  // weights of step `v` counted from the first step of row group `rg_from` onwards (v may run into later row
+  // groups of this CTA); nullptr past the last row group
+  auto step_ptr = [&](const uint8_t* wbase, int rg_from, int v) -> const uint8_t* {
+    while (v >= steps_w) { v -= steps_w; wbase += rg_stride; rg_from += gridDim.x; }
+    return rg_from < num_rg ? wbase + v * kStepK : nullptr;
+  };
+  // prologue: the first kDepth steps of this CTA's work (every step commits a group, real or empty)
+  for (int b = 0; b < 2; ++b) {
+    const uint8_t* w = step_ptr(wp, rg, b * kRing);
+#pragma unroll
+    for (int j = 0; j < kRing; ++j) {
+      if (w) issue(fifo + (b * kRing + j) * S::kSlotBytes, w + j * kStepK);
+      cp_async_commit();
+    }
+  }
+
+  const uint8_t* xp[NT];
+#pragma unroll
+  for (int t = 0; t < NT; ++t)
+    xp[t] = reinterpret_cast<const uint8_t*>(reinterpret_cast<const T*>(p.act) + int64_t(min(g + 8 * t, p.M - 1)) * p.lda + k_begin + tig * 16);
+  // channel offsets inside a row group, and this warp's first scale group
+  const int ca = (BITS == 4) ? 2 * g : g;
+  const int cb = (BITS == 4) ? 2 * g + 1 : g + 8;
+  const int64_t group_pitch = int64_t(p.N) * int64_t(sizeof(T));
+  const uint8_t* sp0 = reinterpret_cast<const uint8_t*>(reinterpret_cast<const T*>(p.scale) + int64_t(warp) * (steps_w / SPU) * p.N);
+  const uint8_t* zp0 = p.zp ? reinterpret_cast<const uint8_t*>(p.zp) + (sp0 - reinterpret_cast<const uint8_t*>(p.scale)) : nullptr;
+
+  constexpr float kInvAlpha = (BITS == 4) ? Int4Frag<T>::kInvAlpha : 1.f;
+  constexpr float kOffset = (BITS == 4) ? Int4Frag<T>::kOffset : 0.f;
+  const bool ones = (BITS == 4) || p.zp != nullptr;
+  const uint32_t one2[4] = {Ones<T>::v, Ones<T>::v, Ones<T>::v, Ones<T>::v};
+
+  float tot[NT][4], acc[NT][4], xsum[NT][4];
+#pragma unroll
+  for (int t = 0; t < NT; ++t)
+#pragma unroll
+    for (int i = 0; i < 4; ++i) tot[t][i] = acc[t][i] = xsum[t][i] = 0.f;
+
+  auto compute_step = [&](const uint4& wv, const uint4& w2v, const uint4 (&xv)[NT][2], bool first) {
+    uint32_t xw[NT][8];
+#pragma unroll
+    for (int t = 0; t < NT; ++t) {
+      xw[t][0] = xv[t][0].x; xw[t][1] = xv[t][0].y; xw[t][2] = xv[t][0].z; xw[t][3] = xv[t][0].w;
+      xw[t][4] = xv[t][1].x; xw[t][5] = xv[t][1].y; xw[t][6] = xv[t][1].z; xw[t][7] = xv[t][1].w;
+    }
+    const uint32_t ww[4] = {wv.x, wv.y, wv.z, wv.w};
+    const uint32_t ww2[4] = {w2v.x, w2v.y, w2v.z, w2v.w};
+#pragma unroll
+    for (int q = 0; q < 4; ++q) {
+      uint32_t a[4];
+      if (BITS == 4) {
+        Int4Frag<T>::make(ww[q], a);
+      } else {
+        dequant_int8<T>(ww[q], a[0], a[2]);
+        dequant_int8<T>(ww2[q], a[1], a[3]);
+      }
+#pragma unroll
+      for (int t = 0; t < NT; ++t) {
+        if (first && q == 0) Mma<T>::run0(acc[t], a, xw[t][0], xw[t][1]);
+        else Mma<T>::run(acc[t], a, xw[t][2 * q], xw[t][2 * q + 1]);
+      }
+    }
+  };
+
+  // sum_k x over every flush group of this warp's K slice, once per CTA: an all-ones operand against the
+  // activation fragments leaves the sums in the accumulator layout (columns = tokens); lanes 0..3 store them
+  if (ones) {
+    const uint8_t* xq = xp[0];
+    for (int gi = 0; gi < groups_w; ++gi) {
+#pragma unroll
+      for (int j = 0; j < SPU; ++j) {
+#pragma unroll
+        for (int t = 0; t < NT; ++t) {
+          const uint4* x4 = reinterpret_cast<const uint4*>(xq + (xp[t] - xp[0]));
+          const uint4 x0 = __ldg(x4), x1 = __ldg(x4 + 1);
+          if (j == 0) Mma<T>::run0(xsum[t], one2, x0.x, x0.y); else Mma<T>::run(xsum[t], one2, x0.x, x0.y);
+          Mma<T>::run(xsum[t], one2, x0.z, x0.w);
+          Mma<T>::run(xsum[t], one2, x1.x, x1.y);
+          Mma<T>::run(xsum[t], one2, x1.z, x1.w);
+        }
+        xq += kStepK * int(sizeof(T));
+      }
+      if (g == 0) {
+#pragma unroll
+        for (int t = 0; t < NT; ++t)
+          *reinterpret_cast<float2*>(xs + gi * (8 * NT) + t * 8 + 2 * tig) = make_float2(xsum[t][0], xsum[t][1]);
+      }
+    }
+    __syncwarp();
+  }
+
+  int parity = 0;
+  uint32_t half = 0;  // which half of the FIFO the block being consumed sits in
+  for (; rg < num_rg; rg += gridDim.x) {
+    const int ch_a = rg * 16 + ca, ch_b = rg * 16 + cb;
+    const uint8_t* sp = sp0;
+    const uint8_t* zpp = zp0;
+    float za = kOffset / kInvAlpha, zb = kOffset / kInvAlpha;
+    if (PERCH && p.zp) {
+      za += load_as_f32(p.zp, p.scale_dtype, ch_a) / kInvAlpha;
+      zb += load_as_f32(p.zp, p.scale_dtype, ch_b) / kInvAlpha;
+    }
+    auto load_pair = [&](const uint8_t* base) -> uint32_t {
+      const T* sc = reinterpret_cast<const T*>(base);
+      if (BITS == 4) return __ldg(reinterpret_cast<const uint32_t*>(sc + ch_a));
+      return uint32_t(__ldg(reinterpret_cast<const uint16_t*>(sc + ch_a))) |
+             (uint32_t(__ldg(reinterpret_cast<const uint16_t*>(sc + ch_b))) << 16);
+    };
+    auto flush = [&](int gi, uint32_t sc, const uint8_t* zp_group) {
+      float sa = kInvAlpha, sb = kInvAlpha;
+      if (!PERCH) { sa *= lo16_f32<T>(sc); sb *= hi16_f32<T>(sc); }
+      if (ones) {
+        float fa = za, fb = zb;
+        if (!PERCH && p.zp) {
+          fa += load_as_f32(zp_group, p.scale_dtype, ch_a) / kInvAlpha;
+          fb += load_as_f32(zp_group, p.scale_dtype, ch_b) / kInvAlpha;
+        }
+#pragma unroll
+        for (int t = 0; t < NT; ++t) {
+          const float2 x = *reinterpret_cast<const float2*>(xs + gi * (8 * NT) + t * 8 + 2 * tig);
+          acc[t][0] = fmaf(-fa, x.x, acc[t][0]); acc[t][1] = fmaf(-fa, x.y, acc[t][1]);
+          acc[t][2] = fmaf(-fb, x.x, acc[t][2]); acc[t][3] = fmaf(-fb, x.y, acc[t][3]);
+        }
+      }
+#pragma unroll
+      for (int t = 0; t < NT; ++t) {
+        tot[t][0] = fmaf(sa, acc[t][0], tot[t][0]);
+        tot[t][1] = fmaf(sa, acc[t][1], tot[t][1]);
+        tot[t][2] = fmaf(sb, acc[t][2], tot[t][2]);
+        tot[t][3] = fmaf(sb, acc[t][3], tot[t][3]);
+      }
+    };
+
+    const uint8_t* xq = xp[0];
+    for (int s0 = 0; s0 < steps_w; s0 += kRing) {
+      uint32_t sc[kRing / SPU];
+      if (!PERCH) {
+#pragma unroll
+        for (int i = 0; i < kRing / SPU; ++i) sc[i] = load_pair(sp + i * group_pitch);
+      }
+      // the slots of this block are refilled with the block two ahead (same row group or a later one)
+      const uint8_t* wfill = step_ptr(wp, rg, s0 + kDepth);
+      const uint32_t slots = fifo + half * (kRing * S::kSlotBytes);
+      // activations are fetched one step ahead of their use
+      uint4 xn[NT][2];
+#pragma unroll
+      for (int t = 0; t < NT; ++t) {
+        const uint4* x4 = reinterpret_cast<const uint4*>(xq + (xp[t] - xp[0]));
+        xn[t][0] = __ldg(x4);
+        xn[t][1] = __ldg(x4 + 1);
+      }
+#pragma unroll
+      for (int j = 0; j < kRing; ++j) {
+        uint4 xc[NT][2];
+#pragma unroll
+        for (int t = 0; t < NT; ++t) { xc[t][0] = xn[t][0]; xc[t][1] = xn[t][1]; }
+        if (j + 1 < kRing) {
+#pragma unroll
+          for (int t = 0; t < NT; ++t) {
+            const uint4* x4 = reinterpret_cast<const uint4*>(xq + (j + 1) * (kStepK * int(sizeof(T))) + (xp[t] - xp[0]));
+            xn[t][0] = __ldg(x4);
+            xn[t][1] = __ldg(x4 + 1);
+          }
+        }
+        cp_async_wait<kDepth - 1>();  // step s0+j has landed (at most kDepth-1 newer groups pending)
+        const uint4 wv = lds128(slots + j * S::kSlotBytes);
+        uint4 w2v = wv;
+        if (BITS == 8) w2v = lds128(slots + j * S::kSlotBytes + 16);
+        compute_step(wv, w2v, xc, j % SPU == 0);
+        if (wfill) issue(slots + j * S::kSlotBytes, wfill + j * kStepK);
+        cp_async_commit();
+        if ((j + 1) % SPU == 0) flush((s0 + j) / SPU, PERCH ? 0u : sc[j / SPU], zpp ? zpp + (j / SPU) * group_pitch : nullptr);
+      }
+      half ^= 1;
+      xq += kRing * kStepK * int(sizeof(T));
+      sp += (kRing / SPU) * group_pitch;
+      if (zpp) zpp += (kRing / SPU) * group_pitch;
+    }
+
+    // cross-warp sum of this row group; the other half of `red` is still being read from the previous one
+#pragma unroll
+    for (int t = 0; t < NT; ++t)
+#pragma unroll
+      for (int i = 0; i < 4; ++i) { red[parity][warp][t][i][lane] = tot[t][i]; tot[t][i] = 0.f; }
+    __syncthreads();
+    if (warp == 0) {
+      T* out = reinterpret_cast<T*>(p.out);
+#pragma unroll
+      for (int t = 0; t < NT; ++t)
+#pragma unroll
+        for (int i = 0; i < 4; ++i) {
+          float v = 0.f;
+#pragma unroll
+          for (int w = 0; w < kGemvWarps; ++w) v += red[parity][w][t][i][lane];
+          const int ch = (i < 2) ? ch_a : ch_b;
+          const int m = t * 8 + 2 * tig + (i & 1);
+          if (m < p.M) {
+            if (PERCH) v *= load_as_f32(p.scale, p.scale_dtype, ch);
+            if (p.bias) v += load_as_f32(p.bias, p.bias_dtype, ch);
+            out[int64_t(m) * p.ldo + ch] = from_f32<T>(v);
+          }
+        }
+    }
+    parity ^= 1;
+    wp += rg_stride;
+  }
+  cp_async_wait<0>();
+}
+
 // Correctness path for everything the fast kernels do not cover (any M, K, group size):
 // one thread per output element, fp32 throughout, same order of operations per group.
 template <typename T, int BITS>
@@ -438,7 +683,15 @@ int launch_wo(WoParams p, void* workspace, size_t workspace_bytes, cudaStream_t 
   const int nt = p.M <= 8 ? 1 : 2;
   const unsigned grid = unsigned((p.N + 15) / 16);
   const size_t smem_bytes = GemvSmem<BITS>::kBytes;
+  // the persistent kernel's FIFO is twice as deep, followed by the per-warp table of activation sums
+  const size_t psmem_bytes = 2 * GemvSmem<BITS>::kBytes + size_t(p.K / (spu * kStepK)) * 8 * nt * sizeof(float);
   cudaError_t err;
+  // persistent form (int4): whole row groups only, K slices that are whole FIFO blocks; two resident CTAs per SM
+  const size_t psmem_cap = 2 * GemvSmem<BITS>::kBytes + 16384;
+  const bool persistent = (BITS == 4) && (p.N % 16 == 0) && (p.K % (kStepK * kGemvWarps * kRing) == 0) && psmem_bytes <= psmem_cap;
+  const int num_rg = p.N / 16;
+  const int resident = 2;
+  const unsigned pgrid = unsigned(num_rg < resident * sm_count() ? num_rg : resident * sm_count());
 #define FNN_GEMV_CASE(NT, SPU, PC)                                                                          \
   do {                                                                                                      \
     static bool configured[64] = {};                                                                        \
@@ -448,10 +701,16 @@ int launch_wo(WoParams p, void* workspace, size_t workspace_bytes, cudaStream_t 
     if (!configured[dev & 63]) {                                                                            \
       err = cudaFuncSetAttribute(gemv_mma_kernel<T, BITS, NT, SPU, PC>,                                     \
                                  cudaFuncAttributeMaxDynamicSharedMemorySize, int(smem_bytes));             \
+      if (err == cudaSuccess)                                                                               \
+        err = cudaFuncSetAttribute(gemv_mma_persistent_kernel<T, BITS, NT, SPU, PC>,                        \
+                                   cudaFuncAttributeMaxDynamicSharedMemorySize, int(psmem_cap));            \
       configured[dev & 63] = (err == cudaSuccess);                                                          \
     }                                                                                                       \
     if (err == cudaSuccess) {                                                                               \
-      gemv_mma_kernel<T, BITS, NT, SPU, PC><<<grid, kGemvThreads, smem_bytes, st>>>(p);                     \
+      if (persistent)                                                                                       \
+        gemv_mma_persistent_kernel<T, BITS, NT, SPU, PC><<<pgrid, kGemvThreads, psmem_bytes, st>>>(p, num_rg); \
+      else                                                                                                  \
+        gemv_mma_kernel<T, BITS, NT, SPU, PC><<<grid, kGemvThreads, smem_bytes, st>>>(p);                   \
       err = cudaGetLastError();                                                                             \
     }                                                                                                       \
   } while (0)
