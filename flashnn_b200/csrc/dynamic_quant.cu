@@ -33,10 +33,33 @@ template <typename T> __device__ __forceinline__ int quantise_one(float x, float
   return static_cast<int>(fminf(fmaxf(r, -128.f), 127.f));
 }
 
+template <typename T> __device__ __forceinline__ float lo_of(uint32_t w) {
+  const uint16_t l = static_cast<uint16_t>(w & 0xffffu);
+  return to_f32(*reinterpret_cast<const T*>(&l));
+}
+template <typename T> __device__ __forceinline__ float hi_of(uint32_t w) {
+  const uint16_t h = static_cast<uint16_t>(w >> 16);
+  return to_f32(*reinterpret_cast<const T*>(&h));
+}
+
 // Bits of fp32 that a conversion to T drops, and the midpoint pattern among them.
 template <typename T> struct DropBits;
 template <> struct DropBits<__nv_bfloat16> { static constexpr uint32_t mask = 0xFFFFu, mid = 0x8000u; };
 template <> struct DropBits<__half> { static constexpr uint32_t mask = 0x1FFFu, mid = 0x1000u; };
+
+// Two elements at once: returns the two quantised bytes in bits 0-7 and 8-15, and ORs into `amb` a word whose
+// sign bit is set when either x * (1/s) lies within 3 ulp of a rounding midpoint of T (the caller then redoes
+// the whole chunk with the exact division; that is rare).
+template <typename T> __device__ __forceinline__ uint32_t quantise_pair(uint32_t w, float inv_s, uint32_t& amb) {
+  const float r0 = __fmul_rn(lo_of<T>(w), inv_s), r1 = __fmul_rn(hi_of<T>(w), inv_s);
+  // (dropped bits) - (mid - 3) - 7 wraps below zero exactly when the dropped bits are in [mid-3, mid+3]
+  amb |= ((__float_as_uint(r0) & DropBits<T>::mask) - (DropBits<T>::mid + 4u)) & ~((__float_as_uint(r0) & DropBits<T>::mask) - (DropBits<T>::mid - 3u));
+  amb |= ((__float_as_uint(r1) & DropBits<T>::mask) - (DropBits<T>::mid + 4u)) & ~((__float_as_uint(r1) & DropBits<T>::mask) - (DropBits<T>::mid - 3u));
+  const uint32_t t2 = pack2<T>(r0, r1);  // both rounded to T in one instruction
+  const float t0 = fminf(lo_of<T>(t2), 127.f), t1 = fminf(hi_of<T>(t2), 127.f);
+  const uint32_t q0 = __float_as_uint(__fadd_rn(t0, 12582912.f)), q1 = __float_as_uint(__fadd_rn(t1, 12582912.f));
+  return __byte_perm(q0, q1, 0x0040);  // low bytes of q0, q1 in bytes 0 and 1
+}
 
 // Same result as quantise_one for s > 0, returned in the low byte (two's complement).
 template <typename T> __device__ __forceinline__ uint32_t quantise_fast(float x, float s, float inv_s) {
@@ -70,13 +93,14 @@ template <typename T> __device__ __forceinline__ float abs2max(uint32_t w) {
   return fmaxf(to_f32(lo), to_f32(hi));
 }
 
-template <typename T> __device__ __forceinline__ float lo_of(uint32_t w) {
-  const uint16_t l = static_cast<uint16_t>(w & 0xffffu);
-  return to_f32(*reinterpret_cast<const T*>(&l));
+// running max of |x| over packed pairs, kept as a packed pair (no conversion in the first pass)
+__device__ __forceinline__ uint32_t absmax2(uint32_t m, uint32_t w, __half) {
+  const __half2 r = __hmax2(*reinterpret_cast<__half2*>(&m), __habs2(*reinterpret_cast<__half2*>(&w)));
+  return *reinterpret_cast<const uint32_t*>(&r);
 }
-template <typename T> __device__ __forceinline__ float hi_of(uint32_t w) {
-  const uint16_t h = static_cast<uint16_t>(w >> 16);
-  return to_f32(*reinterpret_cast<const T*>(&h));
+__device__ __forceinline__ uint32_t absmax2(uint32_t m, uint32_t w, __nv_bfloat16) {
+  const __nv_bfloat162 r = __hmax2(*reinterpret_cast<__nv_bfloat162*>(&m), __habs2(*reinterpret_cast<__nv_bfloat162*>(&w)));
+  return *reinterpret_cast<const uint32_t*>(&r);
 }
 
 // Vector path: K % 8 == 0, 16-byte aligned rows in, 8-byte aligned rows out.
@@ -90,15 +114,14 @@ dq_row_vec_kernel(const T* __restrict__ x, int64_t ldx, int8_t* __restrict__ q, 
   const uint4* xr = reinterpret_cast<const uint4*>(x + row * ldx);
   const int nvec = K >> 3;
   uint4 v[NCHUNK];
-  float amax = 0.f;
+  uint32_t m2 = 0;  // packed pair of running maxima (+0, +0)
 #pragma unroll
   for (int c = 0; c < NCHUNK; ++c) {
     const int i = c * blockDim.x + threadIdx.x;
     v[c] = (i < nvec) ? __ldcs(xr + i) : make_uint4(0, 0, 0, 0);
-    amax = fmaxf(amax, fmaxf(fmaxf(abs2max<T>(v[c].x), abs2max<T>(v[c].y)),
-                             fmaxf(abs2max<T>(v[c].z), abs2max<T>(v[c].w))));
+    m2 = absmax2(absmax2(absmax2(absmax2(m2, v[c].x, T()), v[c].y, T()), v[c].z, T()), v[c].w, T());
   }
-  amax = block_max(amax, red);
+  float amax = block_max(fmaxf(lo_of<T>(m2), hi_of<T>(m2)), red);
   const float s = round_to<T>(__fdiv_rn(amax, 127.0f));
   if (threadIdx.x == 0) scale[row] = __float2half_rn(s);
   uint2* qr = reinterpret_cast<uint2*>(q + row * ldq);
@@ -130,14 +153,20 @@ dq_row_vec_kernel(const T* __restrict__ x, int64_t ldx, int8_t* __restrict__ q, 
     if (i < nvec) {
       const uint32_t w[4] = {v[c].x, v[c].y, v[c].z, v[c].w};
       uint32_t o[2];
+      uint32_t amb = 0;
 #pragma unroll
-      for (int h = 0; h < 2; ++h) {
-        const uint32_t q0 = quantise_fast<T>(lo_of<T>(w[2 * h]), s, inv_s);
-        const uint32_t q1 = quantise_fast<T>(hi_of<T>(w[2 * h]), s, inv_s);
-        const uint32_t q2 = quantise_fast<T>(lo_of<T>(w[2 * h + 1]), s, inv_s);
-        const uint32_t q3 = quantise_fast<T>(hi_of<T>(w[2 * h + 1]), s, inv_s);
-        // gather the four low bytes
-        o[h] = __byte_perm(__byte_perm(q0, q1, 0x0040), __byte_perm(q2, q3, 0x0040), 0x5410);
+      for (int h = 0; h < 2; ++h)  // [q0,q1,..] and [q2,q3,..] -> [q0,q1,q2,q3]
+        o[h] = __byte_perm(quantise_pair<T>(w[2 * h], inv_s, amb), quantise_pair<T>(w[2 * h + 1], inv_s, amb), 0x5410);
+      if (static_cast<int32_t>(amb) < 0) {
+        // some element of this chunk sits next to a rounding midpoint: redo the chunk element by element
+#pragma unroll
+        for (int h = 0; h < 2; ++h) {
+          const uint32_t q0 = quantise_fast<T>(lo_of<T>(w[2 * h]), s, inv_s);
+          const uint32_t q1 = quantise_fast<T>(hi_of<T>(w[2 * h]), s, inv_s);
+          const uint32_t q2 = quantise_fast<T>(lo_of<T>(w[2 * h + 1]), s, inv_s);
+          const uint32_t q3 = quantise_fast<T>(hi_of<T>(w[2 * h + 1]), s, inv_s);
+          o[h] = __byte_perm(__byte_perm(q0, q1, 0x0040), __byte_perm(q2, q3, 0x0040), 0x5410);
+        }
       }
       __stcs(qr + i, make_uint2(o[0], o[1]));
     }
