@@ -255,12 +255,32 @@ def run_native(args):
     out_gu = torch.empty(TOKENS, shard.n_gu, dtype=torch.bfloat16).pin_memory()
     out_dn = torch.empty(TOKENS, shard.n_dn, dtype=torch.bfloat16).pin_memory()
 
+    # Two side streams: the second input goes up while the first projection computes, and each output goes
+    # down as soon as its projection is done (PCIe is full duplex).  Everything is joined back into the
+    # launching stream before the step ends, so the CUDA events on that stream bracket all of it.
+    s_in, s_out = torch.cuda.Stream(device), torch.cuda.Stream(device)
+
     def e2e_step():
+        main = torch.cuda.current_stream(device)
+        s_in.wait_stream(main)
+        with torch.cuda.stream(s_in):
+            h = hh.to(device, non_blocking=True)
         x = hx.to(device, non_blocking=True)
-        h = hh.to(device, non_blocking=True)
-        y_gu, y_dn = shard.step(x, h)
-        out_gu.copy_(y_gu, non_blocking=True)
-        out_dn.copy_(y_dn, non_blocking=True)
+        qx, sx = shard.dq(x)
+        y_gu = shard.gemm(qx, shard.w_gu, sx, shard.col_gu)
+        s_out.wait_stream(main)
+        with torch.cuda.stream(s_out):
+            out_gu.copy_(y_gu, non_blocking=True)
+        main.wait_stream(s_in)
+        qh, sh = shard.dq(h)
+        y_dn = shard.gemm(qh, shard.w_dn, sh, shard.col_dn)
+        s_out.wait_stream(main)
+        with torch.cuda.stream(s_out):
+            out_dn.copy_(y_dn, non_blocking=True)
+        main.wait_stream(s_out)
+        for t in (h, y_gu, y_dn):
+            t.record_stream(s_out)
+        h.record_stream(main)
 
     e2e_steps = max(3, min(args.steps, 10))
     barrier()
@@ -299,9 +319,14 @@ def run_native(args):
         gu_ops = W.a8w8_ops(TOKENS, shard.n_gu, HIDDEN)
         achieved = gu_ops / (gu_ms * 1e-3) / 1e12
         int8_peak = 2.0 * peaks["bf16_sustained"]
-        roofline = dict(bound="tensor", kernel="a8w8_umma_kernel (gate/up projection of this rank)",
+        # DRAM bytes of one gate/up launch on one GPU from profiles/a8w8_gate_up_4096x57344x8192.md (one ncu capture:
+        # 619.2 MB read + 452.5 MB written); with G ranks the weight and output parts shrink by G, the activations do not
+        a_bytes = TOKENS * HIDDEN
+        traffic = int(a_bytes + (1071694336 - a_bytes) / world)
+        roofline = dict(bound="tensor", kernel="a8w8_umma_pair_kernel (gate/up projection of this rank)",
                         achieved=round(achieved, 1), peak=round(int8_peak, 1), unit="TFLOP/s",
-                        frac=round(achieved / int8_peak, 4), traffic=None,
+                        frac=round(achieved / int8_peak, 4), traffic=traffic,
+                        traffic_note="ncu capture at one GPU" + ("" if world == 1 else f", scaled to 1/{world} of the columns"),
                         peak_source=f"2 x {peaks['source']} sustained bf16 cuBLAS rate (int8 dense runs at twice the bf16 rate; "
                                     "no int8 figure is in MEASURED_PEAKS.json); ops are int8 multiply-adds counted as 2",
                         nominal_frac=round(achieved / 4500.0, 4), launch_ms=round(gu_ms, 4))
@@ -326,7 +351,8 @@ def run_native(args):
                        "timing": "CUDA events per step on the launching stream, max over ranks"},
             "e2e": {"value": round(total_ops / (e2e_ms_per_step * 1e-3) / 1e12, 3), "unit": "TOPS",
                     "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": d2h, "ms_per_step": round(e2e_ms_per_step, 3),
-                    "note": "pinned host x,h copied in, both outputs copied back, every step; weights stay resident"},
+                    "note": "pinned host x,h copied in, both outputs copied back, every step (copies on side streams, "
+                            "joined into the timed stream before the step ends); weights stay resident"},
             "gpu_launches": 4 * args.steps,
             "clocks": clocks, "roofline": roofline, "cpu_baseline": cpu,
             "allgather_ms": allgather_ms, "wall_s": round(wall, 3), "extra": extra,
