@@ -14,7 +14,8 @@
 // (xsum, a small prologue kernel into caller-provided scratch).
 //
 // Two rings: a deep one filled by TMA (activations + raw weight bytes, 24 KB per stage, hides the HBM/L2
-// latency) and a shallow one of converted weight tiles (16 KB per stage, filled locally).  Barriers:
+// latency) and one of converted weight tiles (16 KB per stage, filled locally; its depth has to cover the
+// commit -> converter -> MMA round trip across the CTA pair, which is several K blocks long).  Barriers:
 // raw_full (local, TMA bytes), conv_full (in the leader: its 4 converter warps + one relayed arrival for the
 // peer's 4, which meet on the peer's conv_done), empty and conv_empty (local, from the leader's tcgen05.commit
 // with a two-CTA mask); tmem_full / tmem_empty as in the A8W8 pair kernel.  Every wait is bounded.
@@ -30,8 +31,8 @@ constexpr int kTM = 128;        // tokens per CTA tile (256 per pair)
 constexpr int kTN = 256;        // channels per pair tile (128 converted per CTA)
 constexpr int kTK = 64;         // K per stage: 128 bytes of 16-bit operand
 constexpr int kPfThreads = 320; // 10 warps
-constexpr int kPfStages = 6;   // TMA ring: activations + raw weight bytes
-constexpr int kPfConvStages = 3;  // ring of converted weight tiles
+constexpr int kPfStages = 5;      // TMA ring: activations + raw weight bytes
+constexpr int kPfConvStages = 5;  // ring of converted weight tiles
 constexpr int kPfGroupM = 16;
 
 struct PfParams {
