@@ -164,29 +164,6 @@ __device__ __forceinline__ bool mbar_wait_bounded(uint64_t* bar, uint32_t parity
   }
 }
 
-// Same as mbar_wait_bounded, with acquire semantics at cluster scope: for barriers that threads of the
-// peer CTA arrive on after writing data this CTA (or its tensor core) goes on to read.
-__device__ __forceinline__ bool mbar_wait_bounded_cluster(uint64_t* bar, uint32_t parity, volatile int* abort_flag) {
-  uint32_t done;
-  const uint32_t addr = smem_u32(bar);
-  const uint64_t t0 = global_timer_ns();
-  uint32_t spins = 0;
-  while (true) {
-    asm volatile(
-        "{\n\t.reg .pred p;\n\t"
-        "mbarrier.try_wait.parity.acquire.cluster.shared::cta.b64 p, [%1], %2;\n\t"
-        "selp.u32 %0, 1, 0, p;\n\t}\n"
-        : "=r"(done)
-        : "r"(addr), "r"(parity)
-        : "memory");
-    if (done) return true;
-    if ((++spins & 0xf) == 0) {
-      if (*abort_flag != 0) return false;
-      if (global_timer_ns() - t0 > kWaitLimitNs) return false;
-    }
-  }
-}
-
 // ---------------------------------------------------------------------------
 // TMA (tiled, 2-D, no multicast)
 // ---------------------------------------------------------------------------

@@ -252,7 +252,7 @@ wo_umma_pair_kernel(const __grid_constant__ CUtensorMap tmap_x, const __grid_con
         tc_fence_after();
         const uint32_t tmem_d = tmem_base + buf * kTN;
         for (int kb = 0; kb < p.k_blocks; ++kb) {
-          ok = mbar_wait_bounded_cluster(&conv_full[cstage], cphase, abort_flag);
+          ok = mbar_wait_bounded(&conv_full[cstage], cphase, abort_flag);
           ok = __all_sync(0xffffffffu, ok);
           if (!ok) {
             if (leader_lane) pf_report(p.status, abort_flag, DEV_TIMEOUT_MMA);
