@@ -489,6 +489,13 @@ def run_case(args):
         op = flashnn_b200.DynamicQuantize()
         fn = lambda: op(x)
         work, unit = W.dynamic_quant_bytes(m, k) / 1e9, "GB/s"
+    elif name in ("rmsdq", "lndq"):
+        m, k = args.m or 4096, args.k or 8192
+        x = W.rand_normal((m, k), 0, torch.bfloat16, outliers=True).to(device)
+        op = (flashnn_b200.RMSNormDquant(k, 1e-5) if name == "rmsdq" else flashnn_b200.LayernormDquant(k, 1e-5))
+        op = op.to(device=device, dtype=torch.bfloat16)
+        fn = lambda: op(x)
+        work, unit = W.dynamic_quant_bytes(m, k) / 1e9, "GB/s"
     else:
         raise SystemExit(f"unknown case {name}")
     ts = time_steps(fn, args.steps, args.warmup, flush_buf)
@@ -504,7 +511,7 @@ def main():
     ap.add_argument("--warmup", type=int, default=5)
     ap.add_argument("--impl", choices=["native", "reference"], default="native")
     ap.add_argument("--cpu-rows", type=int, default=256, help="tokens in the CPU-baseline sample")
-    ap.add_argument("--case", choices=["a8w8", "gemv", "dq", "wo"], help="run one kernel only (profiling / A-B timing)")
+    ap.add_argument("--case", choices=["a8w8", "gemv", "dq", "wo", "rmsdq", "lndq"], help="run one kernel only (profiling / A-B timing)")
     ap.add_argument("--m", type=int)
     ap.add_argument("--n", type=int)
     ap.add_argument("--k", type=int)

@@ -1,8 +1,11 @@
 """B200-native implementation of FLASHNN's quantized-GEMM operators
-(DynamicQuantize, GemmA8W8, GemmWeightOnly) behind the reference's module API."""
+(DynamicQuantize, GemmA8W8, GemmWeightOnly) and of the fused norm + quantise
+producers of their int8 operand (RMSNormDquant, LayernormDquant) behind the
+reference's module API."""
 from .kernel_backend import (get_autotune_triton_kernels, get_use_triton,
                              set_autotune_triton_kernels, set_use_triton)
+from .norm import LayernormDquant, RMSNormDquant
 from .quant_gemm import DynamicQuantize, GemmA8W8, GemmWeightOnly
 
-__all__ = ["DynamicQuantize", "GemmA8W8", "GemmWeightOnly", "set_use_triton",
+__all__ = ["DynamicQuantize", "GemmA8W8", "GemmWeightOnly", "RMSNormDquant", "LayernormDquant", "set_use_triton",
            "set_autotune_triton_kernels", "get_use_triton", "get_autotune_triton_kernels"]

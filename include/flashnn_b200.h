@@ -143,6 +143,25 @@ size_t fnn_gemm_weight_only_workspace_bytes(int64_t M, int64_t N, int64_t K, int
                                             int64_t group_size);
 
 /*
+ * RMSNorm / LayerNorm fused with per-token dynamic int8 quantisation (the producer of fnn_gemm_a8w8's A operand).
+ * Replace `triton_rmsnorm_dquant_forward(x, weight, eps)` (flashnn/triton_kernels/rms_norm_dquant.py:80-96) and
+ * `triton_layer_norm_dquant_forward(x, weight, bias, eps)` (flashnn/triton_kernels/layer_norm_dquant.py:91-105);
+ * arithmetic follows `RMSNormDquant._torch_impl` (flashnn/norm.py:39-63: fp32 throughout, clamp to [-128, 127]) and
+ * `LayernormDquant._torch_impl` (flashnn/norm.py:94-124: the normalised row is rounded to the input dtype, the scale
+ * and the quotient are formed in that dtype, clamp to [-128, 127]).
+ *
+ *   x       [M, K]  f16 or bf16, ldx; K a multiple of 8 and at most 32768, rows 16-byte aligned
+ *   weight  [K]     (and bias [K] for the layer norm) of dtype w_dtype: the dtype of x, or f32; 16-byte aligned
+ *   q       [M, K]  int8, ldq (a multiple of 8)
+ *   scale   [M]     in the dtype of x
+ */
+int fnn_rms_norm_dquant(const void* x, int x_dtype, int64_t M, int64_t K, int64_t ldx, const void* weight,
+                        int w_dtype, float eps, int8_t* q, int64_t ldq, void* scale, void* stream);
+int fnn_layer_norm_dquant(const void* x, int x_dtype, int64_t M, int64_t K, int64_t ldx, const void* weight,
+                          const void* bias, int w_dtype, float eps, int8_t* q, int64_t ldq, void* scale,
+                          void* stream);
+
+/*
  * Weight-only GEMM with per-channel scales that needs no workspace from the caller and allocates nothing.
  * No counterpart in the reference; it exists for callers that cannot obtain device memory at call time:
  * a plugin inside a host process that owns every allocation, a server whose memory pool was carved up at

@@ -20,6 +20,8 @@ project):
 * `dequantize_reference`        flashnn/quant_gemm.py:14-36
 * `gemm_weight_only_reference`  flashnn/quant_gemm.py:148-206
 * `gemm_weight_only_fp32`       same contraction with no 16-bit rounding of w*s
+* `rms_norm_dquant`             flashnn/norm.py:39-63
+* `layer_norm_dquant`           flashnn/norm.py:94-124
 """
 from __future__ import annotations
 
@@ -193,3 +195,26 @@ def gemm_weight_only_fp32(act, quant_w, scale_w, bias=None, zero_points=None,
     if bias is not None:
         out = out + bias.float()
     return out if out_ty is None else out.to(out_ty)
+
+
+# ----------------------------------------------------------------------------
+# Norm + dynamic quantisation (the producers of the A8W8 activation operand)
+# ----------------------------------------------------------------------------
+def rms_norm_dquant(x: torch.Tensor, weight: torch.Tensor, eps: float = 1e-6):
+    """fp32 throughout: n = x * rsqrt(mean(x^2) + eps) * weight, scale = max|n| / 127,
+    q = clamp(round(n / scale), -128, 127).  Returns (int8 like x, scale x.shape[:-1] in x's dtype)."""
+    xf = x.float()
+    n = xf * torch.rsqrt(xf.pow(2).mean(-1, keepdim=True) + eps)
+    n = n * weight  # fp32 * (16-bit or fp32) parameter promotes to fp32
+    scale = n.abs().max(dim=-1, keepdim=True)[0] / 127.0
+    q = torch.clamp(torch.round(n / scale), -128.0, 127.0)
+    return q.to(torch.int8), scale.reshape(x.shape[:-1]).type_as(x)
+
+
+def layer_norm_dquant(x: torch.Tensor, weight: torch.Tensor, bias: torch.Tensor, eps: float = 1e-5):
+    """layer_norm in x's dtype, then absmax / 127, the quotient and its rounding all in that dtype.
+    Returns (int8 like x, scale [rows, 1] in x's dtype)."""
+    n = torch.nn.functional.layer_norm(x, (x.shape[-1],), weight, bias, eps)
+    scale = n.abs().max(dim=-1, keepdim=True)[0] / 127.0
+    q = torch.clamp(torch.round(n / scale), -128.0, 127.0)
+    return q.to(torch.int8), scale.reshape(-1, 1)

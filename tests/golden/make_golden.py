@@ -6,7 +6,7 @@ Run once, in a container that has the reference checkout (CPU only):
 
 It imports the reference package, selects its torch backend
 (`set_use_triton(False)`, flashnn/kernel_backend.py:27-29) and calls the
-unmodified operator classes (flashnn/quant_gemm.py:39-209) on small seeded CPU
+unmodified operator classes (flashnn/quant_gemm.py:39-209, flashnn/norm.py:39-124) on small seeded CPU
 tensors.  Inputs and outputs are stored as raw bits (16-bit floats as uint16)
 so the files are independent of the torch version that reads them.
 """
@@ -130,6 +130,42 @@ def wo_cases(flashnn):
     return cases
 
 
+def norm_cases(flashnn):
+    """RMSNormDquant / LayernormDquant on the shapes of the reference's tests
+    (tests/norm/test_rms_norm_dquant.py, tests/norm/test_layer_norm_dquant.py: [4, 128] and [3, 32, 1024],
+    the second one cut to 8 middle rows) with non-trivial weights."""
+    cases = {}
+    for name, kind, shape, dt, eps in [
+        ("rms_f16_4x128", "rms", (4, 128), torch.float16, 1e-5),
+        ("rms_f16_3x8x1024", "rms", (3, 8, 1024), torch.float16, 1e-5),
+        ("rms_bf16_16x4096", "rms", (16, 4096), torch.bfloat16, 1e-6),
+        ("ln_f16_4x128", "ln", (4, 128), torch.float16, 1e-5),
+        ("ln_f16_3x8x1024", "ln", (3, 8, 1024), torch.float16, 1e-5),
+        ("ln_bf16_16x4096", "ln", (16, 4096), torch.bfloat16, 1e-5),
+    ]:
+        g = gen(300 + len(cases))
+        x = torch.randn(*shape, generator=g).to(dt)
+        dim = shape[-1]
+        w = (torch.rand(dim, generator=g) + 0.5).to(dt)
+        if kind == "rms":
+            op = flashnn.RMSNormDquant(dim, eps).to(dt)
+            with torch.no_grad():
+                op.weight.copy_(w)
+                q, s = op(x)
+            d = dict(x=bits(x), weight=bits(w), q=bits(q), scale=bits(s))
+        else:
+            b = (torch.randn(dim, generator=g) * 0.1).to(dt)
+            op = flashnn.LayernormDquant(dim, eps).to(dt)
+            with torch.no_grad():
+                op.weight.copy_(w)
+                op.bias.copy_(b)
+                q, s = op(x)
+            d = dict(x=bits(x), weight=bits(w), bias=bits(b), q=bits(q), scale=bits(s))
+        d.update(dtype=str(dt).split(".")[-1], kind=kind, eps=np.float64(eps))
+        cases[name] = d
+    return cases
+
+
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--reference", required=True, help="path of the reference checkout")
@@ -141,7 +177,8 @@ def main():
     torch.set_num_threads(1)  # fixed reduction order inside the CPU matmul
     for fname, cases in [("dynamic_quant.npz", dq_cases(flashnn)),
                          ("gemm_a8w8.npz", a8w8_cases(flashnn)),
-                         ("gemm_weight_only.npz", wo_cases(flashnn))]:
+                         ("gemm_weight_only.npz", wo_cases(flashnn)),
+                         ("norm_dquant.npz", norm_cases(flashnn))]:
         flat = {}
         for cname, d in cases.items():
             for key, val in d.items():

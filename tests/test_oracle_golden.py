@@ -10,6 +10,7 @@ from tests import golden_io as G
 DQ = G.load("dynamic_quant.npz")
 A8 = G.load("gemm_a8w8.npz")
 WO = G.load("gemm_weight_only.npz")
+ND = G.load("norm_dquant.npz")
 
 
 def same_bits(t: torch.Tensor, arr: np.ndarray):
@@ -83,3 +84,20 @@ def test_int4_pack_roundtrip():
     # byte (j, k): low nibble = channel 2j, high nibble = channel 2j+1
     p = O.pack_int4(w).view(torch.uint8)
     assert int(p[3, 5]) == ((int(w[6, 5]) & 0xF) | ((int(w[7, 5]) & 0xF) << 4))
+
+
+@pytest.mark.parametrize("name", sorted(ND))
+def test_norm_dquant_matches_reference(name):
+    c = ND[name]
+    dt = G.dtype_of(c["dtype"])
+    x = G.tensor(c["x"], dt)
+    w = G.tensor(c["weight"], dt)
+    if str(c["kind"]) == "rms":
+        q, s = O.rms_norm_dquant(x, w, float(c["eps"]))
+        assert s.shape == x.shape[:-1]
+    else:
+        q, s = O.layer_norm_dquant(x, w, G.tensor(c["bias"], dt), float(c["eps"]))
+        assert s.shape == (x.numel() // x.shape[-1], 1)
+    assert q.shape == x.shape and s.dtype == dt
+    same_bits(q, c["q"])
+    same_bits(s, c["scale"])
