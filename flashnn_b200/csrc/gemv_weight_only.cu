@@ -21,6 +21,7 @@
 #include <type_traits>
 
 #include "common.cuh"
+#include "weight_only.cuh"
 
 namespace fnn {
 constexpr int kStepK = 64;   // K covered by one warp-wide 128-bit load per row (4 lanes x 16 B)
@@ -28,20 +29,6 @@ namespace {
 
 constexpr int kGemvWarps = 8;
 constexpr int kGemvThreads = kGemvWarps * 32;
-
-struct WoParams {
-  const void* act;      // [M, K] T
-  const uint8_t* qw;    // int8 [N, K] or packed [N/2, K]
-  const void* scale;    // [N] or [G, N]
-  const void* zp;       // nullptr or like scale
-  const void* bias;     // nullptr or [N]
-  void* out;
-  int64_t lda, ldo;
-  int scale_dtype, bias_dtype;
-  int M, N, K;
-  int group;  // 0 = per channel
-  int* status;  // device status word
-};
 
 template <typename T> struct Mma;
 template <> struct Mma<__half> {
@@ -670,6 +657,11 @@ int gemv_spu(const WoParams& p, int bits, int act_dtype) {
 
 template <typename T, int BITS>
 int launch_wo(WoParams p, void* workspace, size_t workspace_bytes, cudaStream_t st) {
+  if (BITS == 4 && p.M <= 16) {
+    // one to five tokens: integer tensor-pipe kernel (declines shapes it does not cover)
+    const int r = gemv_w4_imma(p, std::is_same<T, __half>::value ? FNN_F16 : FNN_BF16, st);
+    if (r >= 0) return r;
+  }
   const int spu = gemv_spu(p, BITS, std::is_same<T, __half>::value ? FNN_F16 : FNN_BF16);
   if (spu < 0) {
     const int64_t total = int64_t(p.M) * p.N;

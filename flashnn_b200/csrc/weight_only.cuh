@@ -1,0 +1,25 @@
+// Declarations shared by the weight-only kernels.
+#pragma once
+#include "common.cuh"
+
+namespace fnn {
+
+struct WoParams {
+  const void* act;      // [M, K] T
+  const uint8_t* qw;    // int8 [N, K] or packed [N/2, K]
+  const void* scale;    // [N] or [G, N]
+  const void* zp;       // nullptr or like scale
+  const void* bias;     // nullptr or [N]
+  void* out;
+  int64_t lda, ldo;
+  int scale_dtype, bias_dtype;
+  int M, N, K;
+  int group;  // 0 = per channel
+  int* status;  // device status word
+};
+
+// Packed-int4 decode kernel on the integer tensor pipe (gemv_w4_imma.cu), for at most kImmaMaxTokens tokens.
+// Returns an fnn_status, or -1 when the shape or alignment is outside what that kernel handles.
+int gemv_w4_imma(const WoParams& p, int act_dtype, cudaStream_t st);
+
+}  // namespace fnn

@@ -144,3 +144,46 @@ def test_weight_kind_is_inferred_from_shapes():
     with pytest.raises(AssertionError, match="Matrix B must be transposed"):
         flashnn_b200.GemmWeightOnly()(act, torch.zeros(24, 64, dtype=torch.int8).cuda(),
                                       torch.ones(24, dtype=torch.float16).cuda())
+
+
+# The one-to-five-token packed-int4 kernel (integer tensor pipe, activations as three int8 digit planes): every
+# option it handles, K slices of one and many steps, an outlier-heavy row, a tiny and a huge row, and rows of zeros.
+@pytest.mark.parametrize("dt", [torch.bfloat16, torch.float16])
+@pytest.mark.parametrize("m", [1, 2, 3, 5])
+@pytest.mark.parametrize("n,k,group,use_bias,use_zp", [
+    (272, 1024, 64, True, True), (64, 2048, 128, False, False), (48, 4096, 256, True, False), (32, 2048, 0, True, True),
+    (96, 3072, 0, False, False), (16, 8192, 128, False, True), (112, 1024, 0, False, True), (32, 28672, 128, False, False)])
+def test_int4_few_tokens(dt, m, n, k, group, use_bias, use_zp):
+    act, qw, scale, bias, zp = make(4, m, n, k, dt, group, use_bias, use_zp, seed=m + n + k)
+    g = torch.Generator().manual_seed(k)
+    act = torch.where(torch.rand(m, k, generator=g) < 0.002, act * 30, act)  # outliers
+    if m >= 2:
+        act[1] = 0  # a row of zeros gives the bias (or 0)
+    if m >= 3:
+        act[2] = act[2] * (1e-3 if dt == torch.float16 else 1e-30)  # a tiny row
+    if m >= 5:
+        act[4] = act[4] * (50 if dt == torch.float16 else 1e30)  # a huge row
+    out = run(act, qw, scale, bias, zp)
+    ref = O.gemm_weight_only_fp32(act, qw, scale, bias, zp)
+    finite = torch.isfinite(ref.to(dt).float())
+    # relative bound per row (rows differ by up to 60 orders of magnitude) on top of the stated absolute one
+    row_scale = ref.abs().amax(dim=1, keepdim=True)
+    err = (out.float() - ref).abs()
+    bound = ATOL + RTOL * ref.abs() + 4e-3 * row_scale * (2.0 ** -8 if dt == torch.bfloat16 else 2.0 ** -11) * 256
+    assert bool((err <= bound)[finite].all()), f"max excess {(err - bound)[finite].max():.3e}"
+    exact = ref.to(dt)
+    assert int((out != exact)[finite].sum()) <= max(3, 0.02 * out.numel())
+    if m >= 2:
+        want = torch.zeros(n) if bias is None else bias.float()
+        assert torch.equal(out[1].float(), want.to(dt).float())
+
+
+def test_int4_few_tokens_non_finite_row():
+    """A NaN or an infinity in a row makes that whole output row NaN; the other rows are unaffected."""
+    act, qw, scale, bias, zp = make(4, 2, 64, 2048, torch.bfloat16, 128, False, False, seed=3)
+    clean = run(act, qw, scale)
+    act2 = act.clone()
+    act2[0, 100] = float("inf")
+    out = run(act2, qw, scale)
+    assert bool(torch.isnan(out[0].float()).all())
+    assert torch.equal(out[1].view(torch.int16), clean[1].view(torch.int16))
