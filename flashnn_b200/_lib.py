@@ -33,6 +33,8 @@ SIGNATURES = {
                                         _c.c_void_p, _c.c_size_t, _c.c_void_p]),
     "fnn_gemm_weight_only_workspace_bytes": (_c.c_size_t, [_c.c_int64, _c.c_int64, _c.c_int64,
                                                            _c.c_int, _c.c_int64]),
+    "fnn_set_option": (_c.c_int, [_c.c_int, _c.c_int]),
+    "fnn_get_option": (_c.c_int, [_c.c_int]),
     "fnn_rms_norm_dquant": (_c.c_int, [_c.c_void_p, _c.c_int, _c.c_int64, _c.c_int64, _c.c_int64, _c.c_void_p, _c.c_int,
                                        _c.c_float, _c.c_void_p, _c.c_int64, _c.c_void_p, _c.c_void_p]),
     "fnn_layer_norm_dquant": (_c.c_int, [_c.c_void_p, _c.c_int, _c.c_int64, _c.c_int64, _c.c_int64, _c.c_void_p,
@@ -83,6 +85,13 @@ def check(status: int):
         l = lib()
         raise FlashNNError(status, f"{l.fnn_status_string(status).decode()}: "
                                    f"{l.fnn_last_error_string().decode()}")
+
+
+OPT_STATIC_WEIGHTS = 1
+
+
+def set_option(option: int, value: int) -> None:
+    check(lib().fnn_set_option(option, int(value)))
 
 
 def device_status() -> int:

@@ -1,6 +1,7 @@
 // Status plumbing shared by every entry point of the C ABI: per-thread error
 // text, the per-device status word that kernels write when a bounded wait runs
 // out, and cached device properties.
+#include <atomic>
 #include <cstdarg>
 #include <cstdio>
 #include <mutex>
@@ -49,6 +50,11 @@ int check_cuda(cudaError_t e, const char* what) {
   if (e == cudaSuccess) return FNN_OK;
   return fail(FNN_ERR_CUDA, "%s: %s", what, cudaGetErrorString(e));
 }
+
+namespace {
+std::atomic<int> g_opt_static_weights{0};
+}
+bool opt_static_weights() { return g_opt_static_weights.load(std::memory_order_relaxed) != 0; }
 
 int* device_status_word() {
   const int dev = current_device();
@@ -99,6 +105,19 @@ int sm_count() {
 }  // namespace fnn
 
 extern "C" int fnn_version(void) { return FNN_VERSION; }
+
+extern "C" int fnn_set_option(int option, int value) {
+  if (option == FNN_OPT_STATIC_WEIGHTS) {
+    fnn::g_opt_static_weights.store(value != 0, std::memory_order_relaxed);
+    return FNN_OK;
+  }
+  return fnn::fail(FNN_ERR_UNSUPPORTED, "fnn_set_option: unknown option %d", option);
+}
+
+extern "C" int fnn_get_option(int option) {
+  if (option == FNN_OPT_STATIC_WEIGHTS) return fnn::g_opt_static_weights.load(std::memory_order_relaxed);
+  return -1;
+}
 
 extern "C" const char* fnn_last_error_string(void) { return fnn::g_error; }
 

@@ -19,6 +19,7 @@ int fail(int status, const char* fmt, ...);
 int check_cuda(cudaError_t e, const char* what);
 int* device_status_word();  // device address of this device's status word, or nullptr
 int sm_count();
+bool opt_static_weights();  // FNN_OPT_STATIC_WEIGHTS
 // 2-D tiled tensor map over a row-major [rows, cols] matrix of 1- or 2-byte elements (row pitch in bytes);
 // the box is box_cols x box_rows elements, out-of-range elements read as zero.
 int make_tmap_2d(CUtensorMap* m, int elem_bytes, const void* base, int64_t rows, int64_t cols, int64_t pitch_bytes,

@@ -153,6 +153,11 @@ gemv_w4_imma_kernel(const WoParams p, const int num_rg) {
   const int nblk = K / (kImmaStepK * kImmaWarps * kImmaBlk);  // blocks per row group in a warp's K slice
   const int k_begin = warp * nblk * (kImmaBlk * kImmaStepK);
 
+  // Under programmatic stream serialisation this grid may start while the preceding kernel drains: let the next
+  // launch do the same, fetch weights (which that kernel does not write), and only then wait for it.  Without
+  // that launch attribute both instructions do nothing.
+  asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
+
   // ---- weights: start the FIFO before anything else -------------------------------------------------------------
   const uint32_t fifo = smem_u32(smem) + warp * (DEPTH * kImmaSlotBytes) + lane * 16;
   const int64_t rg_stride = int64_t(gridDim.x) * 8 * K;
@@ -192,6 +197,8 @@ gemv_w4_imma_kernel(const WoParams p, const int num_rg) {
     cp_async_commit();  // one group per block, real or empty, keeps the wait count fixed
     advance_fill();
   }
+
+  asm volatile("griddepcontrol.wait;" ::: "memory");  // activations and outputs belong to the stream order
 
   // ---- activations -> digit planes (once per CTA) ----------------------------------------------------------------
   float* sx = reinterpret_cast<float*>(smem + L.sx);
@@ -480,8 +487,18 @@ int launch_imma_x(const WoParams& p, size_t smem_bytes, cudaStream_t st) {
   // fewest CTAs that still reach the smallest possible number of row groups per CTA
   const int rounds = (num_rg + cap - 1) / cap;
   const int grid = (num_rg + rounds - 1) / rounds;
-  gemv_w4_imma_kernel<T, NF, SPU, PERCH, GZP, DEPTH, XREG><<<grid, kImmaCtaThreads, smem_bytes, st>>>(p, num_rg);
-  return check_cuda(cudaGetLastError(), "weight-only int4 decode launch");
+  cudaLaunchConfig_t cfg = {};
+  cfg.gridDim = dim3(unsigned(grid));
+  cfg.blockDim = dim3(kImmaCtaThreads);
+  cfg.dynamicSmemBytes = smem_bytes;
+  cfg.stream = st;
+  cudaLaunchAttribute attr[1];
+  attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+  attr[0].val.programmaticStreamSerializationAllowed = 1;
+  cfg.attrs = attr;
+  cfg.numAttrs = opt_static_weights() ? 1 : 0;
+  return check_cuda(cudaLaunchKernelEx(&cfg, gemv_w4_imma_kernel<T, NF, SPU, PERCH, GZP, DEPTH, XREG>, p, num_rg),
+                    "weight-only int4 decode launch");
 }
 
 template <typename T, int NF, int SPU, bool PERCH, bool GZP, int DEPTH>

@@ -48,6 +48,24 @@ typedef enum fnn_dtype {
   FNN_F32 = 2
 } fnn_dtype;
 
+/*
+ * Process-wide options (fnn_set_option / fnn_get_option).  No counterpart in the reference.
+ *
+ * FNN_OPT_STATIC_WEIGHTS (default 0).  A promise by the caller: the qweight, scale, zero_points and bias buffers given
+ * to fnn_gemm_weight_only are not written by the kernel that directly precedes the call in the same stream (true for
+ * inference, where weights are loaded once).  With it set, the packed-int4 decode kernel is launched with programmatic
+ * stream serialisation: its CTAs may become resident while the preceding kernel drains and start fetching weights; they
+ * touch neither the activations nor the output until that kernel has completed and its writes are visible
+ * (griddepcontrol.wait).  Results are unchanged; back-to-back decode calls lose the launch gap between them.
+ */
+typedef enum fnn_option {
+  FNN_OPT_STATIC_WEIGHTS = 1
+} fnn_option;
+
+/* Sets an option; FNN_ERR_UNSUPPORTED for an unknown one.  fnn_get_option returns the value, or -1 if unknown. */
+int fnn_set_option(int option, int value);
+int fnn_get_option(int option);
+
 /* Library version (FNN_VERSION of the build). */
 int fnn_version(void);
 

@@ -187,3 +187,29 @@ def test_int4_few_tokens_non_finite_row():
     out = run(act2, qw, scale)
     assert bool(torch.isnan(out[0].float()).all())
     assert torch.equal(out[1].view(torch.int16), clean[1].view(torch.int16))
+
+
+def test_static_weights_option_keeps_stream_order():
+    """FNN_OPT_STATIC_WEIGHTS lets the int4 decode kernel start before the preceding kernel has finished; it must
+    still see the activations that kernel wrote and must not overwrite an output that kernel still reads."""
+    import flashnn_b200
+    from flashnn_b200 import _lib
+    act, qw, scale, bias, zp = make(4, 2, 512, 8192, torch.bfloat16, 128, False, False, seed=11)
+    op = flashnn_b200.GemmWeightOnly(torch.bfloat16)
+    a, q, s = act.cuda(), qw.cuda(), scale.cuda()
+    base = [op(a * float(i + 1), q, s).cpu() for i in range(4)]
+    _lib.set_option(_lib.OPT_STATIC_WEIGHTS, 1)
+    try:
+        assert _lib.lib().fnn_get_option(_lib.OPT_STATIC_WEIGHTS) == 1
+        outs = []
+        for rep in range(3):
+            for i in range(4):
+                x = a * float(i + 1)  # produced by the kernel right before the call
+                y = op(x, q, s)
+                outs.append((i, y, y.float().sum()))  # consumed by the kernel right after it
+        torch.cuda.synchronize()
+        assert _lib.device_status() == 0
+        for i, y, _ in outs:
+            assert torch.equal(y.cpu().view(torch.int16), base[i].view(torch.int16))
+    finally:
+        _lib.set_option(_lib.OPT_STATIC_WEIGHTS, 0)
