@@ -26,11 +26,12 @@ int make_tmap_2d(CUtensorMap* m, int elem_bytes, const void* base, int64_t rows,
                  int box_cols, int box_rows, bool swizzle128);
 
 
-// Prefill-shaped weight-only GEMM with per-channel scales (gemm_weight_only.cu).  Returns an fnn_status, or -1
-// when the operands do not meet the TMA path's alignment rules.
+// Prefill-shaped weight-only GEMM (gemm_weight_only.cu); group == 0: per-channel scales, else the K-group size.
+// Returns an fnn_status, or -1 when the operands do not meet the TMA path's alignment rules or the group size is
+// not a multiple of the kernel's K block.
 int weight_only_prefill(const void* act, int act_dtype, int64_t lda, const void* qweight, int bits, const void* scale,
-                        const void* zp, int scale_dtype, const void* bias, int bias_dtype, void* out, int64_t ldo,
-                        int M, int N, int K, void* workspace, size_t workspace_bytes, cudaStream_t st);
+                        const void* zp, int scale_dtype, int group, const void* bias, int bias_dtype, void* out,
+                        int64_t ldo, int M, int N, int K, void* workspace, size_t workspace_bytes, cudaStream_t st);
 
 // codes written to the device status word
 enum DeviceCode : int {

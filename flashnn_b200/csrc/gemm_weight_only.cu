@@ -36,14 +36,15 @@ constexpr int kPfConvStages = 5;  // ring of converted weight tiles
 constexpr int kPfGroupM = 16;
 
 struct PfParams {
-  const void* scale;  // [N]
-  const void* zp;     // nullptr or [N]
+  const void* scale;  // [N], or [K / group, N] for group-wise scales
+  const void* zp;     // nullptr or like scale
   const void* bias;   // nullptr or [N]
   const float* xsum;  // [M] row sums of the activations (only with zero-points)
   void* out;
   int64_t ldo;
   int scale_dtype, bias_dtype;
   int M, N, K;
+  int group;  // 0: per-channel scales; else the K-group size (a multiple of the 64-wide K block)
   int tiles_m, tiles_n, k_blocks;
   int* status;
 };
@@ -92,6 +93,21 @@ __device__ __forceinline__ uint32_t pf_sub2(uint32_t a, uint32_t b, __nv_bfloat1
   return *reinterpret_cast<uint32_t*>(&r);
 }
 
+__device__ __forceinline__ uint32_t pf_mul2(uint32_t a, uint32_t b, __half) {
+  __half2 r = __hmul2(*reinterpret_cast<__half2*>(&a), *reinterpret_cast<__half2*>(&b));
+  return *reinterpret_cast<uint32_t*>(&r);
+}
+__device__ __forceinline__ uint32_t pf_mul2(uint32_t a, uint32_t b, __nv_bfloat16) {
+  __nv_bfloat162 r = __hmul2(*reinterpret_cast<__nv_bfloat162*>(&a), *reinterpret_cast<__nv_bfloat162*>(&b));
+  return *reinterpret_cast<uint32_t*>(&r);
+}
+// group-wise dequantisation of two exact integer values: T((n - zp) * s), the value the reference's torch path
+// stores (flashnn/quant_gemm.py:20-36); n - zp is exact for integer zero-points, so this is one rounding
+template <typename T> __device__ __forceinline__ uint32_t pf_dequant2(uint32_t n2, uint32_t s2, uint32_t z2, bool has_zp) {
+  if (has_zp) n2 = pf_sub2(n2, z2, T());
+  return pf_mul2(n2, s2, T());
+}
+
 // four int8 -> four exact T values (two registers, k order preserved)
 template <typename T> __device__ __forceinline__ void cvt_int8x4(uint32_t w, uint32_t& r01, uint32_t& r23);
 template <> __device__ __forceinline__ void cvt_int8x4<__half>(uint32_t w, uint32_t& r01, uint32_t& r23) {
@@ -136,7 +152,9 @@ __device__ __forceinline__ void umma_f16_pair(uint32_t tmem_d, uint64_t desc_a, 
 // byte offset of 16-byte chunk `kc` (0..7) of row `row` in a K-major tile with 128-byte rows and 128-byte swizzle
 __device__ __forceinline__ uint32_t sw128(uint32_t row, uint32_t kc) { return row * 128u + ((kc ^ (row & 7u)) << 4); }
 
-template <typename T, int BITS>
+// GRP: group-wise scales.  The converter warps then write T((n - zp) * s[k / group, n]) instead of the bare integer
+// and the epilogue only adds the bias.
+template <typename T, int BITS, bool GRP>
 __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(kPfThreads, 1)
 wo_umma_pair_kernel(const __grid_constant__ CUtensorMap tmap_x, const __grid_constant__ CUtensorMap tmap_w,
                     const PfParams p) {
@@ -321,12 +339,12 @@ wo_umma_pair_kernel(const __grid_constant__ CUtensorMap tmap_x, const __grid_con
       const int n0 = nb * kTN;
       for (int j = lane; j < kTN; j += 32) {
         const bool in = n0 + j < p.N;
-        const float s = in ? load_as_f32(p.scale, p.scale_dtype, n0 + j) : 0.f;
+        const float s = GRP ? 1.f : (in ? load_as_f32(p.scale, p.scale_dtype, n0 + j) : 0.f);
         cs[j] = s;
-        cz[j] = (in && p.zp) ? s * load_as_f32(p.zp, p.scale_dtype, n0 + j) : 0.f;
+        cz[j] = (!GRP && in && p.zp) ? s * load_as_f32(p.zp, p.scale_dtype, n0 + j) : 0.f;
         cb[j] = (in && p.bias) ? load_as_f32(p.bias, p.bias_dtype, n0 + j) : 0.f;
       }
-      const float xs = (p.zp && row < p.M) ? p.xsum[row] : 0.f;
+      const float xs = (!GRP && p.zp && row < p.M) ? p.xsum[row] : 0.f;
       __syncwarp();
 
       ok = mbar_wait_bounded(&tmem_full_bar[buf], acc_phase, abort_flag);
@@ -372,8 +390,27 @@ wo_umma_pair_kernel(const __grid_constant__ CUtensorMap tmap_x, const __grid_con
     int stage = 0, cstage = 0;
     uint32_t phase = 0, cphase = 0;
     bool ok = true;
+    // group-wise scales: packed (s, s) and (zp, zp) of the four channels this thread converts, reloaded per K group
+    uint32_t gs2[4] = {0, 0, 0, 0}, gz2[4] = {0, 0, 0, 0};
+    const bool has_zp = p.zp != nullptr;
+    const int kb_per_group = GRP ? p.group / kTK : 1;
     for (int t = pair_id; t < num_tiles && ok; t += num_pairs) {
+      int mb_c, nb_c;
+      pf_tile_coords(t, p.tiles_m, p.tiles_n, mb_c, nb_c);
+      const int ch_base = nb_c * kTN + int(rank) * (kTN / 2);  // first channel of this CTA's half of the tile
       for (int kb = 0; kb < p.k_blocks; ++kb) {
+        if (GRP && kb % kb_per_group == 0) {
+          const int64_t grow = int64_t(kb / kb_per_group) * p.N;
+#pragma unroll
+          for (int i = 0; i < 4; ++i) {
+            // int8: rows ct/4 + 32 i; int4: packed rows ct/4 + 32 (i / 2), channel 2 * prow + (i & 1)
+            const int ch = ch_base + ((BITS == 8) ? (ct >> 2) + 32 * i : 2 * ((ct >> 2) + 32 * (i >> 1)) + (i & 1));
+            const float sv = ch < p.N ? load_as_f32(p.scale, p.scale_dtype, grow + ch) : 0.f;
+            const float zv = (has_zp && ch < p.N) ? load_as_f32(p.zp, p.scale_dtype, grow + ch) : 0.f;
+            gs2[i] = pack2<T>(sv, sv);
+            gz2[i] = pack2<T>(zv, zv);
+          }
+        }
         ok = mbar_wait_bounded(&conv_empty[cstage], cphase ^ 1, abort_flag) &&
              mbar_wait_bounded(&raw_full[stage], phase, abort_flag);
         ok = __all_sync(0xffffffffu, ok);
@@ -395,6 +432,12 @@ wo_umma_pair_kernel(const __grid_constant__ CUtensorMap tmap_x, const __grid_con
             cvt_int8x4<T>(w.y, o0.z, o0.w);
             cvt_int8x4<T>(w.z, o1.x, o1.y);
             cvt_int8x4<T>(w.w, o1.z, o1.w);
+            if (GRP) {
+              o0.x = pf_dequant2<T>(o0.x, gs2[i], gz2[i], has_zp); o0.y = pf_dequant2<T>(o0.y, gs2[i], gz2[i], has_zp);
+              o0.z = pf_dequant2<T>(o0.z, gs2[i], gz2[i], has_zp); o0.w = pf_dequant2<T>(o0.w, gs2[i], gz2[i], has_zp);
+              o1.x = pf_dequant2<T>(o1.x, gs2[i], gz2[i], has_zp); o1.y = pf_dequant2<T>(o1.y, gs2[i], gz2[i], has_zp);
+              o1.z = pf_dequant2<T>(o1.z, gs2[i], gz2[i], has_zp); o1.w = pf_dequant2<T>(o1.w, gs2[i], gz2[i], has_zp);
+            }
             *reinterpret_cast<uint4*>(sw + sw128(row, 2 * c)) = o0;
             *reinterpret_cast<uint4*>(sw + sw128(row, 2 * c + 1)) = o1;
           }
@@ -410,6 +453,17 @@ wo_umma_pair_kernel(const __grid_constant__ CUtensorMap tmap_x, const __grid_con
             cvt_int4x8<T>(w.y, l0.z, l0.w, h0.z, h0.w);
             cvt_int4x8<T>(w.z, l1.x, l1.y, h1.x, h1.y);
             cvt_int4x8<T>(w.w, l1.z, l1.w, h1.z, h1.w);
+            if (GRP) {
+              const uint32_t sl = gs2[2 * i], zl = gz2[2 * i], sh = gs2[2 * i + 1], zh = gz2[2 * i + 1];
+              l0.x = pf_dequant2<T>(l0.x, sl, zl, has_zp); l0.y = pf_dequant2<T>(l0.y, sl, zl, has_zp);
+              l0.z = pf_dequant2<T>(l0.z, sl, zl, has_zp); l0.w = pf_dequant2<T>(l0.w, sl, zl, has_zp);
+              l1.x = pf_dequant2<T>(l1.x, sl, zl, has_zp); l1.y = pf_dequant2<T>(l1.y, sl, zl, has_zp);
+              l1.z = pf_dequant2<T>(l1.z, sl, zl, has_zp); l1.w = pf_dequant2<T>(l1.w, sl, zl, has_zp);
+              h0.x = pf_dequant2<T>(h0.x, sh, zh, has_zp); h0.y = pf_dequant2<T>(h0.y, sh, zh, has_zp);
+              h0.z = pf_dequant2<T>(h0.z, sh, zh, has_zp); h0.w = pf_dequant2<T>(h0.w, sh, zh, has_zp);
+              h1.x = pf_dequant2<T>(h1.x, sh, zh, has_zp); h1.y = pf_dequant2<T>(h1.y, sh, zh, has_zp);
+              h1.z = pf_dequant2<T>(h1.z, sh, zh, has_zp); h1.w = pf_dequant2<T>(h1.w, sh, zh, has_zp);
+            }
             *reinterpret_cast<uint4*>(sw + sw128(2 * prow, 2 * c)) = l0;
             *reinterpret_cast<uint4*>(sw + sw128(2 * prow, 2 * c + 1)) = l1;
             *reinterpret_cast<uint4*>(sw + sw128(2 * prow + 1, 2 * c)) = h0;
@@ -449,12 +503,12 @@ __global__ void row_sum_kernel(const T* __restrict__ act, int64_t lda, float* __
   if (lane == 0) xsum[row] = s;
 }
 
-template <typename T, int BITS>
-int launch_prefill(const T* act, int64_t lda, const uint8_t* qw, PfParams p, float* xsum_ws, cudaStream_t st) {
+template <typename T, int BITS, bool GRP>
+int launch_prefill_g(const T* act, int64_t lda, const uint8_t* qw, PfParams p, float* xsum_ws, cudaStream_t st) {
   using L = PfSmem<BITS>;
   static_assert(L::kDynamicBytes <= 227 * 1024, "shared memory budget");
   static_assert(L::kStageBytes % 1024 == 0 && L::kWBytes % 1024 == 0 && L::kConvOff % 1024 == 0, "tile alignment");
-  auto kern = wo_umma_pair_kernel<T, BITS>;
+  auto kern = wo_umma_pair_kernel<T, BITS, GRP>;
   static std::once_flag once[64];
   int dev = 0;
   cudaGetDevice(&dev);
@@ -463,7 +517,7 @@ int launch_prefill(const T* act, int64_t lda, const uint8_t* qw, PfParams p, flo
     attr_err = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, L::kDynamicBytes);
   });
   if (attr_err != cudaSuccess) return check_cuda(attr_err, "cudaFuncSetAttribute(weight-only prefill)");
-  if (p.zp) {
+  if (p.zp && !GRP) {
     row_sum_kernel<T><<<unsigned((int64_t(p.M) * 32 + 255) / 256), 256, 0, st>>>(act, lda, xsum_ws, p.M, p.K);
     if (int e = check_cuda(cudaGetLastError(), "row_sum launch")) return e;
     p.xsum = xsum_ws;
@@ -481,18 +535,25 @@ int launch_prefill(const T* act, int64_t lda, const uint8_t* qw, PfParams p, flo
   return check_cuda(cudaGetLastError(), "weight-only prefill launch");
 }
 
+template <typename T, int BITS>
+int launch_prefill(const T* act, int64_t lda, const uint8_t* qw, PfParams p, float* xsum_ws, cudaStream_t st) {
+  return p.group > 0 ? launch_prefill_g<T, BITS, true>(act, lda, qw, p, xsum_ws, st)
+                     : launch_prefill_g<T, BITS, false>(act, lda, qw, p, xsum_ws, st);
+}
+
 }  // namespace
 
 // Entry used by fnn_gemm_weight_only for M > 16 with per-channel scales.  Returns -1 when the operands do
 // not meet the TMA path's alignment rules (the caller then takes the generic kernel).
 int weight_only_prefill(const void* act, int act_dtype, int64_t lda, const void* qweight, int bits, const void* scale,
-                        const void* zp, int scale_dtype, const void* bias, int bias_dtype, void* out, int64_t ldo,
-                        int M, int N, int K, void* workspace, size_t workspace_bytes, cudaStream_t st) {
+                        const void* zp, int scale_dtype, int group, const void* bias, int bias_dtype, void* out,
+                        int64_t ldo, int M, int N, int K, void* workspace, size_t workspace_bytes, cudaStream_t st) {
+  if (group > 0 && (group % kTK != 0 || K % group != 0)) return -1;  // a K block must lie inside one scale group
   if (reinterpret_cast<uintptr_t>(act) % 16 != 0 || (lda * 2) % 16 != 0) return -1;
   if (reinterpret_cast<uintptr_t>(qweight) % 16 != 0 || K % 16 != 0) return -1;
   if (bits == 4 && N % 2 != 0) return -1;
   float* xsum = nullptr;
-  if (zp) {
+  if (zp && group == 0) {
     const size_t need = size_t(M) * sizeof(float);
     if (!workspace || workspace_bytes < need)
       return fail(FNN_ERR_WORKSPACE, "gemm_weight_only: zero-points need %zu bytes of workspace, got %zu", need, workspace_bytes);
@@ -501,7 +562,7 @@ int weight_only_prefill(const void* act, int act_dtype, int64_t lda, const void*
   }
   PfParams p{};
   p.scale = scale; p.zp = zp; p.bias = bias; p.xsum = nullptr; p.out = out; p.ldo = ldo;
-  p.scale_dtype = scale_dtype; p.bias_dtype = bias_dtype; p.M = M; p.N = N; p.K = K;
+  p.scale_dtype = scale_dtype; p.bias_dtype = bias_dtype; p.M = M; p.N = N; p.K = K; p.group = group;
   p.status = device_status_word();
   const uint8_t* qw = static_cast<const uint8_t*>(qweight);
   if (act_dtype == FNN_F16) {
@@ -571,7 +632,7 @@ extern "C" int fnn_gemm_weight_only_prefill_static(const void* act, int act_dtyp
 
   // Every element the kernel reads (rows 0..M-1) is rewritten by the row-sum kernel of this same call, so nothing
   // left over from an earlier call is ever used and nothing has to be cleared.
-  const int r = weight_only_prefill(act, act_dtype, lda, qweight, weight_bits, scale, zero_points, scale_dtype, bias,
+  const int r = weight_only_prefill(act, act_dtype, lda, qweight, weight_bits, scale, zero_points, scale_dtype, 0, bias,
                                     bias_dtype, out, ldo, int(M), int(N), int(K), g_static_row_sums_addr[dev],
                                     sizeof(float) * kStaticRows, static_cast<cudaStream_t>(stream));
   if (r < 0)

@@ -751,10 +751,11 @@ extern "C" int fnn_gemm_weight_only(const void* act, int act_dtype, int64_t lda,
   p.out = out; p.lda = lda; p.ldo = ldo; p.scale_dtype = scale_dtype; p.bias_dtype = bias_dtype;
   p.M = int(M); p.N = int(N); p.K = int(K); p.group = int(group_size);
   cudaStream_t st = static_cast<cudaStream_t>(stream);
-  if (M > 16 && group_size == 0) {
-    // prefill shapes with per-channel scales: tensor-core kernel (falls through when TMA cannot address the operands)
-    const int r = weight_only_prefill(act, act_dtype, lda, qweight, weight_bits, scale, zero_points, scale_dtype, bias,
-                                      bias_dtype, out, ldo, int(M), int(N), int(K), workspace, workspace_bytes, st);
+  if (M > 16) {
+    // prefill shapes: tensor-core kernel (falls through when TMA cannot address the operands or the group size is odd)
+    const int r = weight_only_prefill(act, act_dtype, lda, qweight, weight_bits, scale, zero_points, scale_dtype,
+                                      int(group_size), bias, bias_dtype, out, ldo, int(M), int(N), int(K), workspace,
+                                      workspace_bytes, st);
     if (r >= 0) return r;
   }
   if (act_dtype == FNN_F16)

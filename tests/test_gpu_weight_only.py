@@ -81,8 +81,8 @@ def test_decode_shapes(kind, dt, group, m):
     assert_within_bound(out, act, qw, scale, bias, zp)
 
 
-@pytest.mark.parametrize("kind,m,n,k,group", [(4, 17, 64, 256, 64), (8, 40, 50, 200, 0), (4, 3, 30, 96, 32),
-                                              (8, 2, 7, 33, 0), (4, 130, 128, 512, 128)])
+@pytest.mark.parametrize("kind,m,n,k,group", [(4, 17, 64, 256, 32), (8, 40, 50, 200, 0), (4, 3, 30, 96, 32),
+                                              (8, 2, 7, 33, 0), (4, 130, 128, 480, 96)])
 def test_generic_path_shapes(kind, m, n, k, group):
     act, qw, scale, bias, zp = make(kind, m, n, k, torch.float16, group, True, True, seed=k)
     out = run(act, qw, scale, bias, zp)
@@ -213,3 +213,49 @@ def test_static_weights_option_keeps_stream_order():
             assert torch.equal(y.cpu().view(torch.int16), base[i].view(torch.int16))
     finally:
         _lib.set_option(_lib.OPT_STATIC_WEIGHTS, 0)
+
+
+# Prefill shapes (M > 16) with group-wise scales run on the tensor-core kernel, whose converter warps store
+# T((w - zp) * s) exactly as the reference's torch path does (flashnn/quant_gemm.py:20-36), so the parity of record
+# for this path is the restated reference: same weights bit for bit, only the fp32 summation order differs.
+@pytest.mark.parametrize("kind", [8, 4])
+@pytest.mark.parametrize("dt", [torch.float16, torch.bfloat16])
+@pytest.mark.parametrize("m,n,k,group,use_bias,use_zp", [
+    (17, 64, 256, 64, False, False), (130, 128, 512, 128, True, True), (300, 1000, 2048, 128, True, False),
+    (513, 258, 1024, 256, False, True), (64, 512, 4096, 64, True, True)])
+def test_prefill_group_wise_shapes(kind, dt, m, n, k, group, use_bias, use_zp):
+    act, qw, scale, bias, zp = make(kind, m, n, k, dt, group, use_bias, use_zp, seed=m + kind + group)
+    out = run(act, qw, scale, bias, zp)
+    # the reference's dequantised weights (rounded to 16 bits per group), its fp32 product, the bias added in fp32 and
+    # one final rounding: what its int4 branch does; its int8 branch rounds once more before the bias
+    # (flashnn/quant_gemm.py:168-173), which the kernel deliberately does not
+    w = qw if kind == 8 else O.unpack_int4(qw)
+    dq = O.dequantize_reference(w.transpose(0, 1), scale, zp)
+    ref32 = torch.matmul(act.float(), dq.float())
+    if bias is not None:
+        ref32 = ref32 + bias.float()
+    ref = ref32.to(dt).float()
+    err = (out.float() - ref32).abs()
+    bound = ATOL + RTOL * ref32.abs()
+    assert bool((err <= bound).all()), f"max excess {(err - bound).max():.3e}"
+    assert float((out.float() != ref).float().mean()) < 0.02  # almost everywhere the same 16-bit value
+    if kind == 4 or bias is None:  # the reference's own output, where it rounds as the kernel does
+        whole = O.gemm_weight_only_reference(act, qw, scale, bias, zp, out_ty=dt).float()
+        assert float((out.float() != whole).float().mean()) < 0.02
+    # against the fp32 dequant-matmul the rounding of w*s shows: report-only bound, a few per cent of one output's scale
+    ref2 = O.gemm_weight_only_fp32(act, qw, scale, bias, zp)
+    assert float((out.float() - ref2).abs().max()) <= 0.02 * float(ref2.abs().max())
+
+
+def test_prefill_group_wise_full_size():
+    """A16W4 prefill at the decode config's weight shape (N=28672, K=8192, group 128) with 256 tokens: sampled rows
+    against the restated reference."""
+    from flashnn_b200 import workloads as W
+    w = W.a16w4_decode(16)
+    g = torch.Generator().manual_seed(9)
+    x = torch.randn(256, 8192, generator=g).to(torch.bfloat16)
+    out = run(x, w["qw"], w["scale"])
+    rows = [0, 17, 100, 255]
+    ref = O.gemm_weight_only_reference(x[rows], w["qw"], w["scale"], None, None, out_ty=torch.bfloat16).float()
+    err = (out[rows].float() - ref).abs()
+    assert bool((err <= ATOL + RTOL * ref.abs()).all())
