@@ -534,6 +534,20 @@ def run_case(args):
         op = flashnn_b200.DynamicQuantize()
         fn = lambda: op(x)
         work, unit = W.dynamic_quant_bytes(m, k) / 1e9, "GB/s"
+    elif name == "moe":
+        # Mixtral-8x7B-shaped expert layer (gate/up): E = 8, top-2, K = 4096 -> N = 28672, int8 weights
+        sys.path.insert(0, os.path.dirname(os.path.abspath(__file__)))
+        from tests.moe_util import make_moe_case
+        m, n, k = args.m or 64, args.n or 28672, args.k or 4096
+        e, top_k, bm = 8, 2, (16 if m <= 64 else 128)
+        c = {kk: v.to(device) for kk, v in make_moe_case(m, e, n, k, top_k, bm, seed=0).items()}
+        out = torch.empty(m, top_k, n, dtype=torch.bfloat16, device=device)
+        fn = lambda: flashnn_b200.fused_moe_a8w8_forward(c["a"], c["b"], out, c["alpha_row"], c["alpha_col"], c["topk_w"],
+                                                         c["topk_ids"], c["sorted_ids"], c["expert_ids"], c["npp"], True, top_k, bm)
+        if m <= 256:
+            work, unit = (e * n * k + m * top_k * n * 2 + m * k) / 1e9, "GB/s"
+        else:
+            work, unit = 2.0 * m * top_k * n * k / 1e12, "TOPS"
     elif name in ("rmsdq", "lndq"):
         m, k = args.m or 4096, args.k or 8192
         x = W.rand_normal((m, k), 0, torch.bfloat16, outliers=True).to(device)
@@ -556,7 +570,7 @@ def main():
     ap.add_argument("--warmup", type=int, default=5)
     ap.add_argument("--impl", choices=["native", "reference"], default="native")
     ap.add_argument("--cpu-rows", type=int, default=256, help="tokens in the CPU-baseline sample")
-    ap.add_argument("--case", choices=["a8w8", "gemv", "dq", "wo", "rmsdq", "lndq"], help="run one kernel only (profiling / A-B timing)")
+    ap.add_argument("--case", choices=["a8w8", "gemv", "dq", "wo", "rmsdq", "lndq", "moe"], help="run one kernel only (profiling / A-B timing)")
     ap.add_argument("--m", type=int)
     ap.add_argument("--n", type=int)
     ap.add_argument("--k", type=int)

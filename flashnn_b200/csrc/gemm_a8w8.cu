@@ -38,6 +38,14 @@ struct A8W8Params {
   int M, N, K;
   int tiles_m, tiles_n, k_blocks;
   int* status;  // device status word
+  // Fused-MoE mode (kernel template flag MOE): A is the expert-sorted copy of the token rows [EM, K], B is the
+  // stack of expert weights seen as [E * N, K]; a tile is `tile_rows` sorted slots of one expert x BN channels.
+  const int32_t* sorted_ids;       // [EM] flat (token * top_k + choice) index per slot, >= num_valid for padding
+  const int32_t* expert_ids;       // [EM / block_m] expert of each block of block_m slots
+  const int32_t* num_post_padded;  // [1] slots in use (a multiple of block_m)
+  const void* topk_w;              // [num_valid] routing weights
+  int topk_w_dtype, top_k, block_m, tile_rows, num_valid, mul_w;
+  int64_t col_stride_e;            // elements between two experts' rows of alpha_col
 };
 
 template <int BN, int STAGES> struct SmemLayout {
@@ -109,7 +117,34 @@ __device__ __forceinline__ void store_chunk(const uint32_t (&r)[32], int row, in
   }
 }
 
-template <typename OutT, int BN, int STAGES>
+// Fused-MoE epilogue of 32 accumulator columns of one sorted slot, in the order of the reference kernel
+// (flashnn/triton_kernels/fused_moe_a8w8.py:155-170): acc * alpha_row, * alpha_col, * routing weight, cast.
+template <typename OutT>
+__device__ __forceinline__ void store_chunk_moe(const uint32_t (&r)[32], int64_t out_row, int col0, float rs, float rw,
+                                                bool mul_w, const float* cs, const A8W8Params& p, bool vec_ok) {
+  if (col0 >= p.N) return;
+  float v[32];
+#pragma unroll
+  for (int j = 0; j < 32; ++j) {
+    float t = __fmul_rn(__fmul_rn(float(int32_t(r[j])), rs), cs[j]);
+    if (mul_w) t = __fmul_rn(t, rw);
+    v[j] = t;
+  }
+  OutT* orow = reinterpret_cast<OutT*>(p.out) + out_row * p.ldo + col0;
+  if (col0 + 32 <= p.N && vec_ok) {
+#pragma unroll
+    for (int j = 0; j < 32; j += 8)
+      *reinterpret_cast<uint4*>(orow + j) =
+          make_uint4(pack2<OutT>(v[j], v[j + 1]), pack2<OutT>(v[j + 2], v[j + 3]),
+                     pack2<OutT>(v[j + 4], v[j + 5]), pack2<OutT>(v[j + 6], v[j + 7]));
+  } else {
+#pragma unroll
+    for (int j = 0; j < 32; ++j)
+      if (col0 + j < p.N) orow[j] = from_f32<OutT>(v[j]);
+  }
+}
+
+template <typename OutT, int BN, int STAGES, bool MOE>
 __global__ void __launch_bounds__(kThreads, 1)
 a8w8_umma_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ CUtensorMap tmap_b,
                  const A8W8Params p) {
@@ -130,6 +165,9 @@ a8w8_umma_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_consta
   const int lane = threadIdx.x & 31;
   const int num_tiles = p.tiles_m * p.tiles_n;
   constexpr uint32_t kTmemCols = 2 * BN;
+  // fused MoE: row tiles past the slots in use are skipped by every role alike
+  const int rows_in_use = MOE ? __ldg(p.num_post_padded) : 0;
+  const int tile_rows = MOE ? p.tile_rows : kBM;
 
   if (threadIdx.x == 0) {
     *abort_flag = 0;
@@ -165,6 +203,9 @@ a8w8_umma_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_consta
     for (int t = blockIdx.x; t < num_tiles && ok; t += gridDim.x) {
       int mb, nb;
       tile_coords(t, p.tiles_m, p.tiles_n, mb, nb);
+      if (MOE && mb * tile_rows >= rows_in_use) continue;
+      // fused MoE: the tile's weights are rows [e * N + nb * BN, ...) of the expert stack
+      const int b_row = nb * BN + (MOE ? __ldg(p.expert_ids + (mb * tile_rows) / p.block_m) * p.N : 0);
       for (int kb = 0; kb < p.k_blocks; ++kb) {
         ok = mbar_wait_bounded(&empty_bar[stage], phase ^ 1, abort_flag);
         ok = __all_sync(0xffffffffu, ok);
@@ -175,8 +216,8 @@ a8w8_umma_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_consta
         if (leader) {
           uint8_t* sa = smem + stage * L::kStageBytes;
           mbar_expect_tx(&full_bar[stage], L::kStageBytes);
-          tma_load_2d(sa, &tmap_a, &full_bar[stage], kb * kBK, mb * kBM);
-          tma_load_2d(sa + L::kABytes, &tmap_b, &full_bar[stage], kb * kBK, nb * BN);
+          tma_load_2d(sa, &tmap_a, &full_bar[stage], kb * kBK, mb * tile_rows);
+          tma_load_2d(sa + L::kABytes, &tmap_b, &full_bar[stage], kb * kBK, b_row);
           ++issued;
         }
         __syncwarp();
@@ -203,9 +244,15 @@ a8w8_umma_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_consta
     int local = 0;
     bool ok = true;
     bool issued_any = false;
-    for (int t = blockIdx.x; t < num_tiles && ok; t += gridDim.x, ++local) {
+    for (int t = blockIdx.x; t < num_tiles && ok; t += gridDim.x) {
+      if (MOE) {
+        int mb, nb;
+        tile_coords(t, p.tiles_m, p.tiles_n, mb, nb);
+        if (mb * tile_rows >= rows_in_use) continue;
+      }
       const int buf = local & 1;
       const uint32_t acc_phase = (local >> 1) & 1;
+      ++local;
       ok = mbar_wait_bounded(&tmem_empty_bar[buf], acc_phase ^ 1, abort_flag);
       ok = __all_sync(0xffffffffu, ok);
       if (!ok) {
@@ -253,17 +300,33 @@ a8w8_umma_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_consta
     const bool acc_vec_ok = p.acc_out && (p.ldacc % 4 == 0) && (reinterpret_cast<uintptr_t>(p.acc_out) % 16 == 0);
     int local = 0;
     bool ok = true;
-    for (int t = blockIdx.x; t < num_tiles && ok; t += gridDim.x, ++local) {
+    for (int t = blockIdx.x; t < num_tiles && ok; t += gridDim.x) {
       int mb, nb;
       tile_coords(t, p.tiles_m, p.tiles_n, mb, nb);
+      if (MOE && mb * tile_rows >= rows_in_use) continue;
       const int buf = local & 1;
       const uint32_t acc_phase = (local >> 1) & 1;
-      const int row = mb * kBM + quarter * 32 + lane;
+      ++local;
+      const int row = mb * tile_rows + quarter * 32 + lane;
       const int n0 = nb * BN;
       // column scales of this tile -> this warp's smem copy (fp32); row scale -> register
+      const int64_t col_base = MOE ? int64_t(__ldg(p.expert_ids + (mb * tile_rows) / p.block_m)) * p.col_stride_e : 0;
       for (int j = lane; j < BN; j += 32)
-        cs[j] = (n0 + j < p.N) ? load_as_f32(p.alpha_col, p.col_dtype, n0 + j) : 0.f;
-      const float rs = (row < p.M) ? load_as_f32(p.alpha_row, p.row_dtype, row) : 0.f;
+        cs[j] = (n0 + j < p.N) ? load_as_f32(p.alpha_col, p.col_dtype, col_base + n0 + j) : 0.f;
+      float rs = 0.f, rw = 1.f;
+      int64_t out_row = -1;  // fused MoE: the flat (token, choice) index this slot writes, or -1
+      if (MOE) {
+        if (quarter * 32 + lane < tile_rows) {
+          const int flat = __ldg(p.sorted_ids + row);
+          if (flat >= 0 && flat < p.num_valid) {
+            out_row = flat;
+            rs = load_as_f32(p.alpha_row, p.row_dtype, flat / p.top_k);
+            if (p.mul_w) rw = load_as_f32(p.topk_w, p.topk_w_dtype, flat);
+          }
+        }
+      } else {
+        rs = (row < p.M) ? load_as_f32(p.alpha_row, p.row_dtype, row) : 0.f;
+      }
       __syncwarp();
 
       ok = mbar_wait_bounded(&tmem_full_bar[buf], acc_phase, abort_flag);
@@ -279,7 +342,11 @@ a8w8_umma_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_consta
         uint32_t r[32];
         tmem_ld_32x32(taddr + c * 32, r);
         tc_wait_ld();
-        store_chunk<OutT>(r, row, n0 + c * 32, rs, cs + c * 32, same16, p, vec_ok, acc_vec_ok);
+        if (MOE) {
+          if (out_row >= 0) store_chunk_moe<OutT>(r, out_row, n0 + c * 32, rs, rw, p.mul_w != 0, cs + c * 32, p, vec_ok);
+        } else {
+          store_chunk<OutT>(r, row, n0 + c * 32, rs, cs + c * 32, same16, p, vec_ok, acc_vec_ok);
+        }
       }
       tc_fence_before();
       __syncwarp();
@@ -546,7 +613,7 @@ template <typename OutT, int BN, int STAGES>
 int launch_umma(const int8_t* a, int64_t lda, const int8_t* b, int64_t ldb, A8W8Params p, cudaStream_t st) {
   using L = SmemLayout<BN, STAGES>;
   static_assert(L::kDynamicBytes <= 227 * 1024, "shared memory budget");
-  auto kern = a8w8_umma_kernel<OutT, BN, STAGES>;
+  auto kern = a8w8_umma_kernel<OutT, BN, STAGES, false>;
   static std::once_flag once[64];
   int dev = 0;
   cudaGetDevice(&dev);
@@ -611,8 +678,111 @@ int dispatch(const int8_t* a, int64_t lda, const int8_t* b, int64_t ldb, const A
   return launch_umma<OutT, 64, 8>(a, lda, b, ldb, p, st);
 }
 
+// ---------------------------------------------------------------------------
+// fused MoE (expert-sorted grouped GEMM)
+// ---------------------------------------------------------------------------
+// Copies token rows into expert-sorted order: slot s gets row sorted_ids[s] / top_k of A, padding slots get zeros.
+// One warp per slot, 16 bytes per lane and step (K % 16 == 0).
+__global__ void moe_gather_rows_kernel(const int8_t* __restrict__ a, int64_t lda, const int32_t* __restrict__ sorted_ids,
+                                       const int32_t* __restrict__ num_post_padded, int num_valid, int top_k,
+                                       int8_t* __restrict__ a_sorted, int K, int EM) {
+  const int slot = blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5);
+  if (slot >= EM || slot >= __ldg(num_post_padded)) return;
+  const int lane = threadIdx.x & 31;
+  const int flat = __ldg(sorted_ids + slot);
+  const bool valid = flat >= 0 && flat < num_valid;
+  const uint4* src = reinterpret_cast<const uint4*>(a + int64_t(valid ? flat / top_k : 0) * lda);
+  uint4* dst = reinterpret_cast<uint4*>(a_sorted + int64_t(slot) * K);
+  for (int i = lane; i < K / 16; i += 32) dst[i] = valid ? __ldg(src + i) : make_uint4(0, 0, 0, 0);
+}
+
+template <typename OutT, int BN, int STAGES>
+int launch_moe(const int8_t* a_sorted, int64_t EM, const int8_t* b, int64_t E, A8W8Params p, cudaStream_t st) {
+  using L = SmemLayout<BN, STAGES>;
+  auto kern = a8w8_umma_kernel<OutT, BN, STAGES, true>;
+  static std::once_flag once[64];
+  int dev = 0;
+  cudaGetDevice(&dev);
+  cudaError_t attr_err = cudaSuccess;
+  std::call_once(once[dev & 63], [&] {
+    attr_err = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, L::kDynamicBytes);
+  });
+  if (attr_err != cudaSuccess) return check_cuda(attr_err, "cudaFuncSetAttribute(fused moe a8w8)");
+  CUtensorMap ta, tb;
+  if (int e = make_tmap_i8(&ta, a_sorted, EM, p.K, p.K, kBM)) return e;
+  if (int e = make_tmap_i8(&tb, b, E * p.N, p.K, p.K, BN)) return e;
+  p.tiles_m = int(EM / p.tile_rows);
+  p.tiles_n = (p.N + BN - 1) / BN;
+  p.k_blocks = (p.K + kBK - 1) / kBK;
+  const int tiles = p.tiles_m * p.tiles_n;
+  const int grid = tiles < sm_count() ? tiles : sm_count();
+  kern<<<grid, kThreads, L::kDynamicBytes, st>>>(ta, tb, p);
+  return check_cuda(cudaGetLastError(), "fused moe a8w8 launch");
+}
+
+template <typename OutT>
+int dispatch_moe(const int8_t* a_sorted, int64_t EM, const int8_t* b, int64_t E, const A8W8Params& p, cudaStream_t st) {
+  // the widest tile that still gives every SM work; small problems stream the expert weights with 64-wide tiles
+  const int sms = sm_count();
+  const int64_t tiles_m = EM / p.tile_rows;
+  if (tiles_m * ((p.N + 255) / 256) >= sms) return launch_moe<OutT, 256, 4>(a_sorted, EM, b, E, p, st);
+  if (tiles_m * ((p.N + 127) / 128) >= sms) return launch_moe<OutT, 128, 6>(a_sorted, EM, b, E, p, st);
+  return launch_moe<OutT, 64, 8>(a_sorted, EM, b, E, p, st);
+}
+
 }  // namespace
 }  // namespace fnn
+
+extern "C" size_t fnn_fused_moe_a8w8_workspace_bytes(int64_t EM, int64_t K) {
+  if (EM <= 0 || K <= 0) return 0;
+  return (size_t(EM) * size_t(K) + 255) / 256 * 256;  // the expert-sorted copy of the token rows
+}
+
+extern "C" int fnn_fused_moe_a8w8(const int8_t* a, int64_t lda, const int8_t* b, int64_t E, int64_t N, int64_t K,
+                                  const void* alpha_row, int row_dtype, const void* alpha_col, int col_dtype,
+                                  const void* topk_weights, int topk_dtype, const int32_t* sorted_token_ids, int64_t EM,
+                                  const int32_t* expert_ids, const int32_t* num_tokens_post_padded,
+                                  int64_t num_valid_tokens, int top_k, int block_m, int mul_routed_weight, void* out,
+                                  int out_dtype, int64_t ldo, void* workspace, size_t workspace_bytes, void* stream) {
+  using namespace fnn;
+  if (E <= 0 || N < 0 || K <= 0 || EM < 0 || lda < K || ldo < N || num_valid_tokens < 0 || top_k <= 0 || block_m <= 0)
+    return fail(FNN_ERR_SHAPE, "fused_moe_a8w8: E=%lld N=%lld K=%lld EM=%lld lda=%lld ldo=%lld top_k=%d block_m=%d", (long long)E,
+                (long long)N, (long long)K, (long long)EM, (long long)lda, (long long)ldo, top_k, block_m);
+  if (E * N > INT32_MAX || K > INT32_MAX || EM > INT32_MAX || num_valid_tokens > INT32_MAX)
+    return fail(FNN_ERR_SHAPE, "fused_moe_a8w8: sizes must be below 2^31");
+  if (EM % block_m != 0) return fail(FNN_ERR_SHAPE, "fused_moe_a8w8: %lld sorted slots are not a multiple of block_m=%d", (long long)EM, block_m);
+  if (block_m > kBM && block_m % kBM != 0)
+    return fail(FNN_ERR_UNSUPPORTED, "fused_moe_a8w8: block_m must be at most %d or a multiple of it (got %d)", kBM, block_m);
+  if (out_dtype != FNN_F16 && out_dtype != FNN_BF16) return fail(FNN_ERR_DTYPE, "fused_moe_a8w8: output must be f16 or bf16");
+  if (row_dtype < FNN_F16 || row_dtype > FNN_F32 || col_dtype < FNN_F16 || col_dtype > FNN_F32)
+    return fail(FNN_ERR_DTYPE, "fused_moe_a8w8: scales must be f16, bf16 or f32");
+  if (mul_routed_weight && (topk_dtype < FNN_F16 || topk_dtype > FNN_F32)) return fail(FNN_ERR_DTYPE, "fused_moe_a8w8: routing weights must be f16, bf16 or f32");
+  if (EM == 0 || N == 0 || num_valid_tokens == 0) return FNN_OK;
+  if (!a || !b || !alpha_row || !alpha_col || !sorted_token_ids || !expert_ids || !num_tokens_post_padded || !out ||
+      (mul_routed_weight && !topk_weights))
+    return fail(FNN_ERR_NULL_POINTER, "fused_moe_a8w8: null tensor pointer");
+  if (K % 16 != 0 || reinterpret_cast<uintptr_t>(a) % 16 != 0 || lda % 16 != 0 || reinterpret_cast<uintptr_t>(b) % 16 != 0)
+    return fail(FNN_ERR_ALIGNMENT, "fused_moe_a8w8: K and lda must be multiples of 16 and the operands 16-byte aligned");
+  const size_t need = fnn_fused_moe_a8w8_workspace_bytes(EM, K);
+  if (!workspace || workspace_bytes < need) return fail(FNN_ERR_WORKSPACE, "fused_moe_a8w8: needs %zu bytes of workspace, got %zu", need, workspace_bytes);
+  if (reinterpret_cast<uintptr_t>(workspace) % 256 != 0) return fail(FNN_ERR_ALIGNMENT, "fused_moe_a8w8: workspace must be 256-byte aligned");
+  cudaStream_t st = static_cast<cudaStream_t>(stream);
+  int8_t* a_sorted = static_cast<int8_t*>(workspace);
+  moe_gather_rows_kernel<<<unsigned((EM + 7) / 8), 256, 0, st>>>(a, lda, sorted_token_ids, num_tokens_post_padded,
+                                                                 int(num_valid_tokens), top_k, a_sorted, int(K), int(EM));
+  if (int e = check_cuda(cudaGetLastError(), "fused moe gather launch")) return e;
+  A8W8Params p{};
+  p.alpha_row = alpha_row; p.alpha_col = alpha_col; p.out = out; p.acc_out = nullptr;
+  p.ldo = ldo; p.ldacc = 0; p.row_dtype = row_dtype; p.col_dtype = col_dtype;
+  p.M = int(num_valid_tokens); p.N = int(N); p.K = int(K);
+  p.status = device_status_word();
+  p.sorted_ids = sorted_token_ids; p.expert_ids = expert_ids; p.num_post_padded = num_tokens_post_padded;
+  p.topk_w = topk_weights; p.topk_w_dtype = topk_dtype; p.top_k = top_k; p.block_m = block_m;
+  p.tile_rows = block_m < kBM ? block_m : kBM; p.num_valid = int(num_valid_tokens); p.mul_w = mul_routed_weight ? 1 : 0;
+  p.col_stride_e = N;
+  if (out_dtype == FNN_F16) return dispatch_moe<__half>(a_sorted, EM, b, E, p, st);
+  return dispatch_moe<__nv_bfloat16>(a_sorted, EM, b, E, p, st);
+}
 
 extern "C" size_t fnn_gemm_a8w8_workspace_bytes(int64_t, int64_t, int64_t) { return 0; }
 

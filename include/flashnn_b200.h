@@ -130,6 +130,35 @@ int fnn_gemm_a8w8(const int8_t* a, int64_t lda, const int8_t* b, int64_t ldb,
 size_t fnn_gemm_a8w8_workspace_bytes(int64_t M, int64_t N, int64_t K);
 
 /*
+ * Fused mixture-of-experts A8W8 GEMM over expert-sorted token slots.
+ * Replaces `fused_moe_a8w8_forward(A, B, C, alpha_row, alpha_col, topk_weights, topk_ids, sorted_token_ids, expert_ids,
+ * num_tokens_post_padded, mul_routed_weight, top_k, BM)` (flashnn/triton_kernels/fused_moe_a8w8.py:176-290; arithmetic
+ * of the kernel at :96-170).  For every slot s < *num_tokens_post_padded whose flat index f = sorted_token_ids[s] is
+ * below num_valid_tokens, with e = expert_ids[s / block_m]:
+ *     out[f, n] = cast( ((float(sum_k a[f / top_k, k] * b[e, n, k]) * alpha_row[f / top_k]) * alpha_col[e, n])
+ *                        * (mul_routed_weight ? topk_weights[f] : 1) )
+ * Rows of `out` that no slot names are left untouched.  The accumulator is exact int32.
+ *
+ *   a                 [M, K] int8, lda (a multiple of 16); K a multiple of 16
+ *   b                 [E, N, K] int8, contiguous
+ *   alpha_row         [M] row_dtype;  alpha_col [E, N] contiguous, col_dtype;  topk_weights [M * top_k] topk_dtype
+ *   sorted_token_ids  [EM] int32: flat (token * top_k + choice) indices grouped by expert, every expert's group padded
+ *                     to a multiple of block_m with values >= num_valid_tokens
+ *   expert_ids        [EM / block_m] int32;  num_tokens_post_padded [1] int32 (device memory)
+ *   out               [M * top_k, N] f16 or bf16, ldo
+ *   block_m           at most 128, or a multiple of 128
+ *   workspace         fnn_fused_moe_a8w8_workspace_bytes(EM, K) bytes, 256-byte aligned (the expert-sorted copy of
+ *                     the token rows)
+ */
+int fnn_fused_moe_a8w8(const int8_t* a, int64_t lda, const int8_t* b, int64_t E, int64_t N, int64_t K,
+                       const void* alpha_row, int row_dtype, const void* alpha_col, int col_dtype,
+                       const void* topk_weights, int topk_dtype, const int32_t* sorted_token_ids, int64_t EM,
+                       const int32_t* expert_ids, const int32_t* num_tokens_post_padded, int64_t num_valid_tokens,
+                       int top_k, int block_m, int mul_routed_weight, void* out, int out_dtype, int64_t ldo,
+                       void* workspace, size_t workspace_bytes, void* stream);
+size_t fnn_fused_moe_a8w8_workspace_bytes(int64_t EM, int64_t K);
+
+/*
  * Weight-only GEMM / GEMV:  out = act . dequant(W)^T (+ bias), W int8 or packed int4.
  * Replaces `triton_gemm_a16w8_forward` (flashnn/triton_kernels/gemm_a16w8.py:275-338)
  * and `triton_gemm_a16w4_forward` (flashnn/triton_kernels/gemm_a16w4.py:336-406).

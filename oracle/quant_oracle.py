@@ -22,6 +22,10 @@ project):
 * `gemm_weight_only_fp32`       same contraction with no 16-bit rounding of w*s
 * `rms_norm_dquant`             flashnn/norm.py:39-63
 * `layer_norm_dquant`           flashnn/norm.py:94-124
+* `fused_moe_a8w8`              flashnn/triton_kernels/fused_moe_a8w8.py:96-170 -- PARITY UNPINNED for this one
+                                function: the reference has neither a torch implementation nor a test of the fused
+                                MoE kernels, so this restates the Triton kernel's arithmetic from its source and is
+                                cross-checked only against a token-by-token formulation (tests/test_moe_oracle.py)
 """
 from __future__ import annotations
 
@@ -218,3 +222,34 @@ def layer_norm_dquant(x: torch.Tensor, weight: torch.Tensor, bias: torch.Tensor,
     scale = n.abs().max(dim=-1, keepdim=True)[0] / 127.0
     q = torch.clamp(torch.round(n / scale), -128.0, 127.0)
     return q.to(torch.int8), scale.reshape(-1, 1)
+
+
+# ----------------------------------------------------------------------------
+# Fused MoE A8W8 (parity unpinned, see the header)
+# ----------------------------------------------------------------------------
+def fused_moe_a8w8(A, B, alpha_row, alpha_col, topk_weights, sorted_token_ids, expert_ids, num_tokens_post_padded,
+                   num_valid_tokens, mul_routed_weight, top_k, BM, out_ty=torch.float16, C=None):
+    """Block by block as the kernel walks the expert-sorted slots: exact int32 accumulator, then
+    acc * alpha_row * alpha_col (* routing weight) in fp32, in that order, cast to `out_ty`, scattered to the flat
+    (token, choice) rows of C [M, top_k, N].  Rows that no slot names keep what C held (zeros if C is None)."""
+    E, N, K = B.shape
+    M = A.shape[0]
+    if C is None:
+        C = torch.zeros(M, top_k, N, dtype=out_ty)
+    flat_out = C.view(M * top_k, N)
+    padded = int(num_tokens_post_padded.reshape(-1)[0])
+    tw = topk_weights.reshape(-1)
+    for blk in range(padded // BM):
+        e = int(expert_ids[blk])
+        slots = sorted_token_ids[blk * BM:(blk + 1) * BM].long()
+        flat = slots[slots < num_valid_tokens]
+        if flat.numel() == 0:
+            continue
+        rows = flat // top_k
+        acc = gemm_a8w8_acc_i32(A[rows], B[e])
+        v = acc.float() * alpha_row.reshape(-1)[rows].float()[:, None]
+        v = v * alpha_col[e].float()[None, :]
+        if mul_routed_weight:
+            v = v * tw[flat].float()[:, None]
+        flat_out[flat] = v.to(C.dtype)
+    return C
