@@ -10,11 +10,11 @@
 // with IEEE division in fp32 followed by one rounding to T, exactly what the CPU
 // computes for 16-bit tensors.  The int8 cast saturates.
 //
-// The per-element division is replaced by a multiplication with 1/s plus a check:
-// x * (1/s) is within 2 ulp of the true quotient, so rounding it to T gives the
-// same value unless it lies within a few ulp of a midpoint between two T values;
-// only those rare elements take the exact division.  rint and the int8 cast are
-// one magic-number addition (no conversion instructions).
+// The per-element division is replaced by two multiplications with a bracketed
+// reciprocal (quantise.cuh): where both products round to the same T value the exact
+// quotient does too; only the rare elements next to a rounding midpoint of T take the
+// exact division.  rint and the int8 cast are one magic-number addition (no conversion
+// instructions).
 #include "common.cuh"
 #include "quantise.cuh"
 
@@ -80,6 +80,7 @@ dq_row_vec_kernel(const T* __restrict__ x, int64_t ldx, int8_t* __restrict__ q, 
     return;
   }
   const float inv_s = __frcp_rn(s);
+  const InvBracket inv2 = inv_bracket(s);
 #pragma unroll
   for (int c = 0; c < NCHUNK; ++c) {
     const int i = c * blockDim.x + threadIdx.x;
@@ -89,8 +90,8 @@ dq_row_vec_kernel(const T* __restrict__ x, int64_t ldx, int8_t* __restrict__ q, 
       uint32_t amb = 0;
 #pragma unroll
       for (int h = 0; h < 2; ++h)  // [q0,q1,..] and [q2,q3,..] -> [q0,q1,q2,q3]
-        o[h] = __byte_perm(quantise_pair<T>(w[2 * h], inv_s, amb), quantise_pair<T>(w[2 * h + 1], inv_s, amb), 0x5410);
-      if (static_cast<int32_t>(amb) < 0) {
+        o[h] = __byte_perm(quantise_pair<T>(w[2 * h], inv2, amb), quantise_pair<T>(w[2 * h + 1], inv2, amb), 0x5410);
+      if (amb != 0) {
         // some element of this chunk sits next to a rounding midpoint: redo the chunk element by element
 #pragma unroll
         for (int h = 0; h < 2; ++h) {

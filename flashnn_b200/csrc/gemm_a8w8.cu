@@ -37,6 +37,7 @@ struct A8W8Params {
   int row_dtype, col_dtype;
   int M, N, K;
   int tiles_m, tiles_n, k_blocks;
+  int a_tile_bytes;  // single-CTA kernel: bytes the A copy of one stage brings (fewer than 128 rows when M is small)
   int* status;  // device status word
   // Fused-MoE mode (kernel template flag MOE): A is the expert-sorted copy of the token rows [EM, K], B is the
   // stack of expert weights seen as [E * N, K]; a tile is `tile_rows` sorted slots of one expert x BN channels.
@@ -215,7 +216,7 @@ a8w8_umma_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_consta
         }
         if (leader) {
           uint8_t* sa = smem + stage * L::kStageBytes;
-          mbar_expect_tx(&full_bar[stage], L::kStageBytes);
+          mbar_expect_tx(&full_bar[stage], p.a_tile_bytes + L::kBBytes);
           tma_load_2d(sa, &tmap_a, &full_bar[stage], kb * kBK, mb * tile_rows);
           tma_load_2d(sa + L::kABytes, &tmap_b, &full_bar[stage], kb * kBK, b_row);
           ++issued;
@@ -622,8 +623,12 @@ int launch_umma(const int8_t* a, int64_t lda, const int8_t* b, int64_t ldb, A8W8
     attr_err = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, L::kDynamicBytes);
   });
   if (attr_err != cudaSuccess) return check_cuda(attr_err, "cudaFuncSetAttribute(a8w8)");
+  // Decode shapes are bound by the weight stream: the A copy brings only the rows that exist (in whole swizzle
+  // atoms of 8 rows); the tensor core still reads 128 rows, and the accumulator rows behind M are never stored.
+  const int a_rows = p.M < kBM ? (p.M + 7) / 8 * 8 : kBM;
+  p.a_tile_bytes = a_rows * kBK;
   CUtensorMap ta, tb;
-  if (int e = make_tmap_i8(&ta, a, p.M, p.K, lda, kBM)) return e;
+  if (int e = make_tmap_i8(&ta, a, p.M, p.K, lda, a_rows)) return e;
   if (int e = make_tmap_i8(&tb, b, p.N, p.K, ldb, BN)) return e;
   p.tiles_m = (p.M + kBM - 1) / kBM;
   p.tiles_n = (p.N + BN - 1) / BN;
@@ -708,8 +713,10 @@ int launch_moe(const int8_t* a_sorted, int64_t EM, const int8_t* b, int64_t E, A
     attr_err = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, L::kDynamicBytes);
   });
   if (attr_err != cudaSuccess) return check_cuda(attr_err, "cudaFuncSetAttribute(fused moe a8w8)");
+  const int a_rows = (p.tile_rows + 7) / 8 * 8;  // only the block's own slots are copied
+  p.a_tile_bytes = a_rows * kBK;
   CUtensorMap ta, tb;
-  if (int e = make_tmap_i8(&ta, a_sorted, EM, p.K, p.K, kBM)) return e;
+  if (int e = make_tmap_i8(&ta, a_sorted, EM, p.K, p.K, a_rows)) return e;
   if (int e = make_tmap_i8(&tb, b, E * p.N, p.K, p.K, BN)) return e;
   p.tiles_m = int(EM / p.tile_rows);
   p.tiles_n = (p.N + BN - 1) / BN;

@@ -24,6 +24,7 @@
 // workers' totals of a row group in a fixed order and writes the outputs; the workers hand their totals over
 // through a double-buffered array and two pairs of named barriers and never wait for each other.
 // A non-finite activation makes the whole output row NaN.
+#include "async_copy.cuh"
 #include "common.cuh"
 #include "weight_only.cuh"
 
@@ -41,17 +42,6 @@ constexpr int kImmaPlanePad = 64;     // plane pitch = K + 64 bytes: the eight p
 constexpr int kImmaMaxTokens = 5;     // 3 planes per token, 16 MMA columns
 constexpr int kImmaSmemCap = 226 * 1024;  // dynamic shared memory a CTA may ask for
 
-__device__ __forceinline__ void cp_async16(uint32_t smem_dst, const void* gsrc) {
-  asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"(smem_dst), "l"(gsrc) : "memory");
-}
-__device__ __forceinline__ void cp_async4(uint32_t smem_dst, const void* gsrc) {
-  asm volatile("cp.async.ca.shared.global [%0], [%1], 4;" ::"r"(smem_dst), "l"(gsrc) : "memory");
-}
-__device__ __forceinline__ uint32_t lds32(uint32_t addr) {
-  uint32_t v;
-  asm volatile("ld.shared.u32 %0, [%1];" : "=r"(v) : "r"(addr));
-  return v;
-}
 __device__ __forceinline__ uint32_t prmt(uint32_t a, uint32_t b, uint32_t sel) {
   uint32_t r;
   asm("prmt.b32 %0, %1, %2, %3;" : "=r"(r) : "r"(a), "r"(b), "r"(sel));
@@ -65,15 +55,6 @@ __device__ __forceinline__ void lds128_if(uint4& v, uint32_t addr, uint32_t on) 
 // named CTA barriers over all 544 threads (ids 1..4; __syncthreads owns id 0)
 __device__ __forceinline__ void named_barrier_sync(int id) { asm volatile("bar.sync %0, %1;" ::"r"(id), "n"(544) : "memory"); }
 __device__ __forceinline__ void named_barrier_arrive(int id) { asm volatile("bar.arrive %0, %1;" ::"r"(id), "n"(544) : "memory"); }
-__device__ __forceinline__ void cp_async_commit() { asm volatile("cp.async.commit_group;" ::: "memory"); }
-template <int N> __device__ __forceinline__ void cp_async_wait() {
-  asm volatile("cp.async.wait_group %0;" ::"n"(N) : "memory");
-}
-__device__ __forceinline__ uint4 lds128(uint32_t addr) {
-  uint4 v;
-  asm volatile("ld.shared.v4.u32 {%0, %1, %2, %3}, [%4];" : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w) : "r"(addr));
-  return v;
-}
 // d += a (16 x 32 int8, row major) * b (32 x 8 int8, column major)
 __device__ __forceinline__ void imma(int (&d)[4], uint32_t a0, uint32_t a1, uint32_t a2, uint32_t a3, uint32_t b0, uint32_t b1) {
   asm volatile("mma.sync.aligned.m16n8k32.row.col.s32.s8.s8.s32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};"

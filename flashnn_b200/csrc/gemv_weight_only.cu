@@ -20,6 +20,7 @@
 // accumulator layout by a second MMA against an all-ones operand.
 #include <type_traits>
 
+#include "async_copy.cuh"
 #include "common.cuh"
 #include "weight_only.cuh"
 
@@ -144,18 +145,6 @@ template <int BITS> struct GemvSmem {
   static constexpr int kBytes = kGemvWarps * kWarpBytes;
 };
 
-__device__ __forceinline__ void cp_async16(uint32_t smem_dst, const void* gsrc) {
-  asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"(smem_dst), "l"(gsrc) : "memory");
-}
-__device__ __forceinline__ void cp_async_commit() { asm volatile("cp.async.commit_group;" ::: "memory"); }
-template <int N> __device__ __forceinline__ void cp_async_wait() {
-  asm volatile("cp.async.wait_group %0;" ::"n"(N) : "memory");
-}
-__device__ __forceinline__ uint4 lds128(uint32_t addr) {
-  uint4 v;
-  asm volatile("ld.shared.v4.u32 {%0, %1, %2, %3}, [%4];" : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w) : "r"(addr));
-  return v;
-}
 
 // One CTA per row group (16 output channels); its 8 warps split K into equal slices.  Every lane
 // streams exactly the weight bytes its own MMA fragments need: 16 bytes per step (64 k) of one

@@ -149,20 +149,20 @@ norm_dquant_kernel(const NdParams p) {
     const float s = round_to<T>(__fdiv_rn(amax, 127.0f));
     if (threadIdx.x == 0) reinterpret_cast<T*>(p.scale)[row] = from_f32<T>(s);
     const bool plain = !(s > 0.f);  // constant row and zero bias: 0 / 0, which the cast turns into 0
-    const float inv_s = __frcp_rn(s);
+    const InvBracket inv2 = inv_bracket(s);
 #pragma unroll
     for (int c = 0; c < NCHUNK; ++c) {
       const int i = c * blockDim.x + threadIdx.x;
       if (i < nvec) {
         const uint32_t w[4] = {y[c].x, y[c].y, y[c].z, y[c].w};
         uint32_t o[2];
-        uint32_t amb = plain ? 0x80000000u : 0u;
+        uint32_t amb = plain ? 1u : 0u;
         if (!plain) {
 #pragma unroll
           for (int h = 0; h < 2; ++h)
-            o[h] = __byte_perm(quantise_pair<T>(w[2 * h], inv_s, amb), quantise_pair<T>(w[2 * h + 1], inv_s, amb), 0x5410);
+            o[h] = __byte_perm(quantise_pair<T>(w[2 * h], inv2, amb), quantise_pair<T>(w[2 * h + 1], inv2, amb), 0x5410);
         }
-        if (static_cast<int32_t>(amb) < 0) {
+        if (amb != 0) {
 #pragma unroll
           for (int h = 0; h < 2; ++h) {
             const int q0 = quantise_one<T>(lo_of<T>(w[2 * h]), s), q1 = quantise_one<T>(hi_of<T>(w[2 * h]), s);

@@ -1,10 +1,10 @@
 // Device helpers shared by the kernels that quantise a row to int8 in the arithmetic of a 16-bit dtype T
 // (per-token dynamic quantisation and the layer-norm producer): q = rint(T(x / s)) with the int8 cast saturating.
 //
-// The per-element division is replaced by a multiplication with 1/s plus a check: x * (1/s) is within 2 ulp of
-// the true quotient, so rounding it to T gives the same value unless it lies within a few ulp of a midpoint
-// between two T values; only those rare elements take the exact division.  rint and the int8 cast are one
-// magic-number addition (no conversion instructions).
+// The per-element division is replaced by two multiplications with a reciprocal bracketed from below and above:
+// where both products round to the same T value the exact quotient does too; only the rare elements next to a
+// rounding midpoint of T take the exact division.  rint and the int8 cast are one magic-number addition (no
+// conversion instructions).
 #pragma once
 #include "common.cuh"
 
@@ -34,15 +34,24 @@ template <typename T> struct DropBits;
 template <> struct DropBits<__nv_bfloat16> { static constexpr uint32_t mask = 0xFFFFu, mid = 0x8000u; };
 template <> struct DropBits<__half> { static constexpr uint32_t mask = 0x1FFFu, mid = 0x1000u; };
 
-// Two elements at once: returns the two quantised bytes in bits 0-7 and 8-15, and ORs into `amb` a word whose
-// sign bit is set when either x * (1/s) lies within 3 ulp of a rounding midpoint of T (the caller then redoes
-// the whole chunk with the exact division; that is rare).
-template <typename T> __device__ __forceinline__ uint32_t quantise_pair(uint32_t w, float inv_s, uint32_t& amb) {
-  const float r0 = __fmul_rn(lo_of<T>(w), inv_s), r1 = __fmul_rn(hi_of<T>(w), inv_s);
-  // (dropped bits) - (mid - 3) - 7 wraps below zero exactly when the dropped bits are in [mid-3, mid+3]
-  amb |= ((__float_as_uint(r0) & DropBits<T>::mask) - (DropBits<T>::mid + 4u)) & ~((__float_as_uint(r0) & DropBits<T>::mask) - (DropBits<T>::mid - 3u));
-  amb |= ((__float_as_uint(r1) & DropBits<T>::mask) - (DropBits<T>::mid + 4u)) & ~((__float_as_uint(r1) & DropBits<T>::mask) - (DropBits<T>::mid - 3u));
-  const uint32_t t2 = pack2<T>(r0, r1);  // both rounded to T in one instruction
+// 1/s bracketed from below and above: x * lo and x * hi enclose the true quotient x / s (the reciprocal and the
+// product are each within half an ulp, the factors move it by 8 ulp).
+struct InvBracket {
+  float lo, hi;
+};
+__device__ __forceinline__ InvBracket inv_bracket(float s) {
+  const float inv = __frcp_rn(s);
+  return {__fmul_rn(inv, 0.99999952316284f), __fmul_rn(inv, 1.00000047683716f)};  // 1 -+ 2^-21
+}
+
+// Two elements at once: returns the two quantised bytes in bits 0-7 and 8-15.  Both ends of the bracket are
+// rounded to T (one packed conversion each); rounding is monotonic, so where the two agree the exact quotient rounds
+// to the same T value.  Where they differ a bit is ORed into `amb` and the caller redoes the chunk with the exact
+// division (about one element in 5000).
+template <typename T> __device__ __forceinline__ uint32_t quantise_pair(uint32_t w, const InvBracket& inv, uint32_t& amb) {
+  const float x0 = lo_of<T>(w), x1 = hi_of<T>(w);
+  const uint32_t t2 = pack2<T>(__fmul_rn(x0, inv.lo), __fmul_rn(x1, inv.lo));
+  amb |= t2 ^ pack2<T>(__fmul_rn(x0, inv.hi), __fmul_rn(x1, inv.hi));
   const float t0 = fminf(lo_of<T>(t2), 127.f), t1 = fminf(hi_of<T>(t2), 127.f);
   const uint32_t q0 = __float_as_uint(__fadd_rn(t0, 12582912.f)), q1 = __float_as_uint(__fadd_rn(t1, 12582912.f));
   return __byte_perm(q0, q1, 0x0040);  // low bytes of q0, q1 in bytes 0 and 1
