@@ -37,7 +37,6 @@ struct A8W8Params {
   int row_dtype, col_dtype;
   int M, N, K;
   int tiles_m, tiles_n, k_blocks;
-  int a_tile_bytes;  // single-CTA kernel: bytes the A copy of one stage brings (fewer than 128 rows when M is small)
   int* status;  // device status word
   // Fused-MoE mode (kernel template flag MOE): A is the expert-sorted copy of the token rows [EM, K], B is the
   // stack of expert weights seen as [E * N, K]; a tile is `tile_rows` sorted slots of one expert x BN channels.
@@ -49,11 +48,16 @@ struct A8W8Params {
   int64_t col_stride_e;            // elements between two experts' rows of alpha_col
 };
 
-template <int BN, int STAGES> struct SmemLayout {
-  static constexpr int kABytes = kBM * kBK;
+// AROWS: rows of A one stage holds (16, 32, 64 or 128).  Decode shapes are bound by the weight stream, and what
+// bounds that is the bytes a CTA keeps in flight, so their stages carry only the rows of A that exist and there are
+// more of them.  The tensor core still reads 128 rows from the A base (what lies behind the real rows belongs to the
+// following buffers; the accumulator rows it produces are never stored), so the last stage is followed by padding.
+template <int BN, int STAGES, int AROWS = kBM> struct SmemLayout {
+  static constexpr int kABytes = AROWS * kBK;
   static constexpr int kBBytes = BN * kBK;
   static constexpr int kStageBytes = kABytes + kBBytes;
-  static constexpr int kColScaleOff = STAGES * kStageBytes;         // [4][BN] float
+  static constexpr int kTailPad = (kBM * kBK > kStageBytes) ? kBM * kBK - kStageBytes : 0;
+  static constexpr int kColScaleOff = STAGES * kStageBytes + kTailPad;  // [4][BN] float
   static constexpr int kBarOff = kColScaleOff + 4 * BN * 4;          // barriers
   static constexpr int kNumBars = 2 * STAGES + 4 + 1;                // full, empty, tmem full/empty x2, drain
   static constexpr int kTmemSlotOff = kBarOff + kNumBars * 8;
@@ -145,11 +149,11 @@ __device__ __forceinline__ void store_chunk_moe(const uint32_t (&r)[32], int64_t
   }
 }
 
-template <typename OutT, int BN, int STAGES, bool MOE>
+template <typename OutT, int BN, int STAGES, bool MOE, int AROWS>
 __global__ void __launch_bounds__(kThreads, 1)
 a8w8_umma_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ CUtensorMap tmap_b,
                  const A8W8Params p) {
-  using L = SmemLayout<BN, STAGES>;
+  using L = SmemLayout<BN, STAGES, AROWS>;
   extern __shared__ uint8_t smem_raw[];
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
   float* col_scale_smem = reinterpret_cast<float*>(smem + L::kColScaleOff);
@@ -216,7 +220,7 @@ a8w8_umma_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_consta
         }
         if (leader) {
           uint8_t* sa = smem + stage * L::kStageBytes;
-          mbar_expect_tx(&full_bar[stage], p.a_tile_bytes + L::kBBytes);
+          mbar_expect_tx(&full_bar[stage], L::kStageBytes);
           tma_load_2d(sa, &tmap_a, &full_bar[stage], kb * kBK, mb * tile_rows);
           tma_load_2d(sa + L::kABytes, &tmap_b, &full_bar[stage], kb * kBK, b_row);
           ++issued;
@@ -610,11 +614,12 @@ int make_tmap_i8(CUtensorMap* m, const void* base, int64_t rows, int64_t K, int6
   return make_tmap_2d(m, /*elem_bytes=*/1, base, rows, K, ld, kBK, box_rows, /*swizzle128=*/true);
 }
 
-template <typename OutT, int BN, int STAGES>
+template <typename OutT, int BN, int STAGES, int AROWS>
 int launch_umma(const int8_t* a, int64_t lda, const int8_t* b, int64_t ldb, A8W8Params p, cudaStream_t st) {
-  using L = SmemLayout<BN, STAGES>;
+  using L = SmemLayout<BN, STAGES, AROWS>;
   static_assert(L::kDynamicBytes <= 227 * 1024, "shared memory budget");
-  auto kern = a8w8_umma_kernel<OutT, BN, STAGES, false>;
+  static_assert(L::kStageBytes % 1024 == 0 && L::kABytes % 1024 == 0, "tiles must stay 1024-byte aligned");
+  auto kern = a8w8_umma_kernel<OutT, BN, STAGES, false, AROWS>;
   static std::once_flag once[64];
   int dev = 0;
   cudaGetDevice(&dev);
@@ -623,12 +628,8 @@ int launch_umma(const int8_t* a, int64_t lda, const int8_t* b, int64_t ldb, A8W8
     attr_err = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, L::kDynamicBytes);
   });
   if (attr_err != cudaSuccess) return check_cuda(attr_err, "cudaFuncSetAttribute(a8w8)");
-  // Decode shapes are bound by the weight stream: the A copy brings only the rows that exist (in whole swizzle
-  // atoms of 8 rows); the tensor core still reads 128 rows, and the accumulator rows behind M are never stored.
-  const int a_rows = p.M < kBM ? (p.M + 7) / 8 * 8 : kBM;
-  p.a_tile_bytes = a_rows * kBK;
   CUtensorMap ta, tb;
-  if (int e = make_tmap_i8(&ta, a, p.M, p.K, lda, a_rows)) return e;
+  if (int e = make_tmap_i8(&ta, a, p.M, p.K, lda, AROWS)) return e;
   if (int e = make_tmap_i8(&tb, b, p.N, p.K, ldb, BN)) return e;
   p.tiles_m = (p.M + kBM - 1) / kBM;
   p.tiles_n = (p.N + BN - 1) / BN;
@@ -637,6 +638,15 @@ int launch_umma(const int8_t* a, int64_t lda, const int8_t* b, int64_t ldb, A8W8
   const int grid = tiles < sm_count() ? tiles : sm_count();
   kern<<<grid, kThreads, L::kDynamicBytes, st>>>(ta, tb, p);
   return check_cuda(cudaGetLastError(), "a8w8 tcgen05 launch");
+}
+
+// Tile width BN with the stage count that fills shared memory for the rows of A a stage has to hold.
+template <typename OutT, int BN>
+int launch_umma_rows(const int8_t* a, int64_t lda, const int8_t* b, int64_t ldb, const A8W8Params& p, cudaStream_t st) {
+  constexpr int kBudget = 210 * 1024;
+  if (p.M <= 16) return launch_umma<OutT, BN, kBudget / ((16 + BN) * kBK), 16>(a, lda, b, ldb, p, st);
+  if (p.M <= 64) return launch_umma<OutT, BN, kBudget / ((64 + BN) * kBK), 64>(a, lda, b, ldb, p, st);
+  return launch_umma<OutT, BN, kBudget / ((kBM + BN) * kBK) < 8 ? kBudget / ((kBM + BN) * kBK) : 8, kBM>(a, lda, b, ldb, p, st);
 }
 
 template <typename OutT, int STAGES>
@@ -678,9 +688,9 @@ int dispatch(const int8_t* a, int64_t lda, const int8_t* b, int64_t ldb, const A
   const int sms = sm_count();
   if (p.M > kBM && ((p.M + 255) / 256) * ((p.N + 255) / 256) >= sms / 2) return launch_pair<OutT, 6>(a, lda, b, ldb, p, st);
   const int tiles_m = (p.M + kBM - 1) / kBM;
-  if (tiles_m * ((p.N + 255) / 256) >= sms) return launch_umma<OutT, 256, 4>(a, lda, b, ldb, p, st);
-  if (tiles_m * ((p.N + 127) / 128) >= sms) return launch_umma<OutT, 128, 6>(a, lda, b, ldb, p, st);
-  return launch_umma<OutT, 64, 8>(a, lda, b, ldb, p, st);
+  if (tiles_m * ((p.N + 255) / 256) >= sms) return launch_umma_rows<OutT, 256>(a, lda, b, ldb, p, st);
+  if (tiles_m * ((p.N + 127) / 128) >= sms) return launch_umma_rows<OutT, 128>(a, lda, b, ldb, p, st);
+  return launch_umma_rows<OutT, 64>(a, lda, b, ldb, p, st);
 }
 
 // ---------------------------------------------------------------------------
@@ -701,10 +711,11 @@ __global__ void moe_gather_rows_kernel(const int8_t* __restrict__ a, int64_t lda
   for (int i = lane; i < K / 16; i += 32) dst[i] = valid ? __ldg(src + i) : make_uint4(0, 0, 0, 0);
 }
 
-template <typename OutT, int BN, int STAGES>
+template <typename OutT, int BN, int STAGES, int AROWS>
 int launch_moe(const int8_t* a_sorted, int64_t EM, const int8_t* b, int64_t E, A8W8Params p, cudaStream_t st) {
-  using L = SmemLayout<BN, STAGES>;
-  auto kern = a8w8_umma_kernel<OutT, BN, STAGES, true>;
+  using L = SmemLayout<BN, STAGES, AROWS>;
+  static_assert(L::kDynamicBytes <= 227 * 1024, "shared memory budget");
+  auto kern = a8w8_umma_kernel<OutT, BN, STAGES, true, AROWS>;
   static std::once_flag once[64];
   int dev = 0;
   cudaGetDevice(&dev);
@@ -713,10 +724,8 @@ int launch_moe(const int8_t* a_sorted, int64_t EM, const int8_t* b, int64_t E, A
     attr_err = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, L::kDynamicBytes);
   });
   if (attr_err != cudaSuccess) return check_cuda(attr_err, "cudaFuncSetAttribute(fused moe a8w8)");
-  const int a_rows = (p.tile_rows + 7) / 8 * 8;  // only the block's own slots are copied
-  p.a_tile_bytes = a_rows * kBK;
   CUtensorMap ta, tb;
-  if (int e = make_tmap_i8(&ta, a_sorted, EM, p.K, p.K, a_rows)) return e;
+  if (int e = make_tmap_i8(&ta, a_sorted, EM, p.K, p.K, AROWS)) return e;  // a block's own slots (and a few more)
   if (int e = make_tmap_i8(&tb, b, E * p.N, p.K, p.K, BN)) return e;
   p.tiles_m = int(EM / p.tile_rows);
   p.tiles_n = (p.N + BN - 1) / BN;
@@ -727,14 +736,22 @@ int launch_moe(const int8_t* a_sorted, int64_t EM, const int8_t* b, int64_t E, A
   return check_cuda(cudaGetLastError(), "fused moe a8w8 launch");
 }
 
+template <typename OutT, int BN>
+int launch_moe_rows(const int8_t* a_sorted, int64_t EM, const int8_t* b, int64_t E, const A8W8Params& p, cudaStream_t st) {
+  constexpr int kBudget = 210 * 1024;
+  if (p.tile_rows <= 16) return launch_moe<OutT, BN, kBudget / ((16 + BN) * kBK), 16>(a_sorted, EM, b, E, p, st);
+  if (p.tile_rows <= 64) return launch_moe<OutT, BN, kBudget / ((64 + BN) * kBK), 64>(a_sorted, EM, b, E, p, st);
+  return launch_moe<OutT, BN, kBudget / ((kBM + BN) * kBK) < 8 ? kBudget / ((kBM + BN) * kBK) : 8, kBM>(a_sorted, EM, b, E, p, st);
+}
+
 template <typename OutT>
 int dispatch_moe(const int8_t* a_sorted, int64_t EM, const int8_t* b, int64_t E, const A8W8Params& p, cudaStream_t st) {
   // the widest tile that still gives every SM work; small problems stream the expert weights with 64-wide tiles
   const int sms = sm_count();
   const int64_t tiles_m = EM / p.tile_rows;
-  if (tiles_m * ((p.N + 255) / 256) >= sms) return launch_moe<OutT, 256, 4>(a_sorted, EM, b, E, p, st);
-  if (tiles_m * ((p.N + 127) / 128) >= sms) return launch_moe<OutT, 128, 6>(a_sorted, EM, b, E, p, st);
-  return launch_moe<OutT, 64, 8>(a_sorted, EM, b, E, p, st);
+  if (tiles_m * ((p.N + 255) / 256) >= sms) return launch_moe_rows<OutT, 256>(a_sorted, EM, b, E, p, st);
+  if (tiles_m * ((p.N + 127) / 128) >= sms) return launch_moe_rows<OutT, 128>(a_sorted, EM, b, E, p, st);
+  return launch_moe_rows<OutT, 64>(a_sorted, EM, b, E, p, st);
 }
 
 }  // namespace
