@@ -198,8 +198,8 @@ gemv_w4_imma_kernel(const WoParams p, const int num_rg) {
 #pragma unroll
         for (int j = 0; j < 4; ++j) {
           const float a = lo16<T>(w[j]), b = hi16<T>(w[j]);
-          // NaN-propagating maximum of the magnitudes: a NaN or an infinity must reach the check below
-          amax = (a != a || b != b) ? __int_as_float(0x7fc00000) : fmaxf(amax, fmaxf(fabsf(a), fabsf(b)));
+          // a NaN counts as an infinity, which the maximum keeps: both must reach the check below
+          amax = fmaxf(amax, fmaxf(nan_to_inf(fabsf(a)), nan_to_inf(fabsf(b))));
           sum += a + b;
         }
       };
@@ -213,8 +213,7 @@ gemv_w4_imma_kernel(const WoParams p, const int num_rg) {
       for (int i = kHold * kImmaThreads + threadIdx.x; i < nvec; i += kImmaThreads) scan(__ldg(xr + i));
 #pragma unroll
       for (int o = 16; o > 0; o >>= 1) {
-        const float other = __shfl_xor_sync(0xffffffffu, amax, o);
-        amax = (amax != amax || other != other) ? __int_as_float(0x7fc00000) : fmaxf(amax, other);
+        amax = fmaxf(amax, __shfl_xor_sync(0xffffffffu, amax, o));
         sum += __shfl_xor_sync(0xffffffffu, sum, o);
       }
       if (lane == 0 && worker) { scratch[warp] = amax; scratch[kImmaWarps + warp] = sum; }

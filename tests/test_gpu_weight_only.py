@@ -178,12 +178,13 @@ def test_int4_few_tokens(dt, m, n, k, group, use_bias, use_zp):
         assert torch.equal(out[1].float(), want.to(dt).float())
 
 
-def test_int4_few_tokens_non_finite_row():
+@pytest.mark.parametrize("bad", [float("inf"), float("nan")])
+def test_int4_few_tokens_non_finite_row(bad):
     """A NaN or an infinity in a row makes that whole output row NaN; the other rows are unaffected."""
-    act, qw, scale, bias, zp = make(4, 2, 64, 2048, torch.bfloat16, 128, False, False, seed=3)
+    act, qw, scale, bias, zp = make(4, 2, 64, 4096, torch.bfloat16, 128, False, False, seed=3)
     clean = run(act, qw, scale)
     act2 = act.clone()
-    act2[0, 100] = float("inf")
+    act2[0, 100] = bad
     out = run(act2, qw, scale)
     assert bool(torch.isnan(out[0].float()).all())
     assert torch.equal(out[1].view(torch.int16), clean[1].view(torch.int16))
@@ -259,3 +260,38 @@ def test_prefill_group_wise_full_size():
     ref = O.gemm_weight_only_reference(x[rows], w["qw"], w["scale"], None, None, out_ty=torch.bfloat16).float()
     err = (out[rows].float() - ref).abs()
     assert bool((err <= ATOL + RTOL * ref.abs()).all())
+
+
+# Six to sixteen tokens of packed int4 (the 16-bit-fragment decode kernel): group size 128 and per-channel scales,
+# bias, ragged N, short and long K, outlier-heavy rows, a row of zeros and a tiny row.
+@pytest.mark.parametrize("dt", [torch.bfloat16, torch.float16])
+@pytest.mark.parametrize("m", [6, 9, 13, 16])
+@pytest.mark.parametrize("n,k,group,use_bias", [(272, 1024, 128, True), (64, 128, 128, False), (130, 2048, 0, True),
+                                                (1024, 4096, 128, False), (96, 8192, 0, False), (48, 28672, 128, True)])
+def test_int4_six_to_sixteen_tokens(dt, m, n, k, group, use_bias):
+    act, qw, scale, bias, zp = make(4, m, n, k, dt, group, use_bias, False, seed=m + n + k)
+    g = torch.Generator().manual_seed(k + 1)
+    act = torch.where(torch.rand(m, k, generator=g) < 0.002, act * 30, act)  # outliers
+    act[1] = 0  # a row of zeros gives the bias (or 0)
+    act[2] = act[2] * (1e-3 if dt == torch.float16 else 1e-30)  # a tiny row
+    out = run(act, qw, scale, bias, zp)
+    ref = O.gemm_weight_only_fp32(act, qw, scale, bias, zp)
+    row_scale = ref.abs().amax(dim=1, keepdim=True)
+    err = (out.float() - ref).abs()
+    bound = ATOL + RTOL * ref.abs() + 4e-3 * row_scale * (2.0 ** -8 if dt == torch.bfloat16 else 2.0 ** -11) * 256
+    assert bool((err <= bound).all()), f"max excess {(err - bound).max():.3e}"
+    exact = ref.to(dt)
+    assert int((out != exact).sum()) <= max(3, 0.02 * out.numel())
+    want = torch.zeros(n) if bias is None else bias.float()
+    assert torch.equal(out[1].float(), want.to(dt).float())
+
+
+def test_int4_sixteen_tokens_non_finite_row():
+    act, qw, scale, bias, zp = make(4, 16, 256, 2048, torch.bfloat16, 128, False, False, seed=5)
+    clean = run(act, qw, scale)
+    act2 = act.clone()
+    act2[7, 100] = float("nan")
+    out = run(act2, qw, scale)
+    assert bool(torch.isnan(out[7].float()).all())
+    keep = [i for i in range(16) if i != 7]
+    assert torch.equal(out[keep].view(torch.int16), clean[keep].view(torch.int16))
