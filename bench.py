@@ -184,7 +184,8 @@ def time_rotating_graph(fns, rounds, replays=5):
     torch.cuda.current_stream().wait_stream(side)
     torch.cuda.synchronize()
     graph = torch.cuda.CUDAGraph()
-    with torch.cuda.graph(graph):
+    # thread-local capture: other threads of this process (a collective library's watchdog) may keep calling CUDA
+    with torch.cuda.graph(graph, capture_error_mode="thread_local"):
         for _ in range(rounds):
             for fn in fns:
                 fn()
