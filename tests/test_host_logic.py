@@ -58,3 +58,35 @@ def test_workload_byte_and_op_counts():
     assert W.dynamic_quant_bytes(4096, 4096) == 50339840
     assert W.a16w4_bytes(1, 28672, 8192, 128) == 121184256
     assert W.a16w4_bytes(4, 28672, 8192, 128) == 121405440 and W.a16w4_bytes(16, 28672, 8192, 128) == 122290176
+
+
+def test_norm_and_moe_entry_points_reject_cpu_tensors():
+    import flashnn
+    import flashnn_b200
+    assert flashnn.RMSNormDquant is flashnn_b200.RMSNormDquant and flashnn.LayernormDquant is flashnn_b200.LayernormDquant
+    assert flashnn.fused_moe_a8w8_forward is flashnn_b200.fused_moe_a8w8_forward
+    rms, ln = flashnn_b200.RMSNormDquant(64, 1e-5), flashnn_b200.LayernormDquant((64,), 1e-5)
+    assert rms.weight.shape == (64,) and ln.weight.shape == (64,) and ln.bias.shape == (64,) and ln.dim == (64,)
+    x = torch.randn(4, 64).half()
+    with pytest.raises(RuntimeError, match="no CPU path"):
+        rms(x)
+    with pytest.raises(RuntimeError, match="no CPU path"):
+        ln(x)
+    a = torch.zeros(4, 64, dtype=torch.int8)
+    b = torch.zeros(2, 16, 64, dtype=torch.int8)
+    c = torch.zeros(4, 1, 16, dtype=torch.float16)
+    ids = torch.zeros(16, dtype=torch.int32)
+    with pytest.raises(RuntimeError, match="no CPU path"):
+        flashnn_b200.fused_moe_a8w8_forward(a, b, c, torch.ones(4), torch.ones(2, 16), torch.ones(4, 1), torch.zeros(4, 1, dtype=torch.int32),
+                                            ids, torch.zeros(1, dtype=torch.int32), torch.tensor([16], dtype=torch.int32), True, 1, 16)
+
+
+def test_options_round_trip_without_a_gpu():
+    from flashnn_b200 import _lib
+    assert _lib.lib().fnn_get_option(_lib.OPT_STATIC_WEIGHTS) == 0
+    _lib.set_option(_lib.OPT_STATIC_WEIGHTS, 1)
+    assert _lib.lib().fnn_get_option(_lib.OPT_STATIC_WEIGHTS) == 1
+    _lib.set_option(_lib.OPT_STATIC_WEIGHTS, 0)
+    assert _lib.lib().fnn_get_option(12345) == -1
+    with pytest.raises(_lib.FlashNNError):
+        _lib.set_option(12345, 1)
