@@ -627,6 +627,94 @@ __global__ void wo_generic_kernel(const WoParams p) {
   reinterpret_cast<T*>(p.out)[int64_t(m) * p.ldo + n] = from_f32<T>(total);
 }
 
+// Decode shapes the tensor-core kernels decline (K not a multiple of 512, unusual group sizes): one warp per weight
+// row (two channels of packed int4, one of int8), lanes stride over K with coalesced 16-byte loads, fp32 throughout,
+// one scale group at a time so that w*s is never rounded.  K % 16 == 0, group % 16 == 0 (or per-channel), M <= 16.
+template <typename T, int BITS, int MT>
+__global__ void __launch_bounds__(256) wo_row_warp_kernel(const WoParams p) {
+  constexpr int CH = (BITS == 4) ? 2 : 1;  // channels per weight row
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int row = blockIdx.x * 8 + warp;
+  const int rows = (BITS == 4) ? p.N / 2 : p.N;
+  if (row >= rows) return;
+  const uint8_t* wr = p.qw + int64_t(row) * p.K;
+  const T* x = reinterpret_cast<const T*>(p.act);
+  const int glen = p.group > 0 ? p.group : p.K;
+  float tot[MT][CH];
+#pragma unroll
+  for (int m = 0; m < MT; ++m)
+#pragma unroll
+    for (int c = 0; c < CH; ++c) tot[m][c] = 0.f;
+  for (int k0 = lane * 16; k0 < p.K; k0 += 32 * 16) {
+    const uint4 wv = __ldg(reinterpret_cast<const uint4*>(wr + k0));
+    const uint32_t ww[4] = {wv.x, wv.y, wv.z, wv.w};
+    float wf[CH][16];
+#pragma unroll
+    for (int j = 0; j < 16; ++j) {
+      const int b = int((ww[j >> 2] >> (8 * (j & 3))) & 0xffu);
+      if (BITS == 4) {
+        wf[0][j] = float(((b & 0xF) ^ 8) - 8);
+        wf[CH - 1][j] = float(((b >> 4) ^ 8) - 8);
+      } else {
+        wf[0][j] = float(int(int8_t(b)));
+      }
+    }
+    // the 16 k of this chunk lie in one scale group
+    const int64_t g_off = p.group > 0 ? int64_t(k0 / glen) * p.N : 0;
+    float s[CH], z[CH];
+#pragma unroll
+    for (int c = 0; c < CH; ++c) {
+      const int ch = row * CH + c;
+      s[c] = load_as_f32(p.scale, p.scale_dtype, g_off + ch);
+      z[c] = p.zp ? load_as_f32(p.zp, p.scale_dtype, g_off + ch) : 0.f;
+    }
+#pragma unroll
+    for (int m = 0; m < MT; ++m) {
+      if (m < p.M) {
+        const uint4* xp = reinterpret_cast<const uint4*>(x + int64_t(m) * p.lda + k0);
+        const uint4 xa = __ldg(xp), xb = __ldg(xp + 1);
+        const uint32_t xw[8] = {xa.x, xa.y, xa.z, xa.w, xb.x, xb.y, xb.z, xb.w};
+        float acc[CH], xs = 0.f;
+#pragma unroll
+        for (int c = 0; c < CH; ++c) acc[c] = 0.f;
+#pragma unroll
+        for (int j = 0; j < 16; ++j) {
+          const uint16_t h = uint16_t(xw[j >> 1] >> (16 * (j & 1)));
+          const float xf = to_f32(*reinterpret_cast<const T*>(&h));
+          xs += xf;
+#pragma unroll
+          for (int c = 0; c < CH; ++c) acc[c] = fmaf(xf, wf[c][j], acc[c]);
+        }
+#pragma unroll
+        for (int c = 0; c < CH; ++c) tot[m][c] = fmaf(s[c], acc[c] - z[c] * xs, tot[m][c]);
+      }
+    }
+  }
+#pragma unroll
+  for (int m = 0; m < MT; ++m)
+#pragma unroll
+    for (int c = 0; c < CH; ++c) {
+      float v = tot[m][c];
+#pragma unroll
+      for (int o = 16; o > 0; o >>= 1) v += __shfl_xor_sync(0xffffffffu, v, o);
+      tot[m][c] = v;
+    }
+  if (lane == 0) {
+#pragma unroll
+    for (int m = 0; m < MT; ++m) {
+      if (m < p.M) {
+#pragma unroll
+        for (int c = 0; c < CH; ++c) {
+          const int ch = row * CH + c;
+          float v = tot[m][c];
+          if (p.bias) v += load_as_f32(p.bias, p.bias_dtype, ch);
+          reinterpret_cast<T*>(p.out)[int64_t(m) * p.ldo + ch] = from_f32<T>(v);
+        }
+      }
+    }
+  }
+}
+
 // Steps (of 64 k) per partial-sum flush of the fast kernel, or -1 when the fast kernel does not apply.
 int gemv_spu(const WoParams& p, int bits, int act_dtype) {
   if (p.M > 16) return -1;
@@ -653,6 +741,18 @@ int launch_wo(WoParams p, void* workspace, size_t workspace_bytes, cudaStream_t 
   }
   const int spu = gemv_spu(p, BITS, std::is_same<T, __half>::value ? FNN_F16 : FNN_BF16);
   if (spu < 0) {
+    // decode shapes outside the tensor-core kernels: coalesced warp-per-row kernel when the rows can be read in
+    // 16-byte pieces, else one thread per output
+    const bool rows16 = p.M <= 16 && p.K % 16 == 0 && (p.group == 0 || p.group % 16 == 0) &&
+                        reinterpret_cast<uintptr_t>(p.qw) % 16 == 0 && reinterpret_cast<uintptr_t>(p.act) % 16 == 0 &&
+                        p.lda % 8 == 0 && (BITS == 8 || p.N % 2 == 0);
+    if (rows16) {
+      const int rows = (BITS == 4) ? p.N / 2 : p.N;
+      const unsigned grid = unsigned((rows + 7) / 8);
+      if (p.M <= 4) wo_row_warp_kernel<T, BITS, 4><<<grid, 256, 0, st>>>(p);
+      else wo_row_warp_kernel<T, BITS, 16><<<grid, 256, 0, st>>>(p);
+      return check_cuda(cudaGetLastError(), "weight-only row-per-warp launch");
+    }
     const int64_t total = int64_t(p.M) * p.N;
     wo_generic_kernel<T, BITS><<<unsigned((total + 255) / 256), 256, 0, st>>>(p);
     return check_cuda(cudaGetLastError(), "weight-only generic launch");

@@ -295,3 +295,14 @@ def test_int4_sixteen_tokens_non_finite_row():
     assert bool(torch.isnan(out[7].float()).all())
     keep = [i for i in range(16) if i != 7]
     assert torch.equal(out[keep].view(torch.int16), clean[keep].view(torch.int16))
+
+
+# Decode shapes whose K the tensor-core kernels decline (not a multiple of 512): the coalesced warp-per-row kernel.
+@pytest.mark.parametrize("kind,m,n,k,group,use_bias,use_zp", [
+    (4, 1, 512, 11008, 128, False, False), (4, 4, 256, 11008, 128, True, True), (4, 16, 64, 1104, 48, True, False),
+    (8, 3, 100, 1040, 0, True, True), (8, 9, 48, 2064, 16, False, True), (4, 2, 32, 80, 0, False, False)])
+@pytest.mark.parametrize("dt", [torch.float16, torch.bfloat16])
+def test_decode_odd_k_shapes(kind, m, n, k, group, use_bias, use_zp, dt):
+    act, qw, scale, bias, zp = make(kind, m, n, k, dt, group, use_bias, use_zp, seed=k + m)
+    out = run(act, qw, scale, bias, zp)
+    assert_within_bound(out, act, qw, scale, bias, zp)
