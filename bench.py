@@ -522,6 +522,15 @@ def run_case(args):
         op = flashnn_b200.GemmWeightOnly(torch.bfloat16)
         fn = lambda: op(x, qw, sc)
         work, unit = W.a16w4_bytes(m, n, k, 128) / 1e9, "GB/s"
+    elif name == "gemv8":
+        m, n, k = args.m or 1, args.n or 28672, args.k or 8192
+        g = torch.Generator().manual_seed(1)
+        x = torch.randn(m, k, generator=g).to(torch.bfloat16).to(device)
+        qw = torch.randint(-127, 128, (n, k), generator=g, dtype=torch.int8).to(device)
+        sc = (torch.rand(k // 128, n, generator=g) * 0.045 + 0.005).to(torch.bfloat16).to(device)
+        op = flashnn_b200.GemmWeightOnly(torch.bfloat16)
+        fn = lambda: op(x, qw, sc)
+        work, unit = (n * k + 2 * (k // 128) * n + 2 * m * k + 2 * m * n) / 1e9, "GB/s"
     elif name == "wo":
         m, n, k = args.m or 2048, args.n or 8192, args.k or 8192
         w = W.a16w8_prefill(m, n, k)
@@ -571,7 +580,7 @@ def main():
     ap.add_argument("--warmup", type=int, default=5)
     ap.add_argument("--impl", choices=["native", "reference"], default="native")
     ap.add_argument("--cpu-rows", type=int, default=256, help="tokens in the CPU-baseline sample")
-    ap.add_argument("--case", choices=["a8w8", "gemv", "dq", "wo", "rmsdq", "lndq", "moe"], help="run one kernel only (profiling / A-B timing)")
+    ap.add_argument("--case", choices=["a8w8", "gemv", "gemv8", "dq", "wo", "rmsdq", "lndq", "moe"], help="run one kernel only (profiling / A-B timing)")
     ap.add_argument("--m", type=int)
     ap.add_argument("--n", type=int)
     ap.add_argument("--k", type=int)

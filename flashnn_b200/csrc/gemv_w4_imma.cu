@@ -1,4 +1,5 @@
-// Packed-int4 weight-only GEMV for one to five tokens on the integer tensor pipe.
+// Weight-only GEMV for one to five tokens on the integer tensor pipe: packed int4 weights, and int8 weights, which
+// need no expansion at all.
 //
 // The op is HBM-bound: every weight byte is read once, so what decides the speed is how few instructions a
 // warp spends per weight byte.  Expanding a nibble to a 16-bit float costs about one integer-pipe instruction
@@ -24,6 +25,8 @@
 // workers' totals of a row group in a fixed order and writes the outputs; the workers hand their totals over
 // through a double-buffered array and two pairs of named barriers and never wait for each other.
 // A non-finite activation makes the whole output row NaN.
+// int8 weights take the same route with 32 bytes per lane and step (16 bytes of each of its two weight rows, which go
+// into the MMA operand as they are) and an 8-step FIFO of the same size in bytes.
 #include "async_copy.cuh"
 #include "common.cuh"
 #include "weight_only.cuh"
@@ -36,8 +39,8 @@ constexpr int kImmaThreads = kImmaWarps * 32;   // worker threads: they stream t
 constexpr int kImmaCtaThreads = kImmaThreads + 32;  // plus one warp that sums the workers' totals and writes the outputs
 constexpr int kImmaStepK = 64;        // k per warp step: 4 lanes x 16 bytes of one packed row
 constexpr int kImmaBlk = 4;           // steps per unrolled block of the main loop; the FIFO holds depth / 4 blocks
-constexpr int kImmaSlotBytes = 512;   // one step of one warp
-constexpr int kImmaDeep = 16;         // FIFO steps per lane when shared memory allows (else 8)
+__host__ __device__ constexpr int imma_slot_bytes(int bits) { return bits == 4 ? 512 : 1024; }  // one step of one warp
+__host__ __device__ constexpr int imma_deep(int bits) { return bits == 4 ? 16 : 8; }  // FIFO steps per lane when shared memory allows (else half)
 constexpr int kImmaPlanePad = 64;     // plane pitch = K + 64 bytes: the eight planes a warp reads hit distinct banks
 constexpr int kImmaMaxTokens = 5;     // 3 planes per token, 16 MMA columns
 constexpr int kImmaSmemCap = 226 * 1024;  // dynamic shared memory a CTA may ask for
@@ -86,10 +89,10 @@ struct ImmaLayout {
 __host__ __device__ constexpr int imma_sring_warp(int depth, int spu, bool perch) { return perch ? 0 : (depth / spu) * 32; }
 // depth: FIFO steps per lane; sring_warp: imma_sring_warp(); zp_groups: K / group when group-wise zero-points are
 // given, else 0
-__host__ __device__ inline ImmaLayout imma_layout(int M, int K, int nf, int depth, int sring_warp, int zp_groups) {
+__host__ __device__ inline ImmaLayout imma_layout(int bits, int M, int K, int nf, int depth, int sring_warp, int zp_groups) {
   const int groups = zp_groups;
   ImmaLayout l;
-  l.planes = kImmaWarps * depth * kImmaSlotBytes;
+  l.planes = kImmaWarps * depth * imma_slot_bytes(bits);
   l.red = l.planes + 3 * M * (K + kImmaPlanePad);
   l.fin = l.red + 2 * kImmaWarps * nf * 4 * 32 * 4;
   l.sx = l.fin + 2 * 16 * 16 * 4;
@@ -116,9 +119,11 @@ __device__ __forceinline__ void imma0(int (&d)[4], uint32_t a0, uint32_t a1, uin
 // One CTA per SM: the 128 registers this allows keep a block of four steps free of reloads.
 // XREG: K == 8192, one column block: a lane's digit-plane fragments (8 steps x 16 bytes, the same for every row
 // group) stay in registers instead of being re-read from shared memory at every step.
-template <typename T, int NF, int SPU, bool PERCH, bool GZP, int DEPTH, bool XREG>
+template <typename T, int BITS, int NF, int SPU, bool PERCH, bool GZP, int DEPTH, bool XREG>
 __global__ void __launch_bounds__(kImmaCtaThreads, 1)
 gemv_w4_imma_kernel(const WoParams p, const int num_rg) {
+  constexpr int kImmaSlotBytes = imma_slot_bytes(BITS);
+  constexpr bool W8 = BITS == 8;
   extern __shared__ __align__(128) uint8_t smem[];
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int g = lane >> 2, tig = lane & 3;
@@ -128,7 +133,7 @@ gemv_w4_imma_kernel(const WoParams p, const int num_rg) {
   const int groups = PERCH ? 0 : K / (SPU * kImmaStepK);
   constexpr int kImmaSringWarp = imma_sring_warp(DEPTH, SPU, PERCH);
   constexpr int kImmaSringBytes = kImmaWarps * kImmaSringWarp;
-  const ImmaLayout L = imma_layout(M, K, NF, DEPTH, kImmaSringWarp, group_zp ? groups : 0);
+  const ImmaLayout L = imma_layout(BITS, M, K, NF, DEPTH, kImmaSringWarp, group_zp ? groups : 0);
   const int pitch = K + kImmaPlanePad;
   constexpr int kRingBlocks = DEPTH / kImmaBlk;
   const int nblk = K / (kImmaStepK * kImmaWarps * kImmaBlk);  // blocks per row group in a warp's K slice
@@ -140,10 +145,17 @@ gemv_w4_imma_kernel(const WoParams p, const int num_rg) {
   asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
 
   // ---- weights: start the FIFO before anything else -------------------------------------------------------------
+  // a slot is [32 lanes][16 B]; int8 weights use two such halves (the lane's first and second weight row)
   const uint32_t fifo = smem_u32(smem) + warp * (DEPTH * kImmaSlotBytes) + lane * 16;
-  const int64_t rg_stride = int64_t(gridDim.x) * 8 * K;
+  // weight rows of a row group: 8 packed rows (int4) or 16 rows (int8); this lane reads packed row g, or rows 2g and
+  // 2g + 1, which are MMA rows g and g + 8 in both cases (channels 2g and 2g + 1 of the group)
+  const int64_t rg_stride = int64_t(gridDim.x) * (W8 ? 16 : 8) * K;
   // fill cursor: the next block of this CTA's work to request; it runs kRingBlocks blocks ahead of the consumer
-  const uint8_t* wfill = p.qw + (int64_t(blockIdx.x) * 8 + g) * K + k_begin + tig * 16;
+  const uint8_t* wfill = p.qw + (int64_t(blockIdx.x) * (W8 ? 16 : 8) + (W8 ? 2 * g : g)) * K + k_begin + tig * 16;
+  auto copy_step = [&](uint32_t slot_addr, const uint8_t* w) {
+    cp_async16(slot_addr, w);
+    if (W8) cp_async16(slot_addr + 512, w + K);
+  };
   int fill_rg = worker ? int(blockIdx.x) : num_rg, fill_blk = 0;  // (the reducer warp never requests anything)
   const int64_t fill_wrap = rg_stride - int64_t(nblk - 1) * (kImmaBlk * kImmaStepK);  // last block -> first of the next row group
   // the block's group scales (zero-points) travel with it: lanes with tig == 0 copy the packed pair of their two channels
@@ -174,7 +186,7 @@ gemv_w4_imma_kernel(const WoParams p, const int num_rg) {
     fill_scales(b);
 #pragma unroll
     for (int j = 0; j < kImmaBlk; ++j)
-      if (fill_rg < num_rg) cp_async16(fifo + (b * kImmaBlk + j) * kImmaSlotBytes, wfill + j * kImmaStepK);
+      if (fill_rg < num_rg) copy_step(fifo + (b * kImmaBlk + j) * kImmaSlotBytes, wfill + j * kImmaStepK);
     cp_async_commit();  // one group per block, real or empty, keeps the wait count fixed
     advance_fill();
   }
@@ -234,7 +246,7 @@ gemv_w4_imma_kernel(const WoParams p, const int num_rg) {
       int shift = 22 - e;
       shift = shift > 120 ? 120 : shift;
       const float up = bad ? 0.f : __uint_as_float(uint32_t(127 + shift) << 23);  // 2^shift
-      const float down = __uint_as_float(uint32_t(127 - shift - 4) << 23);          // 2^-shift / 16
+      const float down = __uint_as_float(uint32_t(127 - shift - (W8 ? 0 : 4)) << 23);  // 2^-shift (/ 16 for int4, whose int8 form is 16 n)
       if (threadIdx.x == 0) {
         sx[m] = bad ? __int_as_float(0x7fc00000) : down;
         xsum[m] = sum;
@@ -390,10 +402,17 @@ gemv_w4_imma_kernel(const WoParams p, const int num_rg) {
           else lds128_if(xv[f], xa[f] + j * kImmaStepK, xon[f]);
         }
         const uint4 wv = lds128(slots + j * kImmaSlotBytes);
-        const uint32_t a0 = (wv.x << 4) & 0xF0F0F0F0u, a1 = wv.x & 0xF0F0F0F0u;
-        const uint32_t a2 = (wv.y << 4) & 0xF0F0F0F0u, a3 = wv.y & 0xF0F0F0F0u;
-        const uint32_t c0 = (wv.z << 4) & 0xF0F0F0F0u, c1 = wv.z & 0xF0F0F0F0u;
-        const uint32_t c2 = (wv.w << 4) & 0xF0F0F0F0u, c3 = wv.w & 0xF0F0F0F0u;
+        uint32_t a0, a1, a2, a3, c0, c1, c2, c3;
+        if (W8) {  // 16 bytes of row 2g and of row 2g + 1, used as they are
+          const uint4 w2 = lds128(slots + j * kImmaSlotBytes + 512);
+          a0 = wv.x; a1 = w2.x; a2 = wv.y; a3 = w2.y;
+          c0 = wv.z; c1 = w2.z; c2 = wv.w; c3 = w2.w;
+        } else {
+          a0 = (wv.x << 4) & 0xF0F0F0F0u; a1 = wv.x & 0xF0F0F0F0u;
+          a2 = (wv.y << 4) & 0xF0F0F0F0u; a3 = wv.y & 0xF0F0F0F0u;
+          c0 = (wv.z << 4) & 0xF0F0F0F0u; c1 = wv.z & 0xF0F0F0F0u;
+          c2 = (wv.w << 4) & 0xF0F0F0F0u; c3 = wv.w & 0xF0F0F0F0u;
+        }
         const bool first = !PERCH && (j % SPU == 0);  // per-channel scales: the accumulator was zeroed above
 #pragma unroll
         for (int f = 0; f < NF; ++f) {
@@ -406,7 +425,7 @@ gemv_w4_imma_kernel(const WoParams p, const int num_rg) {
           float sa = 1.f, sb = 1.f, za = 0.f, zb = 0.f;
           if (!PERCH) {
             sa = lo16<T>(sc[j / SPU]); sb = hi16<T>(sc[j / SPU]);
-            if (GZP) { za = 16.f * lo16<T>(zc[j / SPU]); zb = 16.f * hi16<T>(zc[j / SPU]); }
+            if (GZP) { za = (W8 ? 1.f : 16.f) * lo16<T>(zc[j / SPU]); zb = (W8 ? 1.f : 16.f) * hi16<T>(zc[j / SPU]); }
           }
 #pragma unroll
           for (int f = 0; f < NF; ++f) {
@@ -425,7 +444,7 @@ gemv_w4_imma_kernel(const WoParams p, const int num_rg) {
       // copies of a lane are 64 bytes apart, so the warp asks for 256 contiguous bytes of each of its 8 rows at once.
       if (fill_ok) {
 #pragma unroll
-        for (int j = 0; j < kImmaBlk; ++j) cp_async16(slots + j * kImmaSlotBytes, wfill + j * kImmaStepK);
+        for (int j = 0; j < kImmaBlk; ++j) copy_step(slots + j * kImmaSlotBytes, wfill + j * kImmaStepK);
       }
       fill_scales(ring);
       cp_async_commit();
@@ -451,15 +470,15 @@ gemv_w4_imma_kernel(const WoParams p, const int num_rg) {
   cp_async_wait<0>();
 }
 
-template <typename T, int NF, int SPU, bool PERCH, bool GZP, int DEPTH, bool XREG>
+template <typename T, int BITS, int NF, int SPU, bool PERCH, bool GZP, int DEPTH, bool XREG>
 int launch_imma_x(const WoParams& p, size_t smem_bytes, cudaStream_t st) {
   static bool configured[64] = {};
   int dev = 0;
   cudaGetDevice(&dev);
   if (!configured[dev & 63]) {
-    const cudaError_t err = cudaFuncSetAttribute(gemv_w4_imma_kernel<T, NF, SPU, PERCH, GZP, DEPTH, XREG>,
+    const cudaError_t err = cudaFuncSetAttribute(gemv_w4_imma_kernel<T, BITS, NF, SPU, PERCH, GZP, DEPTH, XREG>,
                                                  cudaFuncAttributeMaxDynamicSharedMemorySize, kImmaSmemCap);
-    if (err != cudaSuccess) return check_cuda(err, "weight-only int4 decode kernel attribute");
+    if (err != cudaSuccess) return check_cuda(err, "weight-only decode kernel attribute");
     configured[dev & 63] = true;
   }
   const int num_rg = p.N / 16;
@@ -477,38 +496,40 @@ int launch_imma_x(const WoParams& p, size_t smem_bytes, cudaStream_t st) {
   attr[0].val.programmaticStreamSerializationAllowed = 1;
   cfg.attrs = attr;
   cfg.numAttrs = opt_static_weights() ? 1 : 0;
-  return check_cuda(cudaLaunchKernelEx(&cfg, gemv_w4_imma_kernel<T, NF, SPU, PERCH, GZP, DEPTH, XREG>, p, num_rg),
-                    "weight-only int4 decode launch");
+  return check_cuda(cudaLaunchKernelEx(&cfg, gemv_w4_imma_kernel<T, BITS, NF, SPU, PERCH, GZP, DEPTH, XREG>, p, num_rg),
+                    "weight-only decode (integer tensor pipe) launch");
 }
 
-template <typename T, int NF, int SPU, bool PERCH, bool GZP, int DEPTH>
+template <typename T, int BITS, int NF, int SPU, bool PERCH, bool GZP, int DEPTH>
 int launch_imma(const WoParams& p, size_t smem_bytes, cudaStream_t st) {
-  if (NF == 1 && DEPTH == kImmaDeep && p.K == 8192) return launch_imma_x<T, NF, SPU, PERCH, GZP, DEPTH, (NF == 1 && DEPTH == kImmaDeep)>(p, smem_bytes, st);
-  return launch_imma_x<T, NF, SPU, PERCH, GZP, DEPTH, false>(p, smem_bytes, st);
+  constexpr bool kCanHold = NF == 1 && DEPTH == imma_deep(BITS);
+  if (kCanHold && p.K == 8192) return launch_imma_x<T, BITS, NF, SPU, PERCH, GZP, DEPTH, kCanHold>(p, smem_bytes, st);
+  return launch_imma_x<T, BITS, NF, SPU, PERCH, GZP, DEPTH, false>(p, smem_bytes, st);
 }
 
-template <typename T, int NF, int DEPTH>
+template <typename T, int BITS, int NF, int DEPTH>
 int launch_imma_spu(const WoParams& p, int spu, size_t smem_bytes, cudaStream_t st) {
-  if (p.group == 0) return launch_imma<T, NF, 4, true, false, DEPTH>(p, smem_bytes, st);
+  if (p.group == 0) return launch_imma<T, BITS, NF, 4, true, false, DEPTH>(p, smem_bytes, st);
   if (p.zp) {
-    if (spu == 1) return launch_imma<T, NF, 1, false, true, DEPTH>(p, smem_bytes, st);
-    if (spu == 2) return launch_imma<T, NF, 2, false, true, DEPTH>(p, smem_bytes, st);
-    return launch_imma<T, NF, 4, false, true, DEPTH>(p, smem_bytes, st);
+    if (spu == 1) return launch_imma<T, BITS, NF, 1, false, true, DEPTH>(p, smem_bytes, st);
+    if (spu == 2) return launch_imma<T, BITS, NF, 2, false, true, DEPTH>(p, smem_bytes, st);
+    return launch_imma<T, BITS, NF, 4, false, true, DEPTH>(p, smem_bytes, st);
   }
-  if (spu == 1) return launch_imma<T, NF, 1, false, false, DEPTH>(p, smem_bytes, st);
-  if (spu == 2) return launch_imma<T, NF, 2, false, false, DEPTH>(p, smem_bytes, st);
-  return launch_imma<T, NF, 4, false, false, DEPTH>(p, smem_bytes, st);
+  if (spu == 1) return launch_imma<T, BITS, NF, 1, false, false, DEPTH>(p, smem_bytes, st);
+  if (spu == 2) return launch_imma<T, BITS, NF, 2, false, false, DEPTH>(p, smem_bytes, st);
+  return launch_imma<T, BITS, NF, 4, false, false, DEPTH>(p, smem_bytes, st);
 }
 
-template <typename T>
+template <typename T, int BITS>
 int launch_imma_shape(const WoParams& p, int spu, int nf, int depth, size_t smem_bytes, cudaStream_t st) {
-  if (nf == 1) return depth == kImmaDeep ? launch_imma_spu<T, 1, kImmaDeep>(p, spu, smem_bytes, st) : launch_imma_spu<T, 1, 8>(p, spu, smem_bytes, st);
-  return depth == kImmaDeep ? launch_imma_spu<T, 2, kImmaDeep>(p, spu, smem_bytes, st) : launch_imma_spu<T, 2, 8>(p, spu, smem_bytes, st);
+  constexpr int kDeep = imma_deep(BITS), kShallow = kDeep / 2;
+  if (nf == 1) return depth == kDeep ? launch_imma_spu<T, BITS, 1, kDeep>(p, spu, smem_bytes, st) : launch_imma_spu<T, BITS, 1, kShallow>(p, spu, smem_bytes, st);
+  return depth == kDeep ? launch_imma_spu<T, BITS, 2, kDeep>(p, spu, smem_bytes, st) : launch_imma_spu<T, BITS, 2, kShallow>(p, spu, smem_bytes, st);
 }
 
 }  // namespace
 
-int gemv_w4_imma(const WoParams& p, int act_dtype, cudaStream_t st) {
+int gemv_w4_imma(const WoParams& p, int bits, int act_dtype, cudaStream_t st) {
   if (p.M < 1 || p.M > kImmaMaxTokens) return -1;
   if (p.N % 16 != 0) return -1;
   if (reinterpret_cast<uintptr_t>(p.qw) % 16 != 0) return -1;
@@ -522,19 +543,24 @@ int gemv_w4_imma(const WoParams& p, int act_dtype, cudaStream_t st) {
     if (p.group % kImmaStepK != 0 || (spu != 1 && spu != 2 && spu != 4)) return -1;
     groups = p.zp ? p.K / p.group : 0;
   } else if (slice > 65536) {
-    return -1;  // the int32 accumulator runs over the whole slice: |acc| <= slice * 2^14
+    return -1;  // the int32 accumulator runs over the whole slice: |acc| <= slice * 128 * 128
   }
   if (p.K % (kImmaStepK * kImmaWarps * kImmaBlk) != 0) return -1;
   const int nf = p.M <= 2 ? 1 : 2;
-  int depth = kImmaDeep;
-  ImmaLayout L = imma_layout(p.M, p.K, nf, depth, imma_sring_warp(depth, spu, p.group == 0), groups);
+  const int deep = imma_deep(bits);
+  int depth = deep;
+  ImmaLayout L = imma_layout(bits, p.M, p.K, nf, depth, imma_sring_warp(depth, spu, p.group == 0), groups);
   if (L.total > kImmaSmemCap) {
-    depth = 8;
-    L = imma_layout(p.M, p.K, nf, depth, imma_sring_warp(depth, spu, p.group == 0), groups);
+    depth = deep / 2;
+    L = imma_layout(bits, p.M, p.K, nf, depth, imma_sring_warp(depth, spu, p.group == 0), groups);
   }
   if (L.total > kImmaSmemCap) return -1;
-  if (act_dtype == FNN_F16) return launch_imma_shape<__half>(p, spu, nf, depth, L.total, st);
-  return launch_imma_shape<__nv_bfloat16>(p, spu, nf, depth, L.total, st);
+  if (bits == 4) {
+    if (act_dtype == FNN_F16) return launch_imma_shape<__half, 4>(p, spu, nf, depth, L.total, st);
+    return launch_imma_shape<__nv_bfloat16, 4>(p, spu, nf, depth, L.total, st);
+  }
+  if (act_dtype == FNN_F16) return launch_imma_shape<__half, 8>(p, spu, nf, depth, L.total, st);
+  return launch_imma_shape<__nv_bfloat16, 8>(p, spu, nf, depth, L.total, st);
 }
 
 }  // namespace fnn

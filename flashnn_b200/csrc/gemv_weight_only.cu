@@ -734,9 +734,9 @@ int gemv_spu(const WoParams& p, int bits, int act_dtype) {
 
 template <typename T, int BITS>
 int launch_wo(WoParams p, void* workspace, size_t workspace_bytes, cudaStream_t st) {
-  if (BITS == 4 && p.M <= 16) {
+  if (p.M <= 16) {
     // one to five tokens: integer tensor-pipe kernel (declines shapes it does not cover)
-    const int r = gemv_w4_imma(p, std::is_same<T, __half>::value ? FNN_F16 : FNN_BF16, st);
+    const int r = gemv_w4_imma(p, BITS, std::is_same<T, __half>::value ? FNN_F16 : FNN_BF16, st);
     if (r >= 0) return r;
   }
   const int spu = gemv_spu(p, BITS, std::is_same<T, __half>::value ? FNN_F16 : FNN_BF16);

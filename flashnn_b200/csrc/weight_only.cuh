@@ -21,8 +21,8 @@ struct WoParams {
 // |x| with NaN mapped to +infinity, so that a running fmaxf keeps a non-finite input visible
 __device__ __forceinline__ float nan_to_inf(float v) { return v != v ? __int_as_float(0x7f800000) : v; }
 
-// Packed-int4 decode kernel on the integer tensor pipe (gemv_w4_imma.cu), for at most kImmaMaxTokens tokens.
+// Decode kernel on the integer tensor pipe (gemv_w4_imma.cu) for one to five tokens; bits = 4 (packed) or 8.
 // Returns an fnn_status, or -1 when the shape or alignment is outside what that kernel handles.
-int gemv_w4_imma(const WoParams& p, int act_dtype, cudaStream_t st);
+int gemv_w4_imma(const WoParams& p, int bits, int act_dtype, cudaStream_t st);
 
 }  // namespace fnn

@@ -306,3 +306,28 @@ def test_decode_odd_k_shapes(kind, m, n, k, group, use_bias, use_zp, dt):
     act, qw, scale, bias, zp = make(kind, m, n, k, dt, group, use_bias, use_zp, seed=k + m)
     out = run(act, qw, scale, bias, zp)
     assert_within_bound(out, act, qw, scale, bias, zp)
+
+
+# int8 weights, one to five tokens, on the integer tensor pipe (the weight bytes are the MMA operand as they are).
+@pytest.mark.parametrize("dt", [torch.bfloat16, torch.float16])
+@pytest.mark.parametrize("m", [1, 2, 3, 5])
+@pytest.mark.parametrize("n,k,group,use_bias,use_zp", [
+    (1024, 4096, 64, True, True), (64, 8192, 128, False, False), (48, 4096, 256, True, False), (32, 8192, 0, True, True),
+    (96, 12288, 0, False, False), (16, 8192, 128, False, True), (32, 28672, 128, True, False)])
+def test_int8_few_tokens(dt, m, n, k, group, use_bias, use_zp):
+    act, qw, scale, bias, zp = make(8, m, n, k, dt, group, use_bias, use_zp, seed=m + n + k)
+    g = torch.Generator().manual_seed(k)
+    act = torch.where(torch.rand(m, k, generator=g) < 0.002, act * 30, act)  # outliers
+    if m >= 2:
+        act[1] = 0
+    out = run(act, qw, scale, bias, zp)
+    ref = O.gemm_weight_only_fp32(act, qw, scale, bias, zp)
+    row_scale = ref.abs().amax(dim=1, keepdim=True)
+    err = (out.float() - ref).abs()
+    bound = ATOL + RTOL * ref.abs() + 4e-3 * row_scale * (2.0 ** -8 if dt == torch.bfloat16 else 2.0 ** -11) * 256
+    assert bool((err <= bound).all()), f"max excess {(err - bound).max():.3e}"
+    exact = ref.to(dt)
+    assert int((out != exact).sum()) <= max(3, 0.02 * out.numel())
+    if m >= 2:
+        want = torch.zeros(n) if bias is None else bias.float()
+        assert torch.equal(out[1].float(), want.to(dt).float())
