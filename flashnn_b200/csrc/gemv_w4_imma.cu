@@ -89,11 +89,12 @@ struct ImmaLayout {
 __host__ __device__ constexpr int imma_sring_warp(int depth, int spu, bool perch) { return perch ? 0 : (depth / spu) * 32; }
 // depth: FIFO steps per lane; sring_warp: imma_sring_warp(); zp_groups: K / group when group-wise zero-points are
 // given, else 0
-__host__ __device__ inline ImmaLayout imma_layout(int bits, int M, int K, int nf, int depth, int sring_warp, int zp_groups) {
+__host__ __device__ inline ImmaLayout imma_layout(int bits, int M, int K, int nf, int depth, int sring_warp, int zp_groups,
+                                                  int planes_per_token = 3) {
   const int groups = zp_groups;
   ImmaLayout l;
   l.planes = kImmaWarps * depth * imma_slot_bytes(bits);
-  l.red = l.planes + 3 * M * (K + kImmaPlanePad);
+  l.red = l.planes + planes_per_token * M * (K + kImmaPlanePad);
   l.fin = l.red + 2 * kImmaWarps * nf * 4 * 32 * 4;
   l.sx = l.fin + 2 * 16 * 16 * 4;
   l.xsum = l.sx + 32;
@@ -119,7 +120,9 @@ __device__ __forceinline__ void imma0(int (&d)[4], uint32_t a0, uint32_t a1, uin
 // One CTA per SM: the 128 registers this allows keep a block of four steps free of reloads.
 // XREG: K == 8192, one column block: a lane's digit-plane fragments (8 steps x 16 bytes, the same for every row
 // group) stay in registers instead of being re-read from shared memory at every step.
-template <typename T, int BITS, int NF, int SPU, bool PERCH, bool GZP, int DEPTH, bool XREG>
+// A8: the activations are int8 already (A8W8 decode): they are copied into the planes as they are, one column per
+// token, the int32 sums stay exact all the way to the reducer, which applies the A8W8 scaling rule.
+template <typename T, int BITS, int NF, int SPU, bool PERCH, bool GZP, int DEPTH, bool XREG, bool A8 = false>
 __global__ void __launch_bounds__(kImmaCtaThreads, 1)
 gemv_w4_imma_kernel(const WoParams p, const int num_rg) {
   constexpr int kImmaSlotBytes = imma_slot_bytes(BITS);
@@ -133,7 +136,7 @@ gemv_w4_imma_kernel(const WoParams p, const int num_rg) {
   const int groups = PERCH ? 0 : K / (SPU * kImmaStepK);
   constexpr int kImmaSringWarp = imma_sring_warp(DEPTH, SPU, PERCH);
   constexpr int kImmaSringBytes = kImmaWarps * kImmaSringWarp;
-  const ImmaLayout L = imma_layout(BITS, M, K, NF, DEPTH, kImmaSringWarp, group_zp ? groups : 0);
+  const ImmaLayout L = imma_layout(BITS, M, K, NF, DEPTH, kImmaSringWarp, group_zp ? groups : 0, A8 ? 1 : 3);
   const int pitch = K + kImmaPlanePad;
   constexpr int kRingBlocks = DEPTH / kImmaBlk;
   const int nblk = K / (kImmaStepK * kImmaWarps * kImmaBlk);  // blocks per row group in a warp's K slice
@@ -197,7 +200,15 @@ gemv_w4_imma_kernel(const WoParams p, const int num_rg) {
   float* sx = reinterpret_cast<float*>(smem + L.sx);
   float* xsum = reinterpret_cast<float*>(smem + L.xsum);
   float* fin2 = reinterpret_cast<float*>(smem + L.fin);
-  {
+  if (A8) {
+    // int8 activations: row m becomes plane m as it is
+    for (int m = 0; m < M; ++m) {
+      const uint4* src = reinterpret_cast<const uint4*>(reinterpret_cast<const int8_t*>(p.act) + int64_t(m) * p.lda);
+      uint4* dst = reinterpret_cast<uint4*>(smem + L.planes + m * pitch);
+      for (int i = worker ? int(threadIdx.x) : K / 16; i < K / 16; i += kImmaThreads) dst[i] = __ldg(src + i);
+    }
+    __syncthreads();
+  } else {
     float* scratch = fin2;  // [2][16 warps] floats, free until the first row group is written
     constexpr int kHold = 4;  // 16-byte chunks of a row a thread keeps in registers between the two passes
     for (int m = 0; m < M; ++m) {
@@ -309,6 +320,36 @@ gemv_w4_imma_kernel(const WoParams p, const int num_rg) {
     int half = 0;
     for (int rg = blockIdx.x; rg < num_rg; rg += gridDim.x, half ^= 1) {
       named_barrier_sync(1 + half);
+      if (A8) {
+        // exact int32 totals; MMA column c is token c
+        int* fi = reinterpret_cast<int*>(fin);
+#pragma unroll
+        for (int f = 0; f < NF; ++f) {
+          int4 v = make_int4(0, 0, 0, 0);
+#pragma unroll
+          for (int w = 0; w < kImmaWarps; ++w) {
+            const int4 t = *reinterpret_cast<const int4*>(red + (((half * kImmaWarps + w) * NF + f) * 32 + lane) * 4);
+            v.x += t.x; v.y += t.y; v.z += t.z; v.w += t.w;
+          }
+          *reinterpret_cast<int2*>(fi + g * 16 + 8 * f + 2 * tig) = make_int2(v.x, v.y);
+          *reinterpret_cast<int2*>(fi + (g + 8) * 16 + 8 * f + 2 * tig) = make_int2(v.z, v.w);
+        }
+        if (rg + 2 * int(gridDim.x) < num_rg) named_barrier_arrive(3 + half);
+        __syncwarp();
+        T* out = reinterpret_cast<T*>(p.out);
+        const bool same16 = (p.row_dtype == p.scale_dtype) && (p.row_dtype != FNN_F32);
+        for (int idx = lane; idx < 16 * M; idx += 32) {
+          const int cl = idx & 15, tok = idx >> 4;
+          const int row = (cl & 1) ? (cl >> 1) + 8 : (cl >> 1);
+          const int acc = fi[row * 16 + tok];
+          const int ch = rg * 16 + cl;
+          if (p.acc_out) p.acc_out[int64_t(tok) * p.ldacc + ch] = acc;
+          float sc = __fmul_rn(load_as_f32(p.row_scale, p.row_dtype, tok), load_as_f32(p.scale, p.scale_dtype, ch));
+          if (same16) sc = round_through(sc, p.row_dtype);
+          out[int64_t(tok) * p.ldo + ch] = from_f32<T>(__fmul_rn(float(acc), sc));
+        }
+        __syncwarp();
+      } else {
 #pragma unroll
       for (int f = 0; f < NF; ++f) {
         float4 v = make_float4(0.f, 0.f, 0.f, 0.f);
@@ -337,12 +378,13 @@ gemv_w4_imma_kernel(const WoParams p, const int num_rg) {
         out[int64_t(tok) * p.ldo + ch] = from_f32<T>(v);
       }
       __syncwarp();
+      }
     }
     return;
   }
 
   // ---- main loop ---------------------------------------------------------------------------------------------------
-  const int ncol = 3 * M;
+  const int ncol = A8 ? M : 3 * M;
   // lanes whose MMA column lies past the last digit plane feed zeros and never load
   uint32_t xbase[NF], xon[NF];
 #pragma unroll
@@ -429,6 +471,11 @@ gemv_w4_imma_kernel(const WoParams p, const int num_rg) {
           }
 #pragma unroll
           for (int f = 0; f < NF; ++f) {
+            if (A8) {  // exact sums: the bits travel to the reducer as they are
+              tot[f][0] = __int_as_float(acc[f][0]); tot[f][1] = __int_as_float(acc[f][1]);
+              tot[f][2] = __int_as_float(acc[f][2]); tot[f][3] = __int_as_float(acc[f][3]);
+              continue;
+            }
             float v0 = float(acc[f][0]), v1 = float(acc[f][1]), v2 = float(acc[f][2]), v3 = float(acc[f][3]);
             if (GZP) {
               const float2 cs = *reinterpret_cast<const float2*>(csum + (gi + j / SPU) * (8 * NF) + 8 * f + 2 * tig);
@@ -527,7 +574,58 @@ int launch_imma_shape(const WoParams& p, int spu, int nf, int depth, size_t smem
   return depth == kDeep ? launch_imma_spu<T, BITS, 2, kDeep>(p, spu, smem_bytes, st) : launch_imma_spu<T, BITS, 2, kShallow>(p, spu, smem_bytes, st);
 }
 
+template <typename T, int NF, int DEPTH, bool XREG>
+int launch_a8(const WoParams& p, size_t smem_bytes, cudaStream_t st) {
+  auto kern = gemv_w4_imma_kernel<T, 8, NF, 4, true, false, DEPTH, XREG, true>;
+  static bool configured[64] = {};
+  int dev = 0;
+  cudaGetDevice(&dev);
+  if (!configured[dev & 63]) {
+    const cudaError_t err = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, kImmaSmemCap);
+    if (err != cudaSuccess) return check_cuda(err, "a8w8 decode kernel attribute");
+    configured[dev & 63] = true;
+  }
+  const int num_rg = p.N / 16;
+  const int cap = sm_count();
+  const int rounds = (num_rg + cap - 1) / cap;
+  const int grid = (num_rg + rounds - 1) / rounds;
+  kern<<<grid, kImmaCtaThreads, smem_bytes, st>>>(p, num_rg);
+  return check_cuda(cudaGetLastError(), "a8w8 decode (integer tensor pipe) launch");
+}
+
+template <typename T>
+int launch_a8_shape(const WoParams& p, int nf, int depth, size_t smem_bytes, cudaStream_t st) {
+  if (nf == 1) {
+    if (depth == 8) return p.K == 8192 ? launch_a8<T, 1, 8, true>(p, smem_bytes, st) : launch_a8<T, 1, 8, false>(p, smem_bytes, st);
+    return launch_a8<T, 1, 4, false>(p, smem_bytes, st);
+  }
+  return depth == 8 ? launch_a8<T, 2, 8, false>(p, smem_bytes, st) : launch_a8<T, 2, 4, false>(p, smem_bytes, st);
+}
+
 }  // namespace
+
+int gemv_a8w8_imma(const int8_t* a, int64_t lda, const int8_t* b, int64_t ldb, const void* alpha_row, int row_dtype,
+                   const void* alpha_col, int col_dtype, void* out, int out_dtype, int64_t ldo, int M, int N, int K,
+                   int32_t* acc_out, int64_t ldacc, cudaStream_t st) {
+  if (M < 1 || M > 16 || N % 16 != 0 || K % (kImmaStepK * kImmaWarps * kImmaBlk) != 0 || ldb != K) return -1;
+  if (reinterpret_cast<uintptr_t>(a) % 16 != 0 || lda % 16 != 0 || reinterpret_cast<uintptr_t>(b) % 16 != 0) return -1;
+  if (K / kImmaWarps > 65536) return -1;  // |acc| of a warp's K slice stays below 2^31
+  WoParams p{};
+  p.act = a; p.qw = reinterpret_cast<const uint8_t*>(b); p.scale = alpha_col; p.zp = nullptr; p.bias = nullptr;
+  p.out = out; p.lda = lda; p.ldo = ldo; p.scale_dtype = col_dtype; p.bias_dtype = 0;
+  p.M = M; p.N = N; p.K = K; p.group = 0; p.status = nullptr;
+  p.row_scale = alpha_row; p.row_dtype = row_dtype; p.acc_out = acc_out; p.ldacc = ldacc;
+  const int nf = M <= 8 ? 1 : 2;
+  int depth = 8;
+  ImmaLayout L = imma_layout(8, M, K, nf, depth, 0, 0, 1);
+  if (L.total > kImmaSmemCap) {
+    depth = 4;
+    L = imma_layout(8, M, K, nf, depth, 0, 0, 1);
+  }
+  if (L.total > kImmaSmemCap) return -1;
+  if (out_dtype == FNN_F16) return launch_a8_shape<__half>(p, nf, depth, L.total, st);
+  return launch_a8_shape<__nv_bfloat16>(p, nf, depth, L.total, st);
+}
 
 int gemv_w4_imma(const WoParams& p, int bits, int act_dtype, cudaStream_t st) {
   if (p.M < 1 || p.M > kImmaMaxTokens) return -1;

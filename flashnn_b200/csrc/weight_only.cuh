@@ -16,6 +16,11 @@ struct WoParams {
   int M, N, K;
   int group;  // 0 = per channel
   int* status;  // device status word
+  // A8W8 decode through the same kernel (int8 activations): per-token scale and the optional raw accumulator
+  const void* row_scale;
+  int row_dtype;
+  int32_t* acc_out;
+  int64_t ldacc;
 };
 
 // |x| with NaN mapped to +infinity, so that a running fmaxf keeps a non-finite input visible
@@ -24,5 +29,12 @@ __device__ __forceinline__ float nan_to_inf(float v) { return v != v ? __int_as_
 // Decode kernel on the integer tensor pipe (gemv_w4_imma.cu) for one to five tokens; bits = 4 (packed) or 8.
 // Returns an fnn_status, or -1 when the shape or alignment is outside what that kernel handles.
 int gemv_w4_imma(const WoParams& p, int bits, int act_dtype, cudaStream_t st);
+
+// A8W8 GEMM for at most 16 tokens on the same kernel (int8 activations are the MMA's column operand as they are,
+// exact int32 sums, the A8W8 scaling rule in the write-out).  b must be [N, K] with pitch K.  Returns an
+// fnn_status, or -1 when the shape or alignment is outside what the kernel handles.
+int gemv_a8w8_imma(const int8_t* a, int64_t lda, const int8_t* b, int64_t ldb, const void* alpha_row, int row_dtype,
+                   const void* alpha_col, int col_dtype, void* out, int out_dtype, int64_t ldo, int M, int N, int K,
+                   int32_t* acc_out, int64_t ldacc, cudaStream_t st);
 
 }  // namespace fnn

@@ -140,3 +140,26 @@ def test_large_k_beyond_fp32_exactness():
     assert int(ref_acc.abs().max()) > 2 ** 24
     assert torch.equal(acc, ref_acc)
     assert torch.equal(bits16(out), bits16(O.gemm_a8w8_from_acc(ref_acc, row, col, torch.bfloat16)))
+
+
+# Up to 8 tokens against a wide weight matrix run on the per-lane streaming kernel (int8 activations as MMA columns,
+# exact int32 sums through the reducer): accumulator and scaled output bit for bit, all scale dtype combinations,
+# -128 operands, the long K of the down projection.
+@pytest.mark.parametrize("m,n,k", [(1, 8192, 4096), (3, 8192, 8192), (8, 16384, 4096), (5, 8192, 28672), (2, 8208, 8192)])
+@pytest.mark.parametrize("out_ty", [torch.float16, torch.bfloat16])
+def test_decode_streaming_kernel_exact(m, n, k, out_ty):
+    a, b, row, col = make(m, n, k, seed=m + n + k, lo=-128)
+    out, acc = run(a, b, row, col, out_ty)
+    ref_acc = O.gemm_a8w8_acc_i32(a, b)
+    assert torch.equal(acc, ref_acc)
+    assert torch.equal(bits16(out), bits16(O.gemm_a8w8_from_acc(ref_acc, row, col, out_ty)))
+    # same 16-bit dtype on both scales: their product is rounded to that dtype first
+    a, b, row, col = make(m, n, k, seed=m + k, scale_ty=out_ty)
+    out, _ = run(a, b, row, col, out_ty, want_acc=False)
+    assert torch.equal(bits16(out), bits16(O.gemm_a8w8(a, b, row, col, out_ty)))
+    # worst-case operands: |acc| = k * 128 * 128 exceeds 2^24 for every k here
+    a2 = torch.full((m, k), -128, dtype=torch.int8)
+    b2 = torch.full((n, k), -128, dtype=torch.int8)
+    b2[1::2] = 127
+    out, acc = run(a2, b2, row.float(), col.float(), out_ty)
+    assert torch.equal(acc, O.gemm_a8w8_acc_i32(a2, b2))
