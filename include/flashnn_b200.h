@@ -53,7 +53,7 @@ typedef enum fnn_dtype {
  *
  * FNN_OPT_STATIC_WEIGHTS (default 0).  A promise by the caller: the qweight, scale, zero_points and bias buffers given
  * to fnn_gemm_weight_only are not written by the kernel that directly precedes the call in the same stream (true for
- * inference, where weights are loaded once).  With it set, the packed-int4 decode kernel is launched with programmatic
+ * inference, where weights are loaded once).  With it set, the one-to-five-token decode kernel is launched with programmatic
  * stream serialisation: its CTAs may become resident while the preceding kernel drains and start fetching weights; they
  * touch neither the activations nor the output until that kernel has completed and its writes are visible
  * (griddepcontrol.wait).  Results are unchanged; back-to-back decode calls lose the launch gap between them.
