@@ -20,13 +20,16 @@ template <typename T> __device__ __forceinline__ int quantise_one(float x, float
   return static_cast<int>(fminf(fmaxf(r, -128.f), 127.f));
 }
 
-template <typename T> __device__ __forceinline__ float lo_of(uint32_t w) {
-  const uint16_t l = static_cast<uint16_t>(w & 0xffffu);
-  return to_f32(*reinterpret_cast<const T*>(&l));
+// The two halves of a packed pair as fp32.  bf16 is the top half of an fp32, so one shift or one mask each.
+template <typename T> __device__ __forceinline__ float lo_of(uint32_t w);
+template <typename T> __device__ __forceinline__ float hi_of(uint32_t w);
+template <> __device__ __forceinline__ float lo_of<__nv_bfloat16>(uint32_t w) { return __uint_as_float(w << 16); }
+template <> __device__ __forceinline__ float hi_of<__nv_bfloat16>(uint32_t w) { return __uint_as_float(w & 0xffff0000u); }
+template <> __device__ __forceinline__ float lo_of<__half>(uint32_t w) {
+  return __low2float(*reinterpret_cast<const __half2*>(&w));
 }
-template <typename T> __device__ __forceinline__ float hi_of(uint32_t w) {
-  const uint16_t h = static_cast<uint16_t>(w >> 16);
-  return to_f32(*reinterpret_cast<const T*>(&h));
+template <> __device__ __forceinline__ float hi_of<__half>(uint32_t w) {
+  return __high2float(*reinterpret_cast<const __half2*>(&w));
 }
 
 // Bits of fp32 that a conversion to T drops, and the midpoint pattern among them.
@@ -44,6 +47,16 @@ __device__ __forceinline__ InvBracket inv_bracket(float s) {
   return {__fmul_rn(inv, 0.99999952316284f), __fmul_rn(inv, 1.00000047683716f)};  // 1 -+ 2^-21
 }
 
+// min(t, 127) on a packed pair
+__device__ __forceinline__ uint32_t min2_127(uint32_t t2, __half) {
+  const __half2 r = __hmin2(*reinterpret_cast<const __half2*>(&t2), __float2half2_rn(127.f));
+  return *reinterpret_cast<const uint32_t*>(&r);
+}
+__device__ __forceinline__ uint32_t min2_127(uint32_t t2, __nv_bfloat16) {
+  const __nv_bfloat162 r = __hmin2(*reinterpret_cast<const __nv_bfloat162*>(&t2), __float2bfloat162_rn(127.f));
+  return *reinterpret_cast<const uint32_t*>(&r);
+}
+
 // Two elements at once: returns the two quantised bytes in bits 0-7 and 8-15.  Both ends of the bracket are
 // rounded to T (one packed conversion each); rounding is monotonic, so where the two agree the exact quotient rounds
 // to the same T value.  Where they differ a bit is ORed into `amb` and the caller redoes the chunk with the exact
@@ -52,8 +65,8 @@ template <typename T> __device__ __forceinline__ uint32_t quantise_pair(uint32_t
   const float x0 = lo_of<T>(w), x1 = hi_of<T>(w);
   const uint32_t t2 = pack2<T>(__fmul_rn(x0, inv.lo), __fmul_rn(x1, inv.lo));
   amb |= t2 ^ pack2<T>(__fmul_rn(x0, inv.hi), __fmul_rn(x1, inv.hi));
-  const float t0 = fminf(lo_of<T>(t2), 127.f), t1 = fminf(hi_of<T>(t2), 127.f);
-  const uint32_t q0 = __float_as_uint(__fadd_rn(t0, 12582912.f)), q1 = __float_as_uint(__fadd_rn(t1, 12582912.f));
+  const uint32_t tc = min2_127(t2, T());  // |t| <= 128; only +128 needs the clamp (one packed instruction)
+  const uint32_t q0 = __float_as_uint(__fadd_rn(lo_of<T>(tc), 12582912.f)), q1 = __float_as_uint(__fadd_rn(hi_of<T>(tc), 12582912.f));
   return __byte_perm(q0, q1, 0x0040);  // low bytes of q0, q1 in bytes 0 and 1
 }
 
