@@ -58,8 +58,9 @@ dq_row_vec_kernel(const T* __restrict__ x, int64_t ldx, int8_t* __restrict__ q, 
   const float s = round_to<T>(__fdiv_rn(amax, 127.0f));
   if (threadIdx.x == 0) scale[row] = __float2half_rn(s);
   uint2* qr = reinterpret_cast<uint2*>(q + row * ldq);
-  if (!(s > 0.f)) {
-    // all-zero row (or a scale that underflowed to zero in T): fall back to the plain form
+  const InvBracket inv2 = inv_bracket(s);
+  if (!(s > 0.f) || inv_overflowed(inv2)) {
+    // all-zero row, a scale that underflowed to zero in T, or one too small to invert: the plain form
 #pragma unroll
     for (int c = 0; c < NCHUNK; ++c) {
       const int i = c * blockDim.x + threadIdx.x;
@@ -80,7 +81,6 @@ dq_row_vec_kernel(const T* __restrict__ x, int64_t ldx, int8_t* __restrict__ q, 
     return;
   }
   const float inv_s = __frcp_rn(s);
-  const InvBracket inv2 = inv_bracket(s);
 #pragma unroll
   for (int c = 0; c < NCHUNK; ++c) {
     const int i = c * blockDim.x + threadIdx.x;

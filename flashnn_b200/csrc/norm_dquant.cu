@@ -65,17 +65,17 @@ struct NdParams {
   float eps;
 };
 
-// fp32 quotient n / s rounded half-to-even and saturated, in the low byte.  n * (1/s) is within 2 ulp of the
-// quotient; only when it lands next to a half-integer can the rounding differ, and then the division is redone.
-__device__ __forceinline__ uint32_t quantise_f32(float n, float s, float inv_s) {
-  float r = fminf(__fmul_rn(n, inv_s), 127.f);
-  float m = __fadd_rn(r, kRintMagic);
-  const float e = r - (m - kRintMagic);  // exact: the rounding error of the magic addition
-  if (fabsf(fabsf(e) - 0.5f) < 1e-4f) {
-    r = fminf(__fdiv_rn(n, s), 127.f);
-    m = __fadd_rn(r, kRintMagic);
-  }
-  return __float_as_uint(m);
+// fp32 quotient n / s rounded half-to-even and saturated, in the low byte.  Both ends of the bracketed reciprocal are
+// multiplied in and rounded to an integer by the magic addition; rounding is monotonic, so where the two agree the
+// exact quotient rounds to the same integer.  Where they differ (the quotient is within a few ulp of a half-integer,
+// or is not finite) a bit is ORed into `amb` and the caller redoes the chunk with quantise_f32_exact.
+__device__ __forceinline__ uint32_t quantise_f32(float n, const InvBracket& inv, uint32_t& amb) {
+  const uint32_t m = __float_as_uint(__fadd_rn(fminf(__fmul_rn(n, inv.lo), 127.f), kRintMagic));
+  amb |= m ^ __float_as_uint(__fadd_rn(__fmul_rn(n, inv.hi), kRintMagic));
+  return m;
+}
+__device__ __forceinline__ uint32_t quantise_f32_exact(float n, float s) {
+  return __float_as_uint(__fadd_rn(fminf(__fdiv_rn(n, s), 127.f), kRintMagic));
 }
 
 // LN = false: RMSNorm, LN = true: LayerNorm.  T: dtype of x, W: dtype of the norm parameters (T or float).
@@ -148,8 +148,9 @@ norm_dquant_kernel(const NdParams p) {
     const float amax = block_reduce<true>(fmaxf(lo_of<T>(m2), hi_of<T>(m2)), red);
     const float s = round_to<T>(__fdiv_rn(amax, 127.0f));
     if (threadIdx.x == 0) reinterpret_cast<T*>(p.scale)[row] = from_f32<T>(s);
-    const bool plain = !(s > 0.f);  // constant row and zero bias: 0 / 0, which the cast turns into 0
     const InvBracket inv2 = inv_bracket(s);
+    // constant row and zero bias (0 / 0, which the cast turns into 0), or a scale too small to invert
+    const bool plain = !(s > 0.f) || inv_overflowed(inv2);
 #pragma unroll
     for (int c = 0; c < NCHUNK; ++c) {
       const int i = c * blockDim.x + threadIdx.x;
@@ -192,18 +193,28 @@ norm_dquant_kernel(const NdParams p) {
     const float s = __fdiv_rn(amax, 127.f);
     if (threadIdx.x == 0) reinterpret_cast<T*>(p.scale)[row] = from_f32<T>(s);
     const bool zero = !(s > 0.f);  // every normalised value is 0: 0 / 0, which the cast turns into 0
-    const float inv_s = __frcp_rn(s);
+    const InvBracket inv2 = inv_bracket(s);
+    const uint32_t amb0 = inv_overflowed(inv2) ? 1u : 0u;
 #pragma unroll
     for (int c = 0; c < NCHUNK; ++c) {
       const int i = c * blockDim.x + threadIdx.x;
       if (i < nvec) {
         uint32_t o[2] = {0u, 0u};
         if (!zero) {
+          uint32_t amb = amb0;
 #pragma unroll
           for (int h = 0; h < 2; ++h) {
-            const uint32_t q0 = quantise_f32(v[c][4 * h], s, inv_s), q1 = quantise_f32(v[c][4 * h + 1], s, inv_s);
-            const uint32_t q2 = quantise_f32(v[c][4 * h + 2], s, inv_s), q3 = quantise_f32(v[c][4 * h + 3], s, inv_s);
+            const uint32_t q0 = quantise_f32(v[c][4 * h], inv2, amb), q1 = quantise_f32(v[c][4 * h + 1], inv2, amb);
+            const uint32_t q2 = quantise_f32(v[c][4 * h + 2], inv2, amb), q3 = quantise_f32(v[c][4 * h + 3], inv2, amb);
             o[h] = __byte_perm(__byte_perm(q0, q1, 0x0040), __byte_perm(q2, q3, 0x0040), 0x5410);
+          }
+          if (amb != 0) {
+#pragma unroll
+            for (int h = 0; h < 2; ++h) {
+              const uint32_t q0 = quantise_f32_exact(v[c][4 * h], s), q1 = quantise_f32_exact(v[c][4 * h + 1], s);
+              const uint32_t q2 = quantise_f32_exact(v[c][4 * h + 2], s), q3 = quantise_f32_exact(v[c][4 * h + 3], s);
+              o[h] = __byte_perm(__byte_perm(q0, q1, 0x0040), __byte_perm(q2, q3, 0x0040), 0x5410);
+            }
           }
         }
         __stcs(qr + i, make_uint2(o[0], o[1]));

@@ -47,6 +47,9 @@ __device__ __forceinline__ InvBracket inv_bracket(float s) {
   return {__fmul_rn(inv, 0.99999952316284f), __fmul_rn(inv, 1.00000047683716f)};  // 1 -+ 2^-21
 }
 
+// A subnormal scale has no finite reciprocal: such rows take the exact division throughout.
+__device__ __forceinline__ bool inv_overflowed(const InvBracket& inv) { return !(inv.hi <= 3.4028234e38f); }
+
 // min(t, 127) on a packed pair
 __device__ __forceinline__ uint32_t min2_127(uint32_t t2, __half) {
   const __half2 r = __hmin2(*reinterpret_cast<const __half2*>(&t2), __float2half2_rn(127.f));

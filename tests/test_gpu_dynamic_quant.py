@@ -80,3 +80,17 @@ def test_zero_rows_and_strided_rows():
     torch.cuda.synchronize()
     qo, so = O.dynamic_quantize(view.cpu().contiguous(), saturate=True)
     assert torch.equal(qd.cpu(), qo) and torch.equal(sd.cpu(), so)
+
+
+def test_rows_with_subnormal_scale():
+    """Rows whose scale is subnormal in bf16 (its reciprocal overflows fp32) take the exact division."""
+    g = torch.Generator().manual_seed(5)
+    x = (torch.rand(6, 512, generator=g) * 2 - 1)
+    x[:3] *= 1e-37
+    x[3:] *= 3e-39
+    x = x.to(torch.bfloat16)
+    x[1, :7] = 0
+    q, s = run(x)
+    qo, so = O.dynamic_quantize(x, saturate=True)
+    assert torch.equal(s.view(torch.int16), so.view(torch.int16))
+    assert torch.equal(q, qo)
