@@ -137,10 +137,12 @@ int launch_dq(const T* x, int64_t M, int64_t K, int64_t ldx, int8_t* q, int64_t 
     dq_row_generic_kernel<T><<<grid, kDqThreads, 0, st>>>(x, ldx, q, ldq, scale, int(K));
     return check_cuda(cudaGetLastError(), "dynamic_quant (generic) launch");
   }
-  // block size: the smallest of 256 / 512 / 1024 that keeps a thread at <= 4 chunks, if any does
+  // block size: eight chunks per thread where the row is long enough (few threads with much work in flight each,
+  // and several CTAs per SM in different phases, measured faster than wide blocks of four-chunk threads)
   const int nvec = int(K / 8);
-  int threads = ((nvec + 31) / 32) * 32;
-  if (threads > 256) threads = (nvec <= 256 * 4) ? 256 : (nvec <= 512 * 4) ? 512 : kDqMaxThreads;
+  int threads = (((nvec + 7) / 8 + 31) / 32) * 32;
+  if (threads < 64) threads = ((nvec + 31) / 32) * 32 < 64 ? ((nvec + 31) / 32) * 32 : 64;
+  if (threads > kDqMaxThreads) threads = kDqMaxThreads;
   const int nchunk = (nvec + threads - 1) / threads;
 #define FNN_DQ_CASE(N)                                                                     \
   dq_row_vec_kernel<T, N><<<grid, threads, 0, st>>>(x, ldx, q, ldq, scale, int(K))
