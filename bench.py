@@ -13,8 +13,10 @@ total work is fixed and the whole-job rate is total ops / slowest rank's time.
 Rank 0 prints one JSON line.  `value` is measured with the inputs resident in
 HBM; `e2e` is the same step through the public Python API with pinned host
 buffers copied in and the outputs copied back inside the timed region.
-`--impl reference` times the CPU restatement of the reference's torch path
-(oracle/) on a bounded sample of the same workload, on rank 0 only.
+`--impl reference` times the reference's own CPU (torch) implementation of the
+same layer on the host cores, on rank 0 only: the unmodified reference classes
+when the reference tree is installed under baseline/_ref (or mounted at
+/root/reference), else the restatement in oracle/ (reported as kind "port").
 """
 import argparse
 import json
@@ -47,6 +49,57 @@ def measured_peaks():
             p = json.load(f)
         return dict(hbm=p["hbm_gbs"], bf16=p["bf16_tflops"], bf16_sustained=p["bf16_tflops_sustained"], source="measured")
     return dict(hbm=6650.0, bf16=1590.0, bf16_sustained=1400.0, source="fallback")
+
+
+def find_reference():
+    """Directory that holds the reference project's own `flashnn` package, or None."""
+    for cand in (os.path.join(ROOT, "baseline", "_ref"), "/root/reference"):
+        if os.path.exists(os.path.join(cand, "flashnn", "quant_gemm.py")):
+            return cand
+    return None
+
+
+def load_reference_cpu():
+    """The unmodified reference with its torch backend selected: (module, None), or (None, reason)."""
+    path = find_reference()
+    if path is None:
+        return None, "no reference tree under baseline/_ref or /root/reference"
+    try:
+        for name in [n for n in sys.modules if n == "flashnn" or n.startswith("flashnn.")]:
+            del sys.modules[name]
+        sys.path.insert(0, path)
+        import flashnn  # the reference's package (this repository's alias of the same name sits later on the path)
+        if not os.path.abspath(flashnn.__file__).startswith(os.path.abspath(path)):
+            return None, f"`import flashnn` resolved to {flashnn.__file__}, not to the reference"
+        flashnn.set_use_triton(False)
+        return flashnn, None
+    except Exception as e:  # missing dependency of the reference on this host, ...
+        return None, f"importing the reference failed: {type(e).__name__}: {e}"
+
+
+def reference_cpu_layer(rows):
+    """(step function, kind, note): one pass of the FFN layer on the host CPU over the first `rows` tokens, through the
+    reference's own DynamicQuantize / GemmA8W8 classes (kind "reference") or, without them, the oracle port."""
+    from flashnn_b200 import workloads as W
+    w = W.ffn_layer(rows, 0, 1, HIDDEN, INTER)
+    ref, why = load_reference_cpu()
+    if ref is not None:
+        dq, gemm = ref.DynamicQuantize(), ref.GemmA8W8(torch.bfloat16)
+
+        def step():
+            qx, sx = dq(w["x"])
+            gemm(qx, w["w_gu"], sx.float(), w["col_gu"])  # the torch path multiplies the two scales: one dtype for both
+            qh, sh = dq(w["h"])
+            gemm(qh, w["w_dn"], sh.float(), w["col_dn"])
+        return step, "reference", "unmodified reference classes, set_use_triton(False), from " + os.path.relpath(find_reference(), ROOT)
+    from oracle import quant_oracle as O
+
+    def step():
+        qx, sx = O.dynamic_quantize(w["x"], saturate=False)
+        O.gemm_a8w8(qx, w["w_gu"], sx.float(), w["col_gu"], torch.bfloat16)
+        qh, sh = O.dynamic_quantize(w["h"], saturate=False)
+        O.gemm_a8w8(qh, w["w_dn"], sh.float(), w["col_dn"], torch.bfloat16)
+    return step, "port", "oracle port (" + why + ")"
 
 
 class ClockSampler:
@@ -106,16 +159,20 @@ class ClockSampler:
 class FfnShard:
     """This rank's column shard of the layer, resident on the device."""
 
-    def __init__(self, rank, world, device, tokens=TOKENS):
+    def __init__(self, rank, world, device, tokens=TOKENS, share=None):
+        """`share`: another FfnShard of the same rank whose device weights are reused (only the activations differ)."""
         import flashnn_b200
         from flashnn_b200 import workloads as W
         self.W = W
-        w = W.ffn_layer(tokens, rank, world, HIDDEN, INTER)
+        w = W.ffn_layer(tokens, rank, world, HIDDEN, INTER, weights=share is None)
         self.host = w
         self.device = device
         self.x, self.h = w["x"].to(device), w["h"].to(device)
-        self.w_gu, self.w_dn = w["w_gu"].to(device), w["w_dn"].to(device)
-        self.col_gu, self.col_dn = w["col_gu"].to(device), w["col_dn"].to(device)
+        if share is None:
+            self.w_gu, self.w_dn = w["w_gu"].to(device), w["w_dn"].to(device)
+            self.col_gu, self.col_dn = w["col_gu"].to(device), w["col_dn"].to(device)
+        else:
+            self.w_gu, self.w_dn, self.col_gu, self.col_dn = share.w_gu, share.w_dn, share.col_gu, share.col_dn
         self.dq = flashnn_b200.DynamicQuantize()
         self.gemm = flashnn_b200.GemmA8W8(torch.bfloat16)
         self.n_gu, self.n_dn = self.w_gu.shape[0], self.w_dn.shape[0]
@@ -203,30 +260,49 @@ def time_rotating_graph(fns, rounds, replays=5):
     return best
 
 
-def cpu_baseline_sample(host, sample_rows, reps_budget_s=12.0):
-    """The CPU restatement of the reference's torch path on the first `sample_rows` tokens of the
-    same workload (`host` = the full layer's CPU tensors): returns (TOPS, seconds per pass, threads)."""
+def cpu_baseline_sample(sample_rows, budget_s=25.0):
+    """The reference's CPU path on the first `sample_rows` tokens of the same workload:
+    returns (TOPS, seconds per pass, threads, kind, note)."""
     from flashnn_b200 import workloads as W
-    from oracle import quant_oracle as O
-    w = dict(host)
-    w["x"], w["h"] = host["x"][:sample_rows].contiguous(), host["h"][:sample_rows].contiguous()
-
-    def one_pass():
-        qx, sx = O.dynamic_quantize(w["x"], saturate=False)
-        O.gemm_a8w8(qx, w["w_gu"], sx.float(), w["col_gu"], torch.bfloat16)
-        qh, sh = O.dynamic_quantize(w["h"], saturate=False)
-        O.gemm_a8w8(qh, w["w_dn"], sh.float(), w["col_dn"], torch.bfloat16)
-
-    one_pass()  # warm-up
+    torch.set_num_threads(os.cpu_count() or 1)
+    step, kind, note = reference_cpu_layer(sample_rows)
+    step()  # warm-up
     times = []
     t_all = time.perf_counter()
-    while len(times) < 5 and (time.perf_counter() - t_all) < reps_budget_s:
+    while len(times) < 3 and (not times or (time.perf_counter() - t_all) + times[-1] < budget_s):
         t0 = time.perf_counter()
-        one_pass()
+        step()
         times.append(time.perf_counter() - t0)
     best = min(times)
     ops = W.a8w8_ops(sample_rows, N_GU, HIDDEN) + W.a8w8_ops(sample_rows, N_DN, INTER)
-    return ops / best / 1e12, best, torch.get_num_threads()
+    return ops / best / 1e12, best, torch.get_num_threads(), kind, note
+
+
+def int8_yardstick(device, flush_buf):
+    """The library int8 GEMM (torch._int_mm -> cuBLASLt) at 8192^3 on the same event harness: the measured int8
+    tensor-core rate of this GPU, as a burst (L2 flushed, launches timed one by one, best) and sustained
+    (back to back for about a second).  Returns a dict, or one with "error" if the library declines."""
+    try:
+        n = 8192
+        a = torch.randint(-127, 128, (n, n), dtype=torch.int8, device=device)
+        b = torch.randint(-127, 128, (n, n), dtype=torch.int8, device=device)
+        bt = b.t()  # [K, N] view with K contiguous: the layout the weights of this path have
+        ts = time_steps(lambda: torch._int_mm(a, bt), 10, 3, flush_buf)
+        burst = 2.0 * n ** 3 / (min(ts) * 1e-3) / 1e12
+        torch.cuda.synchronize()
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        reps = max(20, int(1.0 / (statistics.median(ts) * 1e-3)))
+        e0.record()
+        for _ in range(reps):
+            torch._int_mm(a, bt)
+        e1.record()
+        torch.cuda.synchronize()
+        sustained = 2.0 * n ** 3 * reps / (e0.elapsed_time(e1) * 1e-3) / 1e12
+        return dict(burst_tops=round(burst, 1), sustained_tops=round(sustained, 1), shape="8192^3",
+                    how="torch._int_mm (cuBLASLt int8), CUDA events; burst = best of 10 with L2 flushed, sustained = "
+                        f"{reps} launches back to back")
+    except Exception as e:
+        return dict(error=f"{type(e).__name__}: {e}")
 
 
 def run_native(args):
@@ -282,7 +358,13 @@ def run_native(args):
     value = total_ops / (ms_per_step * 1e-3) / 1e12
 
     # ---- end to end through the public API with host buffers ----
-    hx, hh = shard.host["x"].pin_memory(), shard.host["h"].pin_memory()
+    # Each rank uploads only its 1/G of the rows of x and h (pinned host memory -> device); with G > 1 the ranks then
+    # all-gather the rows over NVLink (NCCL) inside the timed region, so the host link carries every activation byte
+    # once per node instead of once per rank.  The outputs of this rank's columns go back to pinned host memory.
+    rows_per = TOKENS // world
+    r0 = rank * rows_per
+    hx = shard.host["x"][r0:r0 + rows_per].contiguous().pin_memory()
+    hh = shard.host["h"][r0:r0 + rows_per].contiguous().pin_memory()
     out_gu = torch.empty(TOKENS, shard.n_gu, dtype=torch.bfloat16).pin_memory()
     out_dn = torch.empty(TOKENS, shard.n_dn, dtype=torch.bfloat16).pin_memory()
 
@@ -291,27 +373,36 @@ def run_native(args):
     # launching stream before the step ends, so the CUDA events on that stream bracket all of it.
     s_in, s_out = torch.cuda.Stream(device), torch.cuda.Stream(device)
 
+    def gather_rows(part, k):
+        if world == 1:
+            return part
+        full = torch.empty(TOKENS, k, dtype=torch.bfloat16, device=device)
+        dist.all_gather_into_tensor(full, part)  # enqueued on the current stream
+        return full
+
     def e2e_step():
         main = torch.cuda.current_stream(device)
-        x = hx.to(device, non_blocking=True)  # first on the host-to-device engine: the first projection waits for it
-        s_in.wait_stream(main)                 # (orders the second upload behind the timed region's start only)
+        x_part = hx.to(device, non_blocking=True)  # first on the host-to-device engine: the first projection waits for it
+        s_in.wait_stream(main)                      # (orders the second upload behind the timed region's start only)
         with torch.cuda.stream(s_in):
-            h = hh.to(device, non_blocking=True)
+            h_part = hh.to(device, non_blocking=True)
+        x = gather_rows(x_part, HIDDEN)
         qx, sx = shard.dq(x)
         y_gu = shard.gemm(qx, shard.w_gu, sx, shard.col_gu)
         s_out.wait_stream(main)
         with torch.cuda.stream(s_out):
             out_gu.copy_(y_gu, non_blocking=True)
         main.wait_stream(s_in)
+        h = gather_rows(h_part, INTER)
         qh, sh = shard.dq(h)
         y_dn = shard.gemm(qh, shard.w_dn, sh, shard.col_dn)
         s_out.wait_stream(main)
         with torch.cuda.stream(s_out):
             out_dn.copy_(y_dn, non_blocking=True)
         main.wait_stream(s_out)
-        for t in (h, y_gu, y_dn):
+        for t in (y_gu, y_dn):
             t.record_stream(s_out)
-        h.record_stream(main)
+        h_part.record_stream(main)
 
     e2e_steps = max(3, min(args.steps, 10))
     barrier()
@@ -321,8 +412,9 @@ def run_native(args):
     if world > 1:
         dist.all_reduce(e2e_ms, op=dist.ReduceOp.MAX)
     e2e_ms_per_step = float(e2e_ms.item()) / e2e_steps
-    h2d = hx.numel() * 2 + hh.numel() * 2
-    d2h = out_gu.numel() * 2 + out_dn.numel() * 2
+    # whole-job bytes over the host link per step
+    h2d = world * (hx.numel() * 2 + hh.numel() * 2)
+    d2h = world * (out_gu.numel() * 2 + out_dn.numel() * 2)
 
     # ---- optional all-gather of the sharded outputs, timed apart ----
     allgather_ms = None
@@ -342,14 +434,23 @@ def run_native(args):
         allgather_ms = float(t.item())
         del full_gu, full_dn
 
+    # ---- the other half of the metric, at this N: decode-shaped work on this rank's column shard (all ranks) ----
+    sharded = sharded_decode_extras(rank, world, device, flush_buf, peaks, barrier, shard)
+
     line = None
     if rank == 0:
         # ---- per-kernel figures (rank 0's shard), each timed alone with CUDA events ----
+        yard = int8_yardstick(device, flush_buf)
         qx, sx = shard.dq(shard.x)
         gu_ms = statistics.median(time_steps(lambda: shard.gemm(qx, shard.w_gu, sx, shard.col_gu), 10, 3, flush_buf))
         gu_ops = W.a8w8_ops(TOKENS, shard.n_gu, HIDDEN)
         achieved = gu_ops / (gu_ms * 1e-3) / 1e12
-        int8_peak = 2.0 * peaks["bf16_sustained"]
+        # a launch timed alone is held against a burst figure: the measured int8 library GEMM when it ran, else twice
+        # the measured bf16 burst rate (int8 dense runs at twice the bf16 rate)
+        if "burst_tops" in yard:
+            int8_peak, peak_source = yard["burst_tops"], "measured in this run: torch._int_mm (cuBLASLt int8) 8192^3, best launch with L2 flushed"
+        else:
+            int8_peak, peak_source = 2.0 * peaks["bf16"], f"2 x {peaks['source']} burst bf16 cuBLAS rate (the int8 library GEMM did not run: {yard.get('error')})"
         # DRAM bytes of one gate/up launch on one GPU from profiles/a8w8_gate_up_4096x57344x8192.md (one ncu capture:
         # 619.2 MB read + 452.5 MB written); with G ranks the weight and output parts shrink by G, the activations do not
         a_bytes = TOKENS * HIDDEN
@@ -358,20 +459,32 @@ def run_native(args):
                         achieved=round(achieved, 1), peak=round(int8_peak, 1), unit="TFLOP/s",
                         frac=round(achieved / int8_peak, 4), traffic=traffic,
                         traffic_note="ncu capture at one GPU" + ("" if world == 1 else f", scaled to 1/{world} of the columns"),
-                        peak_source=f"2 x {peaks['source']} sustained bf16 cuBLAS rate (int8 dense runs at twice the bf16 rate; "
-                                    "no int8 figure is in MEASURED_PEAKS.json); ops are int8 multiply-adds counted as 2",
+                        peak_source=peak_source + "; ops are int8 multiply-adds counted as 2",
+                        frac_of_2x_measured_bf16_burst=round(achieved / (2.0 * peaks["bf16"]), 4),
                         nominal_frac=round(achieved / 4500.0, 4), launch_ms=round(gu_ms, 4))
-        extra = dict(kernel_ms=dict(a8w8_gate_up=round(gu_ms, 4)))
+        extra = dict(kernel_ms=dict(a8w8_gate_up=round(gu_ms, 4)), int8_yardstick=yard)
         dq_ms = statistics.median(time_steps(lambda: shard.dq(shard.x), 10, 3, flush_buf))
+        dqh_ms = statistics.median(time_steps(lambda: shard.dq(shard.h), 10, 3, flush_buf))
         extra["kernel_ms"]["dynamic_quant_4096x8192"] = round(dq_ms, 4)
+        extra["kernel_ms"]["dynamic_quant_4096x28672"] = round(dqh_ms, 4)
         extra["dynamic_quant_gbs"] = round(W.dynamic_quant_bytes(TOKENS, HIDDEN) / (dq_ms * 1e-3) / 1e9, 1)
-        extra.update(extra_shapes(device, flush_buf, peaks))
-        # ---- CPU baseline: the reference's torch path (restated in oracle/) on a bounded sample ----
+        extra["dynamic_quant_28672_gbs"] = round(W.dynamic_quant_bytes(TOKENS, INTER) / (dqh_ms * 1e-3) / 1e9, 1)
+        qh, sh = shard.dq(shard.h)
+        dn_ms = statistics.median(time_steps(lambda: shard.gemm(qh, shard.w_dn, sh, shard.col_dn), 10, 3, flush_buf))
+        extra["kernel_ms"]["a8w8_down"] = round(dn_ms, 4)
+        extra["a8w8_down_tops"] = round(W.a8w8_ops(TOKENS, shard.n_dn, INTER) / (dn_ms * 1e-3) / 1e12, 1)
+        extra["sharded_decode"] = sharded
+        if world == 1:
+            extra.update(extra_shapes(device, flush_buf, peaks))
+            if not args.no_triton_reference:
+                extra["reference_triton"] = reference_triton_figures()
+        # ---- CPU baseline: the reference's torch path on the host cores ----
         cpu = None
         if world == 1:
-            tops, secs, threads = cpu_baseline_sample(shard.host, args.cpu_rows)
-            cpu = dict(value=round(tops, 4), unit="TOPS", cores=threads, kind="port",
-                       sample=f"first {args.cpu_rows} of {TOKENS} tokens, full layer, best of <=5 passes, {secs:.2f} s per pass")
+            tops, secs, threads, kind, note = cpu_baseline_sample(args.cpu_rows)
+            cpu = dict(value=round(tops, 4), unit="TOPS", cores=threads, kind=kind,
+                       sample=(f"first {args.cpu_rows} of {TOKENS} tokens" if args.cpu_rows < TOKENS else f"all {TOKENS} tokens")
+                              + f", full layer, best of <=3 passes, {secs:.2f} s per pass; {note}")
         line = {
             "metric": "a8w8_ffn_layer_tops", "value": round(value, 2), "unit": "TOPS", "n_gpus": world,
             "steps": args.steps, "warmup": args.warmup, "ms_per_step": round(ms_per_step, 4),
@@ -382,8 +495,10 @@ def run_native(args):
                        "timing": "CUDA events per step on the launching stream, max over ranks"},
             "e2e": {"value": round(total_ops / (e2e_ms_per_step * 1e-3) / 1e12, 3), "unit": "TOPS",
                     "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": d2h, "ms_per_step": round(e2e_ms_per_step, 3),
-                    "note": "pinned host x,h copied in, both outputs copied back, every step (copies on side streams, "
-                            "joined into the timed stream before the step ends); weights stay resident"},
+                    "note": "every step: each rank copies its 1/G of the rows of x and h up from pinned host memory" +
+                            ("" if world == 1 else ", the ranks all-gather them over NVLink (NCCL, inside the timed region)") +
+                            ", and copies its output columns back (copies on side streams, joined into the timed stream "
+                            "before the step ends); byte counts are whole-job; weights stay resident"},
             "gpu_launches": 4 * args.steps,
             "clocks": clocks, "roofline": roofline, "cpu_baseline": cpu,
             "allgather_ms": allgather_ms, "wall_s": round(wall, 3), "extra": extra,
@@ -393,6 +508,139 @@ def run_native(args):
         dist.destroy_process_group()
     if line is not None:
         print(json.dumps(line), flush=True)
+
+
+def sharded_decode_extras(rank, world, device, flush_buf, peaks, barrier, layer):
+    """The decode-shaped half of the metric on this rank's column shard, at this number of GPUs: the A16W4 GEMV
+    (N = 28672 / G columns, K = 8192, group 128) at M = 1, 4, 16 and the A8W8 FFN layer at M = 1 and 64.  Every rank
+    runs its shard; times are the max over ranks, rates are whole-job (all ranks' bytes / that time)."""
+    import torch.distributed as dist
+    import flashnn_b200
+    from flashnn_b200 import workloads as W
+
+    def max_over_ranks(ms):
+        t = torch.tensor([ms], dtype=torch.float64, device=device)
+        if world > 1:
+            dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        return float(t.item())
+
+    out = {}
+    n_full, k, group = 28672, 8192, 128
+    n_shard = n_full // world
+    wo = flashnn_b200.GemmWeightOnly(torch.bfloat16)
+    w = W.a16w4_decode(16, n_full, k, group)
+    qw = w["qw"][rank * n_shard // 2:(rank + 1) * n_shard // 2].contiguous()
+    sc = w["scale"][:, rank * n_shard:(rank + 1) * n_shard].contiguous()
+    copies = max(4, min(32, -(-(300 << 20) // max(1, qw.numel()))))  # rotating weight copies that together exceed L2
+    qws = [qw.to(device) for _ in range(copies)]
+    scs = [sc.to(device) for _ in range(copies)]
+    for m_ in (1, 4, 16):
+        x = w["x"][:m_].contiguous().to(device)
+        calls = [(lambda q=q, s_=s_: wo(x, q, s_)) for q, s_ in zip(qws, scs)]
+        barrier()
+        ms = max_over_ranks(time_rotating_graph(calls, rounds=max(2, 40 // copies)))
+        gbs = world * W.a16w4_bytes(m_, n_shard, k, group) / ms / 1e6
+        out[f"a16w4_gemv_m{m_}"] = dict(ms=round(ms, 4), gbs_whole_job=round(gbs, 1), gbs_per_gpu=round(gbs / world, 1),
+                                        frac_of_measured_hbm=round(gbs / world / peaks["hbm"], 4), columns_per_rank=n_shard)
+    del qws, scs
+    out["a16w4_gemv_timing"] = (f"{copies} rotating weight copies per rank (> L2 together), calls captured in one CUDA graph "
+                                "and replayed, best of 5, max over ranks")
+    # decode-shaped A8W8 FFN layer on this rank's shard: DynamicQuant + gate/up, DynamicQuant + down
+    for m_ in (1, 64):
+        shard = FfnShard(rank, world, device, tokens=m_, share=layer)
+        barrier()
+        ts = time_steps(shard.step, 10, 3, flush_buf)
+        ms = max_over_ranks(statistics.median(ts))
+        byts = world * (W.a8w8_bytes(m_, shard.n_gu, HIDDEN) + W.a8w8_bytes(m_, shard.n_dn, INTER)
+                        + W.dynamic_quant_bytes(m_, HIDDEN) + W.dynamic_quant_bytes(m_, INTER))
+        out[f"a8w8_ffn_m{m_}"] = dict(ms=round(ms, 4), gbs_whole_job=round(byts / ms / 1e6, 1),
+                                      frac_of_measured_hbm=round(byts / ms / 1e6 / world / peaks["hbm"], 4),
+                                      note="four launches per step from Python with L2 flushed before each step, max over ranks")
+        del shard
+    return out
+
+
+def reference_triton_figures(timeout_s=900):
+    """The reference's own Triton kernels on this GPU (secondary baseline), timed by `bench.py --case ref_triton` in a
+    child process so that a JIT failure or a crash of that code cannot take the benchmark down."""
+    if find_reference() is None:
+        return dict(unavailable="no reference tree under baseline/_ref or /root/reference")
+    try:
+        r = subprocess.run([sys.executable, os.path.abspath(__file__), "--case", "ref_triton"], capture_output=True, text=True,
+                           timeout=timeout_s)
+    except subprocess.TimeoutExpired:
+        return dict(unavailable=f"the reference's Triton kernels did not finish within {timeout_s} s")
+    for ln in reversed(r.stdout.strip().splitlines()):
+        if ln.startswith("{"):
+            return json.loads(ln)
+    return dict(unavailable="no result line", rc=r.returncode, stderr_tail=r.stderr[-600:])
+
+
+def run_ref_triton(args):
+    """Times the unmodified reference's Triton path (set_use_triton(True)) with the same CUDA-event harness:
+    GemmA8W8 at 8192^3 and at the prefill chain's 4096 x 11008 x 4096, DynamicQuantize at 4096 x 4096 and
+    4096 x 8192, GemmWeightOnly A16W4 (group 128) at M = 1, N = 28672, K = 8192.  Each case reports its time or
+    the exception text."""
+    from flashnn_b200 import workloads as W
+    device = torch.device("cuda", 0)
+    torch.cuda.set_device(device)
+    path = find_reference()
+    for name in [n for n in sys.modules if n == "flashnn" or n.startswith("flashnn.")]:
+        del sys.modules[name]
+    sys.path.insert(0, path)
+    out = {"source": os.path.relpath(path, ROOT)}
+    try:
+        import flashnn
+        import triton
+        flashnn.set_use_triton(True)
+        out["triton_version"] = triton.__version__
+    except Exception as e:
+        print(json.dumps({"unavailable": f"import failed: {type(e).__name__}: {e}"}), flush=True)
+        return
+    flush_buf = torch.empty(256 << 20, dtype=torch.uint8, device=device)
+
+    def timed(label, make):
+        try:
+            fn, work, unit = make()
+            ts = time_steps(fn, 10, 3, flush_buf)
+            ms = statistics.median(ts)
+            out[label] = dict(ms=round(ms, 4), rate=round(work / (ms * 1e-3), 1), unit=unit)
+        except Exception as e:
+            out[label] = dict(error=f"{type(e).__name__}: {str(e)[:300]}")
+        torch.cuda.synchronize()
+
+    def a8w8(m, n, k):
+        def make():
+            a, b = W.rand_int8((m, k), 0).to(device), W.rand_int8((n, k), 1).to(device)
+            row = W.rand_uniform((m,), 2, 0.005, 0.02, torch.bfloat16).to(device)  # the Triton launcher wants scale dtype == out dtype
+            col = W.rand_uniform((n,), 3, 0.001, 0.01, torch.bfloat16).to(device)
+            op = flashnn.GemmA8W8(torch.bfloat16)
+            return (lambda: op(a, b, row, col)), W.a8w8_ops(m, n, k) / 1e12, "TOPS"
+        return make
+
+    def dq(m, k):
+        def make():
+            x = W.rand_normal((m, k), 0, torch.bfloat16, outliers=True).to(device)
+            op = flashnn.DynamicQuantize()
+            return (lambda: op(x)), W.dynamic_quant_bytes(m, k) / 1e9, "GB/s"
+        return make
+
+    def a16w4(m):
+        def make():
+            w = W.a16w4_decode(m)
+            x, qw, sc = w["x"].to(device), w["qw"].to(device), w["scale"].to(device)
+            op = flashnn.GemmWeightOnly(torch.bfloat16)
+            return (lambda: op(x, qw, sc)), W.a16w4_bytes(m, 28672, 8192, 128) / 1e9, "GB/s"
+        return make
+
+    timed("gemm_a8w8_8192x8192x8192", a8w8(8192, 8192, 8192))
+    timed("gemm_a8w8_4096x11008x4096", a8w8(4096, 11008, 4096))
+    timed("dynamic_quant_4096x4096", dq(4096, 4096))
+    timed("dynamic_quant_4096x8192", dq(4096, 8192))
+    timed("gemm_a16w4_m1_28672x8192", a16w4(1))
+    timed("gemm_a16w4_m16_28672x8192", a16w4(16))
+    out["timing"] = "CUDA events per call, L2 flushed before each, median of 10 after 3 warm-up calls (JIT compile excluded)"
+    print(json.dumps(out), flush=True)
 
 
 def extra_shapes(device, flush_buf, peaks):
@@ -466,18 +714,20 @@ def run_reference(args):
     if int(os.environ.get("RANK", "0")) != 0:
         return
     from flashnn_b200 import workloads as W
-    from oracle import quant_oracle as O
     torch.set_num_threads(os.cpu_count() or 1)  # torchrun pins OMP_NUM_THREADS to 1; this arm runs on rank 0 alone
-    rows = args.cpu_rows
-    w = W.ffn_layer(rows, 0, 1, HIDDEN, INTER)
-
-    def step():
-        qx, sx = O.dynamic_quantize(w["x"], saturate=False)
-        O.gemm_a8w8(qx, w["w_gu"], sx.float(), w["col_gu"], torch.bfloat16)
-        qh, sh = O.dynamic_quantize(w["h"], saturate=False)
-        O.gemm_a8w8(qh, w["w_dn"], sh.float(), w["col_dn"], torch.bfloat16)
-
-    for _ in range(args.warmup):
+    rows = min(args.cpu_rows, TOKENS)
+    step, kind, note = reference_cpu_layer(rows)
+    t0 = time.perf_counter()
+    step()  # first warm-up step, also the probe for the size of the sample
+    probe = time.perf_counter() - t0
+    # bounded: the whole run (warm-up + timed steps) should end within about four minutes
+    while rows > 64 and probe * (args.steps + args.warmup) > 240.0:
+        rows //= 2
+        step, kind, note = reference_cpu_layer(rows)
+        t0 = time.perf_counter()
+        step()
+        probe = time.perf_counter() - t0
+    for _ in range(max(0, args.warmup - 1)):
         step()
     t0 = time.perf_counter()
     for _ in range(args.steps):
@@ -486,14 +736,15 @@ def run_reference(args):
     ops = W.a8w8_ops(rows, N_GU, HIDDEN) + W.a8w8_ops(rows, N_DN, INTER)
     value = ops / dt / 1e12
     threads = torch.get_num_threads()
-    sample = f"each step = first {rows} of {TOKENS} tokens through the full layer on the host CPU"
+    sample = (f"each step = all {TOKENS} tokens" if rows == TOKENS else f"each step = first {rows} of {TOKENS} tokens") + \
+        f" through the full layer on the host CPU; {note}"
     print(json.dumps({
         "metric": "a8w8_ffn_layer_tops", "value": round(value, 4), "unit": "TOPS", "n_gpus": args.gpus, "steps": args.steps,
         "warmup": args.warmup, "ms_per_step": round(dt * 1e3, 3), "higher_is_better": True, "scaling": "strong",
         "vs_baseline": None, "dtype": "int8 operands multiplied in fp32 (the reference's torch path)", "data": "synthetic",
         "impl": "reference",
         "config": {"workload": WORKLOAD, "tokens": TOKENS, "sample": sample},
-        "cpu_baseline": {"value": round(value, 4), "unit": "TOPS", "cores": threads, "kind": "port", "sample": sample},
+        "cpu_baseline": {"value": round(value, 4), "unit": "TOPS", "cores": threads, "kind": kind, "sample": sample},
         "e2e": {"value": round(value, 4), "unit": "TOPS", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
         "gpu_launches": 0,
     }), flush=True)
@@ -546,8 +797,7 @@ def run_case(args):
         work, unit = W.dynamic_quant_bytes(m, k) / 1e9, "GB/s"
     elif name == "moe":
         # Mixtral-8x7B-shaped expert layer (gate/up): E = 8, top-2, K = 4096 -> N = 28672, int8 weights
-        sys.path.insert(0, os.path.dirname(os.path.abspath(__file__)))
-        from tests.moe_util import make_moe_case
+        from flashnn_b200.workloads import make_moe_case
         m, n, k = args.m or 64, args.n or 28672, args.k or 4096
         e, top_k, bm = 8, 2, (16 if m <= 64 else 128)
         c = {kk: v.to(device) for kk, v in make_moe_case(m, e, n, k, top_k, bm, seed=0).items()}
@@ -579,13 +829,17 @@ def main():
     ap.add_argument("--steps", type=int, default=20)
     ap.add_argument("--warmup", type=int, default=5)
     ap.add_argument("--impl", choices=["native", "reference"], default="native")
-    ap.add_argument("--cpu-rows", type=int, default=256, help="tokens in the CPU-baseline sample")
-    ap.add_argument("--case", choices=["a8w8", "gemv", "gemv8", "dq", "wo", "rmsdq", "lndq", "moe"], help="run one kernel only (profiling / A-B timing)")
+    ap.add_argument("--cpu-rows", type=int, default=TOKENS, help="tokens in the CPU-baseline sample (default: the whole workload)")
+    ap.add_argument("--no-triton-reference", action="store_true", help="skip timing the reference's Triton kernels (extra.reference_triton)")
+    ap.add_argument("--case", choices=["a8w8", "gemv", "gemv8", "dq", "wo", "wog", "rmsdq", "lndq", "moe", "ref_triton", "sweep"],
+                    help="run one kernel only (profiling / A-B timing), the reference's Triton kernels, or the reference's shape sweep")
     ap.add_argument("--m", type=int)
     ap.add_argument("--n", type=int)
     ap.add_argument("--k", type=int)
     args = ap.parse_args()
-    if args.case:
+    if args.case == "ref_triton":
+        run_ref_triton(args)
+    elif args.case:
         run_case(args)
     elif args.impl == "reference":
         run_reference(args)

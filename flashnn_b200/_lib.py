@@ -93,6 +93,7 @@ def check(status: int):
 
 
 OPT_STATIC_WEIGHTS = 1
+OPT_TEST_STALL_US = 2  # test hook, see include/flashnn_b200.h
 
 
 def set_option(option: int, value: int) -> None:

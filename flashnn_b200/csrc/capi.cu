@@ -53,8 +53,10 @@ int check_cuda(cudaError_t e, const char* what) {
 
 namespace {
 std::atomic<int> g_opt_static_weights{0};
+std::atomic<int> g_opt_test_stall_us{0};
 }
 bool opt_static_weights() { return g_opt_static_weights.load(std::memory_order_relaxed) != 0; }
+int opt_test_stall_us() { return g_opt_test_stall_us.load(std::memory_order_relaxed); }
 
 int* device_status_word() {
   const int dev = current_device();
@@ -111,11 +113,18 @@ extern "C" int fnn_set_option(int option, int value) {
     fnn::g_opt_static_weights.store(value != 0, std::memory_order_relaxed);
     return FNN_OK;
   }
+  if (option == FNN_OPT_TEST_STALL_US) {
+    if (value < 0 || value > 1000000)
+      return fnn::fail(FNN_ERR_UNSUPPORTED, "fnn_set_option: FNN_OPT_TEST_STALL_US takes 0 .. 1000000 microseconds (got %d)", value);
+    fnn::g_opt_test_stall_us.store(value, std::memory_order_relaxed);
+    return FNN_OK;
+  }
   return fnn::fail(FNN_ERR_UNSUPPORTED, "fnn_set_option: unknown option %d", option);
 }
 
 extern "C" int fnn_get_option(int option) {
   if (option == FNN_OPT_STATIC_WEIGHTS) return fnn::g_opt_static_weights.load(std::memory_order_relaxed);
+  if (option == FNN_OPT_TEST_STALL_US) return fnn::g_opt_test_stall_us.load(std::memory_order_relaxed);
   return -1;
 }
 

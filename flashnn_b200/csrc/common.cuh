@@ -20,6 +20,7 @@ int check_cuda(cudaError_t e, const char* what);
 int* device_status_word();  // device address of this device's status word, or nullptr
 int sm_count();
 bool opt_static_weights();  // FNN_OPT_STATIC_WEIGHTS
+int opt_test_stall_us();    // FNN_OPT_TEST_STALL_US (0 unless a test set it)
 // 2-D tiled tensor map over a row-major [rows, cols] matrix of 1- or 2-byte elements (row pitch in bytes);
 // the box is box_cols x box_rows elements, out-of-range elements read as zero.
 int make_tmap_2d(CUtensorMap* m, int elem_bytes, const void* base, int64_t rows, int64_t cols, int64_t pitch_bytes,
@@ -137,7 +138,7 @@ constexpr uint64_t kWaitLimitNs = 2000000000ull;
 // Bounded wait: returns false when the limit ran out or another role already
 // reported a failure through *abort_flag (shared memory).
 __device__ __forceinline__ bool mbar_wait_bounded(uint64_t* bar, uint32_t parity,
-                                                  volatile int* abort_flag) {
+                                                  volatile int* abort_flag, uint64_t limit_ns = kWaitLimitNs) {
   uint32_t done;
   const uint32_t addr = smem_u32(bar);
   asm volatile(
@@ -161,7 +162,7 @@ __device__ __forceinline__ bool mbar_wait_bounded(uint64_t* bar, uint32_t parity
     if (done) return true;
     if ((++spins & 0xff) == 0) {
       if (*abort_flag != 0) return false;
-      if (global_timer_ns() - t0 > kWaitLimitNs) return false;
+      if (global_timer_ns() - t0 > limit_ns) return false;
     }
   }
 }

@@ -24,18 +24,6 @@ namespace {
 constexpr int kDqThreads = 256;     // block size of the generic kernel
 constexpr int kDqMaxThreads = 1024;  // largest block of the vector kernel
 
-__device__ __forceinline__ float block_max(float v, float* red) {
-#pragma unroll
-  for (int o = 16; o > 0; o >>= 1) v = fmaxf(v, __shfl_xor_sync(0xffffffffu, v, o));
-  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, nwarp = (blockDim.x + 31) >> 5;
-  if (lane == 0) red[warp] = v;
-  __syncthreads();
-  v = (lane < nwarp) ? red[lane] : 0.f;
-#pragma unroll
-  for (int o = 16; o > 0; o >>= 1) v = fmaxf(v, __shfl_xor_sync(0xffffffffu, v, o));
-  return v;
-}
-
 // Vector path: K % 8 == 0, 16-byte aligned rows in, 8-byte aligned rows out.
 // NCHUNK = 16-byte chunks per thread (row held in registers).
 template <typename T, int NCHUNK>
@@ -54,13 +42,14 @@ dq_row_vec_kernel(const T* __restrict__ x, int64_t ldx, int8_t* __restrict__ q, 
     v[c] = (i < nvec) ? __ldcs(xr + i) : make_uint4(0, 0, 0, 0);
     m2 = absmax2(absmax2(absmax2(absmax2(m2, v[c].x, T()), v[c].y, T()), v[c].z, T()), v[c].w, T());
   }
-  float amax = block_max(fmaxf(lo_of<T>(m2), hi_of<T>(m2)), red);
+  const float amax = block_absmax_keep_nan(max_keep_nan(lo_of<T>(m2), hi_of<T>(m2)), red);
   const float s = round_to<T>(__fdiv_rn(amax, 127.0f));
   if (threadIdx.x == 0) scale[row] = __float2half_rn(s);
   uint2* qr = reinterpret_cast<uint2*>(q + row * ldq);
   const InvBracket inv2 = inv_bracket(s);
-  if (!(s > 0.f) || inv_overflowed(inv2)) {
-    // all-zero row, a scale that underflowed to zero in T, or one too small to invert: the plain form
+  if (!usable_scale(s) || inv_overflowed(inv2)) {
+    // all-zero row, a scale that underflowed to zero in T, one too small to invert, or a row with a NaN or an
+    // infinity in it (scale NaN / infinite): the plain form, in which a NaN quotient is written as 0
 #pragma unroll
     for (int c = 0; c < NCHUNK; ++c) {
       const int i = c * blockDim.x + threadIdx.x;
@@ -117,8 +106,8 @@ dq_row_generic_kernel(const T* __restrict__ x, int64_t ldx, int8_t* __restrict__
   const int64_t row = blockIdx.x;
   const T* xr = x + row * ldx;
   float amax = 0.f;
-  for (int i = threadIdx.x; i < K; i += blockDim.x) amax = fmaxf(amax, fabsf(to_f32(xr[i])));
-  amax = block_max(amax, red);
+  for (int i = threadIdx.x; i < K; i += blockDim.x) amax = max_keep_nan(amax, to_f32(xr[i]));
+  amax = block_absmax_keep_nan(amax, red);
   const float s = round_to<T>(__fdiv_rn(amax, 127.0f));
   if (threadIdx.x == 0) scale[row] = __float2half_rn(s);
   int8_t* qr = q + row * ldq;

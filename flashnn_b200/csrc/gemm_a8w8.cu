@@ -41,6 +41,8 @@ struct A8W8Params {
   int M, N, K;
   int tiles_m, tiles_n, k_blocks;
   int* status;  // device status word
+  unsigned long long wait_ns;  // longest time one wait may take (single-CTA kernel; kWaitLimitNs unless a test shortened it)
+  int skip_kb;                 // -1, or (test hook) the K block of a CTA's first tile whose loads are left out
   // Fused-MoE mode (kernel template flag MOE): A is the expert-sorted copy of the token rows [EM, K], B is the
   // stack of expert weights seen as [E * N, K]; a tile is `tile_rows` sorted slots of one expert x BN channels.
   const int32_t* sorted_ids;       // [EM] flat (token * top_k + choice) index per slot, >= num_valid for padding
@@ -215,13 +217,13 @@ a8w8_umma_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_consta
       // fused MoE: the tile's weights are rows [e * N + nb * BN, ...) of the expert stack
       const int b_row = nb * BN + (MOE ? __ldg(p.expert_ids + (mb * tile_rows) / p.block_m) * p.N : 0);
       for (int kb = 0; kb < p.k_blocks; ++kb) {
-        ok = mbar_wait_bounded(&empty_bar[stage], phase ^ 1, abort_flag);
+        ok = mbar_wait_bounded(&empty_bar[stage], phase ^ 1, abort_flag, p.wait_ns);
         ok = __all_sync(0xffffffffu, ok);
         if (!ok) {
           if (leader) report(p.status, abort_flag, DEV_TIMEOUT_PRODUCER);
           break;
         }
-        if (leader) {
+        if (leader && !(kb == p.skip_kb && t == int(blockIdx.x))) {  // (test hook: one K block's loads left out)
           uint8_t* sa = smem + stage * L::kStageBytes;
           mbar_expect_tx(&full_bar[stage], L::kStageBytes);
           tma_load_2d(sa, &tmap_a, &full_bar[stage], kb * kBK, mb * tile_rows);
@@ -238,7 +240,7 @@ a8w8_umma_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_consta
       int none = 0;
       const long long first = issued > STAGES ? issued - STAGES : 0;
       for (long long i = first; i < issued; ++i)
-        if (!mbar_wait_bounded(&full_bar[i % STAGES], uint32_t((i / STAGES) & 1), &none)) {
+        if (!mbar_wait_bounded(&full_bar[i % STAGES], uint32_t((i / STAGES) & 1), &none, p.wait_ns)) {
           report(p.status, abort_flag, DEV_TIMEOUT_DRAIN);
           break;
         }
@@ -261,7 +263,7 @@ a8w8_umma_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_consta
       const int buf = local & 1;
       const uint32_t acc_phase = (local >> 1) & 1;
       ++local;
-      ok = mbar_wait_bounded(&tmem_empty_bar[buf], acc_phase ^ 1, abort_flag);
+      ok = mbar_wait_bounded(&tmem_empty_bar[buf], acc_phase ^ 1, abort_flag, p.wait_ns);
       ok = __all_sync(0xffffffffu, ok);
       if (!ok) {
         if (leader) report(p.status, abort_flag, DEV_TIMEOUT_MMA);
@@ -270,7 +272,7 @@ a8w8_umma_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_consta
       tc_fence_after();
       const uint32_t tmem_d = tmem_base + buf * BN;
       for (int kb = 0; kb < p.k_blocks; ++kb) {
-        ok = mbar_wait_bounded(&full_bar[stage], phase, abort_flag);
+        ok = mbar_wait_bounded(&full_bar[stage], phase, abort_flag, p.wait_ns);
         ok = __all_sync(0xffffffffu, ok);
         if (!ok) {
           if (leader) report(p.status, abort_flag, DEV_TIMEOUT_MMA);
@@ -297,7 +299,7 @@ a8w8_umma_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_consta
     if (leader && issued_any) {
       int none = 0;
       tc_commit(drain_bar);
-      if (!mbar_wait_bounded(drain_bar, 0, &none)) report(p.status, abort_flag, DEV_TIMEOUT_DRAIN);
+      if (!mbar_wait_bounded(drain_bar, 0, &none, p.wait_ns)) report(p.status, abort_flag, DEV_TIMEOUT_DRAIN);
     }
   } else {
     // -------------------------------- epilogue --------------------------------
@@ -337,7 +339,7 @@ a8w8_umma_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_consta
       }
       __syncwarp();
 
-      ok = mbar_wait_bounded(&tmem_full_bar[buf], acc_phase, abort_flag);
+      ok = mbar_wait_bounded(&tmem_full_bar[buf], acc_phase, abort_flag, p.wait_ns);
       ok = __all_sync(0xffffffffu, ok);
       if (!ok) {
         if (lane == 0) report(p.status, abort_flag, DEV_TIMEOUT_EPILOGUE);
@@ -624,19 +626,24 @@ int launch_umma(const int8_t* a, int64_t lda, const int8_t* b, int64_t ldb, A8W8
   static_assert(L::kStageBytes % 1024 == 0 && L::kABytes % 1024 == 0, "tiles must stay 1024-byte aligned");
   auto kern = a8w8_umma_kernel<OutT, BN, STAGES, false, AROWS>;
   static std::once_flag once[64];
+  static cudaError_t attr_err[64];  // per device, so that a failure is reported on every call and not only the first
   int dev = 0;
   cudaGetDevice(&dev);
-  cudaError_t attr_err = cudaSuccess;
-  std::call_once(once[dev & 63], [&] {
-    attr_err = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, L::kDynamicBytes);
+  dev &= 63;
+  std::call_once(once[dev], [&] {
+    attr_err[dev] = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, L::kDynamicBytes);
   });
-  if (attr_err != cudaSuccess) return check_cuda(attr_err, "cudaFuncSetAttribute(a8w8)");
+  if (attr_err[dev] != cudaSuccess) return check_cuda(attr_err[dev], "cudaFuncSetAttribute(a8w8)");
   CUtensorMap ta, tb;
   if (int e = make_tmap_i8(&ta, a, p.M, p.K, lda, AROWS)) return e;
   if (int e = make_tmap_i8(&tb, b, p.N, p.K, ldb, BN)) return e;
   p.tiles_m = (p.M + kBM - 1) / kBM;
   p.tiles_n = (p.N + BN - 1) / BN;
   p.k_blocks = (p.K + kBK - 1) / kBK;
+  if (const int stall_us = opt_test_stall_us()) {  // test hook: make one wait run out quickly
+    p.wait_ns = 1000ull * unsigned(stall_us);
+    p.skip_kb = p.k_blocks > 1 ? 1 : 0;
+  }
   const int tiles = p.tiles_m * p.tiles_n;
   const int grid = tiles < sm_count() ? tiles : sm_count();
   kern<<<grid, kThreads, L::kDynamicBytes, st>>>(ta, tb, p);
@@ -658,13 +665,14 @@ int launch_pair(const int8_t* a, int64_t lda, const int8_t* b, int64_t ldb, A8W8
   static_assert(L::kDynamicBytes <= 227 * 1024, "shared memory budget");
   auto kern = a8w8_umma_pair_kernel<OutT, STAGES>;
   static std::once_flag once[64];
+  static cudaError_t attr_err[64];  // per device, so that a failure is reported on every call and not only the first
   int dev = 0;
   cudaGetDevice(&dev);
-  cudaError_t attr_err = cudaSuccess;
-  std::call_once(once[dev & 63], [&] {
-    attr_err = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, L::kDynamicBytes);
+  dev &= 63;
+  std::call_once(once[dev], [&] {
+    attr_err[dev] = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, L::kDynamicBytes);
   });
-  if (attr_err != cudaSuccess) return check_cuda(attr_err, "cudaFuncSetAttribute(a8w8 pair)");
+  if (attr_err[dev] != cudaSuccess) return check_cuda(attr_err[dev], "cudaFuncSetAttribute(a8w8 pair)");
   CUtensorMap ta, tb;
   if (int e = make_tmap_i8(&ta, a, p.M, p.K, lda, kBM)) return e;
   if (int e = make_tmap_i8(&tb, b, p.N, p.K, ldb, L::kBN / 2)) return e;
@@ -729,13 +737,14 @@ int launch_moe(const int8_t* a_sorted, int64_t EM, const int8_t* b, int64_t E, A
   static_assert(L::kDynamicBytes <= 227 * 1024, "shared memory budget");
   auto kern = a8w8_umma_kernel<OutT, BN, STAGES, true, AROWS>;
   static std::once_flag once[64];
+  static cudaError_t attr_err[64];  // per device, so that a failure is reported on every call and not only the first
   int dev = 0;
   cudaGetDevice(&dev);
-  cudaError_t attr_err = cudaSuccess;
-  std::call_once(once[dev & 63], [&] {
-    attr_err = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, L::kDynamicBytes);
+  dev &= 63;
+  std::call_once(once[dev], [&] {
+    attr_err[dev] = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, L::kDynamicBytes);
   });
-  if (attr_err != cudaSuccess) return check_cuda(attr_err, "cudaFuncSetAttribute(fused moe a8w8)");
+  if (attr_err[dev] != cudaSuccess) return check_cuda(attr_err[dev], "cudaFuncSetAttribute(fused moe a8w8)");
   CUtensorMap ta, tb;
   if (int e = make_tmap_i8(&ta, a_sorted, EM, p.K, p.K, AROWS)) return e;  // a block's own slots (and a few more)
   if (int e = make_tmap_i8(&tb, b, E * p.N, p.K, p.K, BN)) return e;
@@ -812,6 +821,7 @@ extern "C" int fnn_fused_moe_a8w8(const int8_t* a, int64_t lda, const int8_t* b,
   p.ldo = ldo; p.ldacc = 0; p.row_dtype = row_dtype; p.col_dtype = col_dtype;
   p.M = int(num_valid_tokens); p.N = int(N); p.K = int(K);
   p.status = device_status_word();
+  p.wait_ns = kWaitLimitNs; p.skip_kb = -1;
   p.sorted_ids = sorted_token_ids; p.expert_ids = expert_ids; p.num_post_padded = num_tokens_post_padded;
   p.topk_w = topk_weights; p.topk_w_dtype = topk_dtype; p.top_k = top_k; p.block_m = block_m;
   p.tile_rows = block_m < kBM ? block_m : kBM; p.num_valid = int(num_valid_tokens); p.mul_w = mul_routed_weight ? 1 : 0;
@@ -843,6 +853,7 @@ extern "C" int fnn_gemm_a8w8(const int8_t* a, int64_t lda, const int8_t* b, int6
   p.ldo = ldo; p.ldacc = ldacc; p.row_dtype = row_dtype; p.col_dtype = col_dtype;
   p.M = int(M); p.N = int(N); p.K = int(K);
   p.status = device_status_word();
+  p.wait_ns = kWaitLimitNs; p.skip_kb = -1;
   cudaStream_t st = static_cast<cudaStream_t>(stream);
   if (out_dtype == FNN_F16) return dispatch<__half>(a, lda, b, ldb, p, st);
   return dispatch<__nv_bfloat16>(a, lda, b, ldb, p, st);

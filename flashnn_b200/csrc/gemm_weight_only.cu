@@ -510,13 +510,14 @@ int launch_prefill_g(const T* act, int64_t lda, const uint8_t* qw, PfParams p, f
   static_assert(L::kStageBytes % 1024 == 0 && L::kWBytes % 1024 == 0 && L::kConvOff % 1024 == 0, "tile alignment");
   auto kern = wo_umma_pair_kernel<T, BITS, GRP>;
   static std::once_flag once[64];
+  static cudaError_t attr_err[64];  // per device, so that a failure is reported on every call and not only the first
   int dev = 0;
   cudaGetDevice(&dev);
-  cudaError_t attr_err = cudaSuccess;
-  std::call_once(once[dev & 63], [&] {
-    attr_err = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, L::kDynamicBytes);
+  dev &= 63;
+  std::call_once(once[dev], [&] {
+    attr_err[dev] = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, L::kDynamicBytes);
   });
-  if (attr_err != cudaSuccess) return check_cuda(attr_err, "cudaFuncSetAttribute(weight-only prefill)");
+  if (attr_err[dev] != cudaSuccess) return check_cuda(attr_err[dev], "cudaFuncSetAttribute(weight-only prefill)");
   if (p.zp && !GRP) {
     row_sum_kernel<T><<<unsigned((int64_t(p.M) * 32 + 255) / 256), 256, 0, st>>>(act, lda, xsum_ws, p.M, p.K);
     if (int e = check_cuda(cudaGetLastError(), "row_sum launch")) return e;

@@ -145,12 +145,13 @@ norm_dquant_kernel(const NdParams p) {
         y[c] = make_uint4(o[0], o[1], o[2], o[3]);
       }
     }
-    const float amax = block_reduce<true>(fmaxf(lo_of<T>(m2), hi_of<T>(m2)), red);
+    const float amax = block_absmax_keep_nan(max_keep_nan(lo_of<T>(m2), hi_of<T>(m2)), red);
     const float s = round_to<T>(__fdiv_rn(amax, 127.0f));
     if (threadIdx.x == 0) reinterpret_cast<T*>(p.scale)[row] = from_f32<T>(s);
     const InvBracket inv2 = inv_bracket(s);
-    // constant row and zero bias (0 / 0, which the cast turns into 0), or a scale too small to invert
-    const bool plain = !(s > 0.f) || inv_overflowed(inv2);
+    // constant row and zero bias (0 / 0, which the cast turns into 0), a scale too small to invert, or a row with a
+    // NaN or an infinity in it (every normalised value and the scale are NaN; NaN quotients are written as 0)
+    const bool plain = !usable_scale(s) || inv_overflowed(inv2);
 #pragma unroll
     for (int c = 0; c < NCHUNK; ++c) {
       const int i = c * blockDim.x + threadIdx.x;
@@ -185,14 +186,16 @@ norm_dquant_kernel(const NdParams p) {
 #pragma unroll
         for (int j = 0; j < 8; ++j) {
           v[c][j] = __fmul_rn(__fmul_rn(v[c][j], rstd), w[j]);
-          amax = fmaxf(amax, fabsf(v[c][j]));
+          amax = max_keep_nan(amax, v[c][j]);
         }
       }
     }
-    amax = block_reduce<true>(amax, red);
+    amax = block_absmax_keep_nan(amax, red);
     const float s = __fdiv_rn(amax, 127.f);
     if (threadIdx.x == 0) reinterpret_cast<T*>(p.scale)[row] = from_f32<T>(s);
-    const bool zero = !(s > 0.f);  // every normalised value is 0: 0 / 0, which the cast turns into 0
+    // every normalised value is 0 (0 / 0, which the cast turns into 0), or the row holds a NaN or an infinity: then
+    // the scale is NaN (infinite if only the product overflowed), every quotient is NaN or 0, and q is written as 0
+    const bool zero = !usable_scale(s);
     const InvBracket inv2 = inv_bracket(s);
     const uint32_t amb0 = inv_overflowed(inv2) ? 1u : 0u;
 #pragma unroll

@@ -16,7 +16,7 @@ template <typename T> __device__ __forceinline__ float round_to(float v) {
 
 template <typename T> __device__ __forceinline__ int quantise_one(float x, float s) {
   const float r = rintf(round_to<T>(__fdiv_rn(x, s)));
-  if (r != r) return 0;  // 0/0 on an all-zero row
+  if (r != r) return 0;  // 0/0 on an all-zero row, anything over a NaN scale, infinity over an infinite scale
   return static_cast<int>(fminf(fmaxf(r, -128.f), 127.f));
 }
 
@@ -84,14 +84,37 @@ template <typename T> __device__ __forceinline__ uint32_t quantise_fast(float x,
   return __float_as_uint(__fadd_rn(t, 12582912.f));
 }
 
-// running max of |x| over packed pairs, kept as a packed pair (no conversion in the first pass)
+// running max of |x| over packed pairs, kept as a packed pair (no conversion in the first pass); a NaN element
+// makes its half NaN from then on
 __device__ __forceinline__ uint32_t absmax2(uint32_t m, uint32_t w, __half) {
-  const __half2 r = __hmax2(*reinterpret_cast<__half2*>(&m), __habs2(*reinterpret_cast<__half2*>(&w)));
+  const __half2 r = __hmax2_nan(*reinterpret_cast<__half2*>(&m), __habs2(*reinterpret_cast<__half2*>(&w)));
   return *reinterpret_cast<const uint32_t*>(&r);
 }
 __device__ __forceinline__ uint32_t absmax2(uint32_t m, uint32_t w, __nv_bfloat16) {
-  const __nv_bfloat162 r = __hmax2(*reinterpret_cast<__nv_bfloat162*>(&m), __habs2(*reinterpret_cast<__nv_bfloat162*>(&w)));
+  const __nv_bfloat162 r = __hmax2_nan(*reinterpret_cast<__nv_bfloat162*>(&m), __habs2(*reinterpret_cast<__nv_bfloat162*>(&w)));
   return *reinterpret_cast<const uint32_t*>(&r);
 }
+
+// Maximum of non-negative fp32 values that keeps a NaN: for sign-cleared values the IEEE bit patterns order like
+// unsigned integers, with every NaN pattern above infinity, so an unsigned max of the bits returns a NaN whenever
+// one of the operands is a NaN (fmaxf would drop it).
+__device__ __forceinline__ float max_keep_nan(float a, float b) {
+  return __uint_as_float(max(__float_as_uint(a) & 0x7fffffffu, __float_as_uint(b) & 0x7fffffffu));
+}
+// max_keep_nan over the whole block; `red` holds 32 floats.  Every thread gets the result.
+__device__ __forceinline__ float block_absmax_keep_nan(float v, float* red) {
+#pragma unroll
+  for (int o = 16; o > 0; o >>= 1) v = max_keep_nan(v, __shfl_xor_sync(0xffffffffu, v, o));
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, nwarp = (blockDim.x + 31) >> 5;
+  __syncthreads();  // `red` may still be read from an earlier reduction
+  if (lane == 0) red[warp] = v;
+  __syncthreads();
+  v = (lane < nwarp) ? red[lane] : 0.f;
+#pragma unroll
+  for (int o = 16; o > 0; o >>= 1) v = max_keep_nan(v, __shfl_xor_sync(0xffffffffu, v, o));
+  return v;
+}
+// a scale the fast path can use: positive and finite (NaN and infinity fail both comparisons or the second)
+__device__ __forceinline__ bool usable_scale(float s) { return s > 0.f && s <= 3.4028234e38f; }
 
 }  // namespace fnn

@@ -64,11 +64,15 @@ def a16w4_decode(m=1, n=28672, k=8192, group=128, dtype=torch.bfloat16):
                 scale=rand_uniform((k // group, n), 2, 0.005, 0.05, dtype), group=group, out_ty=dtype)
 
 
-def ffn_layer(m, rank=0, world=1, hidden=8192, inter=28672):
+def ffn_layer(m, rank=0, world=1, hidden=8192, inter=28672, weights=True):
     """Llama-2-70B-shaped FFN, A8W8, column-sharded: rank `rank` of `world` owns output columns
     [r*N/world, (r+1)*N/world) of both projections (gate/up: hidden -> 2*inter; down: inter -> hidden).
-    Activations are replicated; the down projection gets its own N(0,1) input."""
+    Activations are replicated; the down projection gets its own N(0,1) input.  `weights=False` returns
+    the activations only."""
     n_gu, n_dn = 2 * inter, hidden
+    if not weights:
+        return dict(x=rand_normal((m, hidden), 0, torch.bfloat16), h=rand_normal((m, inter), 3, torch.bfloat16),
+                    out_ty=torch.bfloat16)
     assert n_gu % world == 0 and n_dn % world == 0
     s_gu, s_dn = n_gu // world, n_dn // world
 
@@ -106,3 +110,64 @@ def dynamic_quant_bytes(m, k) -> int:
 
 def a16w4_bytes(m, n, k, group) -> int:
     return n * k // 2 + 2 * (k // group) * n + 2 * m * k + 2 * m * n
+
+
+# ----------------------------------------------------------------------------
+# Fused mixture-of-experts cases
+# ----------------------------------------------------------------------------
+def moe_align_block_size(topk_ids: torch.Tensor, num_experts: int, block_m: int):
+    """The block-aligned expert sort the reference's fused-MoE kernels expect as input
+    (flashnn/triton_kernels/fused_moe_a8w8.py:191-209 describes the layout; the reference ships no routine that
+    produces it).  topk_ids [M, top_k] -> (sorted_token_ids [EM] int32, expert_ids [EM / block_m] int32,
+    num_tokens_post_padded [1] int32).  Flat (token * top_k + choice) indices are grouped by expert, each group
+    padded to a multiple of block_m with the value M * top_k; EM is the worst-case length, the unused tail holds
+    padding values and expert 0."""
+    flat = topk_ids.reshape(-1)
+    num_valid = flat.numel()
+    em = num_valid + num_experts * (block_m - 1)
+    em = (em + block_m - 1) // block_m * block_m
+    sorted_ids = torch.full((em,), num_valid, dtype=torch.int32)
+    expert_ids = torch.zeros(em // block_m, dtype=torch.int32)
+    pos = 0
+    for e in range(num_experts):
+        idx = torch.nonzero(flat == e).reshape(-1).to(torch.int32)
+        if idx.numel() == 0:
+            continue
+        n_blocks = (idx.numel() + block_m - 1) // block_m
+        sorted_ids[pos:pos + idx.numel()] = idx
+        expert_ids[pos // block_m:pos // block_m + n_blocks] = e
+        pos += n_blocks * block_m
+    return sorted_ids, expert_ids, torch.tensor([pos], dtype=torch.int32)
+
+
+def make_moe_case(m, e, n, k, top_k, block_m, seed, scale_dt=torch.float32):
+    """Seeded fused-MoE A8W8 problem: int8 tokens [m, k], expert weights [e, n, k], scales, softmax routing."""
+    g = torch.Generator().manual_seed(seed)
+    a = torch.randint(-127, 128, (m, k), generator=g, dtype=torch.int8)
+    b = torch.randint(-127, 128, (e, n, k), generator=g, dtype=torch.int8)
+    alpha_row = (torch.rand(m, generator=g) * 0.015 + 0.005).to(scale_dt)
+    alpha_col = (torch.rand(e, n, generator=g) * 0.009 + 0.001).to(scale_dt)
+    logits = torch.rand(m, e, generator=g)
+    topk_w, topk_ids = torch.topk(torch.softmax(logits, dim=-1), top_k, dim=-1)
+    sorted_ids, expert_ids, npp = moe_align_block_size(topk_ids, e, block_m)
+    return dict(a=a, b=b, alpha_row=alpha_row, alpha_col=alpha_col, topk_w=topk_w.float().contiguous(),
+                topk_ids=topk_ids.to(torch.int32), sorted_ids=sorted_ids, expert_ids=expert_ids, npp=npp)
+
+
+def make_moe_w4_case(m, e, n, k, top_k, block_m, seed, dtype=torch.float16, group=0, use_zp=False):
+    """Seeded fused-MoE A16W4 problem: 16-bit tokens [m, k], packed int4 expert weights [e, n/2, k] (channel 2j in the
+    low nibble of byte (j, k), 2j+1 in the high nibble), scales [e, n] (group == 0) or [e, n, k/group], optional
+    zero-points of the same shape."""
+    g = torch.Generator().manual_seed(seed)
+    a = torch.randn(m, k, generator=g).to(dtype)
+    w4 = torch.randint(-8, 8, (e, n, k), generator=g, dtype=torch.int8)
+    u = w4.to(torch.int16) & 0xF
+    b = (u[:, 0::2] | (u[:, 1::2] << 4)).to(torch.uint8).view(torch.int8).contiguous()
+    sshape = (e, n) if group == 0 else (e, n, k // group)
+    scale = (torch.rand(*sshape, generator=g) * 0.045 + 0.005).to(dtype)
+    zp = torch.randint(-2, 3, sshape, generator=g).to(dtype) if use_zp else None
+    logits = torch.rand(m, e, generator=g)
+    topk_w, topk_ids = torch.topk(torch.softmax(logits, dim=-1), top_k, dim=-1)
+    sorted_ids, expert_ids, npp = moe_align_block_size(topk_ids, e, block_m)
+    return dict(a=a, b=b, w4=w4, scale=scale, zp=zp, topk_w=topk_w.float().contiguous(), topk_ids=topk_ids.to(torch.int32),
+                sorted_ids=sorted_ids, expert_ids=expert_ids, npp=npp)

@@ -57,9 +57,17 @@ typedef enum fnn_dtype {
  * stream serialisation: its CTAs may become resident while the preceding kernel drains and start fetching weights; they
  * touch neither the activations nor the output until that kernel has completed and its writes are visible
  * (griddepcontrol.wait).  Results are unchanged; back-to-back decode calls lose the launch gap between them.
+ *
+ * FNN_OPT_TEST_STALL_US (default 0; a hook for the library's own tests, never set it in production).  With a value
+ * v > 0, fnn_gemm_a8w8 calls that run the single-CTA tensor-core kernel (at most 128 rows, or few tiles) leave out the
+ * loads of one K block of every CTA's first tile and bound every wait of that launch to v microseconds instead of two
+ * seconds.  The wait for the missing block then runs out: the kernel records its time-out code, drains what it has in
+ * flight, frees what it holds and returns without a result, and the next fnn_device_status reports
+ * FNN_ERR_DEVICE_TIMEOUT.  This is how the give-up path of the kernels is exercised without faulting the GPU.
  */
 typedef enum fnn_option {
-  FNN_OPT_STATIC_WEIGHTS = 1
+  FNN_OPT_STATIC_WEIGHTS = 1,
+  FNN_OPT_TEST_STALL_US = 2
 } fnn_option;
 
 /* Sets an option; FNN_ERR_UNSUPPORTED for an unknown one.  fnn_get_option returns the value, or -1 if unknown. */
@@ -92,6 +100,10 @@ int fnn_device_status(int* device_code);
  * absmax/127 and x/scale are each rounded to the input dtype, the quotient is
  * rounded half-to-even, and the int8 cast saturates (+128 becomes +127; the
  * reference's cast wraps it to -128).  A row of zeros gives q = 0, scale = 0.
+ * Non-finite input is not hidden: a row that holds a NaN gets scale = NaN, a row
+ * that holds an infinity (and no NaN) gets scale = infinity, as the reference's
+ * torch path gives; every quotient of such a row is NaN or 0 and q is written
+ * as 0, so a GEMM fed with the row and its scale yields NaN outputs.
  *
  *   x      [M, K]  f16 or bf16 (x_dtype), leading dimension ldx
  *   q      [M, K]  int8, leading dimension ldq
@@ -201,6 +213,9 @@ size_t fnn_gemm_weight_only_workspace_bytes(int64_t M, int64_t N, int64_t K, int
  *   weight  [K]     (and bias [K] for the layer norm) of dtype w_dtype: the dtype of x, or f32; 16-byte aligned
  *   q       [M, K]  int8, ldq (a multiple of 8)
  *   scale   [M]     in the dtype of x
+ *
+ * A row that holds a NaN or an infinity gets scale = NaN and q = 0 (every normalised value, hence every quotient,
+ * is NaN there), as the reference's torch path gives.
  */
 int fnn_rms_norm_dquant(const void* x, int x_dtype, int64_t M, int64_t K, int64_t ldx, const void* weight,
                         int w_dtype, float eps, int8_t* q, int64_t ldq, void* scale, void* stream);

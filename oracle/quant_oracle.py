@@ -212,7 +212,9 @@ def rms_norm_dquant(x: torch.Tensor, weight: torch.Tensor, eps: float = 1e-6):
     n = n * weight  # fp32 * (16-bit or fp32) parameter promotes to fp32
     scale = n.abs().max(dim=-1, keepdim=True)[0] / 127.0
     q = torch.clamp(torch.round(n / scale), -128.0, 127.0)
-    return q.to(torch.int8), scale.reshape(x.shape[:-1]).type_as(x)
+    # a NaN quotient (row of zeros, or a row holding a NaN / an infinity, whose scale is NaN) is cast to 0: what the
+    # reference's .to(torch.int8) yields on x86 hosts, made explicit here so that it does not depend on the host
+    return torch.nan_to_num(q, nan=0.0).to(torch.int8), scale.reshape(x.shape[:-1]).type_as(x)
 
 
 def layer_norm_dquant(x: torch.Tensor, weight: torch.Tensor, bias: torch.Tensor, eps: float = 1e-5):
@@ -221,7 +223,7 @@ def layer_norm_dquant(x: torch.Tensor, weight: torch.Tensor, bias: torch.Tensor,
     n = torch.nn.functional.layer_norm(x, (x.shape[-1],), weight, bias, eps)
     scale = n.abs().max(dim=-1, keepdim=True)[0] / 127.0
     q = torch.clamp(torch.round(n / scale), -128.0, 127.0)
-    return q.to(torch.int8), scale.reshape(-1, 1)
+    return torch.nan_to_num(q.float(), nan=0.0).to(torch.int8), scale.reshape(-1, 1)  # NaN -> 0 as above
 
 
 # ----------------------------------------------------------------------------

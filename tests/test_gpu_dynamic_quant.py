@@ -94,3 +94,23 @@ def test_rows_with_subnormal_scale():
     qo, so = O.dynamic_quantize(x, saturate=True)
     assert torch.equal(s.view(torch.int16), so.view(torch.int16))
     assert torch.equal(q, qo)
+
+
+@pytest.mark.parametrize("dt", [torch.float16, torch.bfloat16])
+@pytest.mark.parametrize("k", [264, 8192, 10001])  # vector kernel (short and long rows) and the generic kernel
+def test_rows_with_a_nan_or_an_infinity(dt, k):
+    """A NaN in a row makes that row's scale NaN, an infinity makes it infinite, exactly as the reference's torch
+    path does; the quantised values of such a row are 0 (a NaN quotient cast to int8), the other rows are untouched."""
+    g = torch.Generator().manual_seed(k)
+    x = torch.randn(5, k, generator=g).to(dt)
+    x[1, k // 3] = float("nan")
+    x[2, k - 1] = float("inf")
+    x[3, 0] = float("-inf")
+    x[3, 5] = float("nan")
+    q, s = run(x)
+    qo, so = O.dynamic_quantize(x, saturate=True)
+    assert torch.isnan(s[1]) and torch.isinf(s[2]) and torch.isnan(s[3])
+    assert torch.equal(torch.isnan(s), torch.isnan(so)) and torch.equal(torch.isinf(s), torch.isinf(so))
+    assert torch.equal(s[[0, 4]].view(torch.int16), so[[0, 4]].view(torch.int16))
+    assert torch.equal(q, qo)
+    assert (q[1:4] == 0).all()

@@ -124,3 +124,24 @@ def test_rejects_bad_arguments():
         flashnn_b200.RMSNormDquant(100).cuda()(x)
     with pytest.raises(RuntimeError):
         flashnn_b200.LayernormDquant(128)(torch.randn(4, 128).half())  # CPU tensor: no CPU path
+
+
+@pytest.mark.parametrize("dt", [torch.float16, torch.bfloat16])
+@pytest.mark.parametrize("kind", ["rms", "ln"])
+def test_rows_with_a_nan_or_an_infinity(kind, dt):
+    """A row that holds a NaN or an infinity comes out with a NaN scale and q = 0 (every quotient is NaN), as the
+    reference's torch path gives; it does not turn into plausible finite data.  Other rows are unaffected."""
+    g = torch.Generator().manual_seed(11)
+    x = torch.randn(4, 1024, generator=g).to(dt)
+    w = (torch.rand(1024, generator=g) + 0.5).to(dt)
+    b = (torch.randn(1024, generator=g) * 0.1).to(dt)
+    clean_q, clean_s = run_rms(x, w, 1e-5) if kind == "rms" else run_ln(x, w, b, 1e-5)
+    x[1, 77] = float("nan")
+    x[2, 1000] = float("inf")
+    q, s = run_rms(x, w, 1e-5) if kind == "rms" else run_ln(x, w, b, 1e-5)
+    qo, so = O.rms_norm_dquant(x, w, 1e-5) if kind == "rms" else O.layer_norm_dquant(x, w, b, 1e-5)
+    s, so, clean_s = s.reshape(-1), so.reshape(-1), clean_s.reshape(-1)
+    assert bool(torch.isnan(s[1])) and bool(torch.isnan(s[2]))
+    assert bool(torch.isnan(so[1])) and bool(torch.isnan(so[2]))
+    assert (q[1:3] == 0).all() and (qo[1:3] == 0).all()
+    assert torch.equal(q[[0, 3]], clean_q[[0, 3]]) and torch.equal(s[[0, 3]].view(torch.int16), clean_s[[0, 3]].view(torch.int16))

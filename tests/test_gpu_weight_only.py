@@ -32,6 +32,23 @@ def assert_within_bound(out, act, qw, scale, bias, zp, max_last_bit_mismatch=0.0
     assert float((out != exact).float().mean()) < max_last_bit_mismatch
 
 
+def assert_rows_within_bound(out, ref, row_factor=None, mask=None):
+    """The stated bound |d| <= 1e-3 + 1e-2 |ref| on every element.  A row that a test multiplied by a factor f > 1
+    (to reach the top of the dtype's range) is the same problem in units f times larger, so its absolute term is
+    f * 1e-3; every other row gets the plain bound."""
+    atol = torch.full((out.shape[0], 1), ATOL)
+    if row_factor:
+        for r, f in row_factor.items():
+            if r < out.shape[0]:
+                atol[r] = ATOL * max(1.0, f)
+    err = (out.float() - ref).abs()
+    bound = atol + RTOL * ref.abs()
+    ok = err <= bound
+    if mask is not None:
+        ok = ok | ~mask
+    assert bool(ok.all()), f"max excess {(err - bound)[~ok].max():.3e}"
+
+
 @pytest.mark.parametrize("name", sorted(WO))
 def test_golden_cases(name):
     c = WO[name]
@@ -166,11 +183,7 @@ def test_int4_few_tokens(dt, m, n, k, group, use_bias, use_zp):
     out = run(act, qw, scale, bias, zp)
     ref = O.gemm_weight_only_fp32(act, qw, scale, bias, zp)
     finite = torch.isfinite(ref.to(dt).float())
-    # relative bound per row (rows differ by up to 60 orders of magnitude) on top of the stated absolute one
-    row_scale = ref.abs().amax(dim=1, keepdim=True)
-    err = (out.float() - ref).abs()
-    bound = ATOL + RTOL * ref.abs() + 4e-3 * row_scale * (2.0 ** -8 if dt == torch.bfloat16 else 2.0 ** -11) * 256
-    assert bool((err <= bound)[finite].all()), f"max excess {(err - bound)[finite].max():.3e}"
+    assert_rows_within_bound(out, ref, {4: 50.0 if dt == torch.float16 else 1e30}, mask=finite)
     exact = ref.to(dt)
     assert int((out != exact)[finite].sum()) <= max(3, 0.02 * out.numel())
     if m >= 2:
@@ -276,10 +289,7 @@ def test_int4_six_to_sixteen_tokens(dt, m, n, k, group, use_bias):
     act[2] = act[2] * (1e-3 if dt == torch.float16 else 1e-30)  # a tiny row
     out = run(act, qw, scale, bias, zp)
     ref = O.gemm_weight_only_fp32(act, qw, scale, bias, zp)
-    row_scale = ref.abs().amax(dim=1, keepdim=True)
-    err = (out.float() - ref).abs()
-    bound = ATOL + RTOL * ref.abs() + 4e-3 * row_scale * (2.0 ** -8 if dt == torch.bfloat16 else 2.0 ** -11) * 256
-    assert bool((err <= bound).all()), f"max excess {(err - bound).max():.3e}"
+    assert_rows_within_bound(out, ref)
     exact = ref.to(dt)
     assert int((out != exact).sum()) <= max(3, 0.02 * out.numel())
     want = torch.zeros(n) if bias is None else bias.float()
@@ -322,10 +332,7 @@ def test_int8_few_tokens(dt, m, n, k, group, use_bias, use_zp):
         act[1] = 0
     out = run(act, qw, scale, bias, zp)
     ref = O.gemm_weight_only_fp32(act, qw, scale, bias, zp)
-    row_scale = ref.abs().amax(dim=1, keepdim=True)
-    err = (out.float() - ref).abs()
-    bound = ATOL + RTOL * ref.abs() + 4e-3 * row_scale * (2.0 ** -8 if dt == torch.bfloat16 else 2.0 ** -11) * 256
-    assert bool((err <= bound).all()), f"max excess {(err - bound).max():.3e}"
+    assert_rows_within_bound(out, ref)
     exact = ref.to(dt)
     assert int((out != exact).sum()) <= max(3, 0.02 * out.numel())
     if m >= 2:
