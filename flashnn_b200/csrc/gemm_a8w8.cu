@@ -128,7 +128,8 @@ __device__ __forceinline__ void store_chunk(const uint32_t (&r)[32], int row, in
 }
 
 // Fused-MoE epilogue of 32 accumulator columns of one sorted slot, in the order of the reference kernel
-// (flashnn/triton_kernels/fused_moe_a8w8.py:155-170): acc * alpha_row, * alpha_col, * routing weight, cast.
+// (flashnn/triton_kernels/fused_moe_a8w8.py:155-170): acc * alpha_row, * alpha_col, * routing weight, cast to fp16,
+// then to the output dtype.
 template <typename OutT>
 __device__ __forceinline__ void store_chunk_moe(const uint32_t (&r)[32], int64_t out_row, int col0, float rs, float rw,
                                                 bool mul_w, const float* cs, const A8W8Params& p, bool vec_ok) {
@@ -138,7 +139,9 @@ __device__ __forceinline__ void store_chunk_moe(const uint32_t (&r)[32], int64_t
   for (int j = 0; j < 32; ++j) {
     float t = __fmul_rn(__fmul_rn(float(int32_t(r[j])), rs), cs[j]);
     if (mul_w) t = __fmul_rn(t, rw);
-    v[j] = t;
+    // the reference kernel casts its accumulator to fp16 whatever the output tensor's dtype is
+    // (fused_moe_a8w8.py:165) and the store converts again: a bf16 output is rounded twice
+    v[j] = std::is_same<OutT, __half>::value ? t : __half2float(__float2half_rn(t));
   }
   OutT* orow = reinterpret_cast<OutT*>(p.out) + out_row * p.ldo + col0;
   if (col0 + 32 <= p.N && vec_ok) {

@@ -22,10 +22,12 @@ project):
 * `gemm_weight_only_fp32`       same contraction with no 16-bit rounding of w*s
 * `rms_norm_dquant`             flashnn/norm.py:39-63
 * `layer_norm_dquant`           flashnn/norm.py:94-124
-* `fused_moe_a8w8`              flashnn/triton_kernels/fused_moe_a8w8.py:96-170 -- PARITY UNPINNED for this one
-                                function: the reference has neither a torch implementation nor a test of the fused
-                                MoE kernels, so this restates the Triton kernel's arithmetic from its source and is
-                                cross-checked only against a token-by-token formulation (tests/test_moe_oracle.py)
+* `fused_moe_a8w8`              flashnn/triton_kernels/fused_moe_a8w8.py:96-170.  The reference has neither a torch
+                                implementation nor a test of its fused-MoE kernels, so this restates the Triton
+                                kernel's arithmetic from its source; it is pinned by tests/golden/fused_moe_a8w8.npz,
+                                outputs of that Triton kernel itself run on a B200 by tests/golden/make_moe_golden.py
+* `fused_moe_a16w4`             flashnn/triton_kernels/fused_moe_a16w4.py:50-323, pinned the same way by
+                                tests/golden/fused_moe_a16w4.npz
 """
 from __future__ import annotations
 
@@ -227,7 +229,7 @@ def layer_norm_dquant(x: torch.Tensor, weight: torch.Tensor, bias: torch.Tensor,
 
 
 # ----------------------------------------------------------------------------
-# Fused MoE A8W8 (parity unpinned, see the header)
+# Fused MoE (pinned by outputs of the reference's Triton kernels, see the header)
 # ----------------------------------------------------------------------------
 def fused_moe_a8w8(A, B, alpha_row, alpha_col, topk_weights, sorted_token_ids, expert_ids, num_tokens_post_padded,
                    num_valid_tokens, mul_routed_weight, top_k, BM, out_ty=torch.float16, C=None):
@@ -253,5 +255,61 @@ def fused_moe_a8w8(A, B, alpha_row, alpha_col, topk_weights, sorted_token_ids, e
         v = v * alpha_col[e].float()[None, :]
         if mul_routed_weight:
             v = v * tw[flat].float()[:, None]
-        flat_out[flat] = v.to(C.dtype)
+        # the kernel casts to fp16 whatever C's dtype is (fused_moe_a8w8.py:165); storing into a bf16 C rounds again
+        flat_out[flat] = v.to(torch.float16).to(C.dtype)
+    return C
+
+
+def fused_moe_a16w4(A, B, scale_b, zero_points, topk_weights, sorted_token_ids, expert_ids, num_tokens_post_padded,
+                    num_valid_tokens, mul_routed_weight, top_k, BM, C=None, exact_scales=False):
+    """Fused-MoE A16W4 as the reference's Triton kernels compute it (flashnn/triton_kernels/fused_moe_a16w4.py).
+
+    A [M, K] fp16/bf16; B [E, N/2, K] packed int4 (byte (j, k): channel 2j in the low nibble, 2j+1 in the high one,
+    `:137,151`); scale_b / zero_points [E, N] (per channel) or [E, N, K/group]; C [M, top_k, N] in A's dtype.
+    Per channel (`:50-183`): the integer weight minus the zero-point, in A's dtype, goes into an fp32-accumulated
+    product; the accumulator is multiplied by the fp32 scale, then by the routing weight, and cast.
+    Per group (`:186-323`): (w - zp) * s is formed in the scale's 16-bit dtype for every K group (one rounding per
+    weight, `:289-303`), the product is accumulated in fp32, multiplied by the routing weight and cast.
+    `exact_scales=True` keeps (w - zp) * s in fp32 instead: the fp32 dequant-matmul bound the CUDA kernels are held to.
+    Rows that no slot names keep what C held (zeros if C is None).  The fp32 summation order of a tensor-core dot
+    product is not defined, so outputs of the Triton kernel are reproduced to within a rounding of the result."""
+    E, NP, K = B.shape
+    N = 2 * NP
+    M = A.shape[0]
+    dt = A.dtype
+    if C is None:
+        C = torch.zeros(M, top_k, N, dtype=dt)
+    flat_out = C.view(M * top_k, N)
+    padded = int(num_tokens_post_padded.reshape(-1)[0])
+    tw = topk_weights.reshape(-1)
+    per_channel = scale_b.dim() == 2
+    for blk in range(padded // BM):
+        e = int(expert_ids[blk])
+        slots = sorted_token_ids[blk * BM:(blk + 1) * BM].long()
+        flat = slots[slots < num_valid_tokens]
+        if flat.numel() == 0:
+            continue
+        rows = flat // top_k
+        w = unpack_int4(B[e])  # [N, K] int8
+        a = A[rows].float()
+        if per_channel:
+            wq = w.to(dt) if zero_points is None else (w.to(dt) - zero_points[e].to(dt)[:, None])
+            if exact_scales:
+                wq = w.float() if zero_points is None else (w.float() - zero_points[e].float()[:, None])
+            acc = a @ wq.float().t()
+            acc = acc * scale_b[e].float()[None, :]
+        else:
+            groups = scale_b.shape[-1]
+            g = K // groups
+            s = scale_b[e].repeat_interleave(g, dim=1)  # [N, K]
+            z = None if zero_points is None else zero_points[e].repeat_interleave(g, dim=1)
+            if exact_scales:
+                wq = (w.float() if z is None else w.float() - z.float()) * s.float()
+            else:
+                wq = w.to(s.dtype) if z is None else (w.to(s.dtype) - z)
+                wq = (wq * s).float()
+            acc = a @ wq.t()
+        if mul_routed_weight:
+            acc = acc * tw[flat].float()[:, None]
+        flat_out[flat] = acc.to(dt)
     return C

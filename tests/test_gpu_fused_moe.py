@@ -44,3 +44,24 @@ def test_sixteen_bit_scales_and_dropped_tokens():
     ref = O.fused_moe_a8w8(c["a"], c["b"], c["alpha_row"], c["alpha_col"], c["topk_w"], c["sorted_ids"], c["expert_ids"],
                            c["npp"], m * top_k, True, top_k, bm, torch.float16, C=torch.full((m, top_k, n), 7.0, dtype=torch.float16))
     assert torch.equal(out.view(torch.int16), ref.view(torch.int16))
+
+
+# Outputs of the reference's own Triton kernel on a B200 (tests/golden/make_moe_golden.py): the CUDA kernel must
+# reproduce them bit for bit, including the fp16 rounding the reference applies before a bf16 store.
+from tests import golden_io as G  # noqa: E402
+
+A8 = G.load("fused_moe_a8w8.npz")
+
+
+@pytest.mark.parametrize("name", sorted(A8))
+def test_reproduces_the_reference_kernel(name):
+    c = A8[name]
+    odt = G.dtype_of(c["out_dtype"])
+    sdt = None if str(c["scale_dtype"]) == "float32" else G.dtype_of(c["scale_dtype"])
+    m, top_k, n, bm = int(c["m"]), int(c["top_k"]), int(c["n"]), int(c["bm"])
+    case = dict(a=G.tensor(c["a"]), b=G.tensor(c["b"]), alpha_row=G.tensor(c["alpha_row"], sdt),
+                alpha_col=G.tensor(c["alpha_col"], sdt), topk_w=G.tensor(c["topk_w"]), topk_ids=G.tensor(c["topk_ids"]),
+                sorted_ids=G.tensor(c["sorted_ids"]), expert_ids=G.tensor(c["expert_ids"]), npp=G.tensor(c["npp"]))
+    out = run(case, top_k, bm, bool(c["mul"]), odt, m, n)
+    ref = G.tensor(c["out"], odt)
+    assert torch.equal(out.view(torch.int16), ref.view(torch.int16))
