@@ -278,29 +278,30 @@ def cpu_baseline_sample(sample_rows, budget_s=25.0):
     return ops / best / 1e12, best, torch.get_num_threads(), kind, note
 
 
-def int8_yardstick(device, flush_buf):
+def int8_yardstick(device, flush_buf, sustained_seconds=0.0):
     """The library int8 GEMM (torch._int_mm -> cuBLASLt) at 8192^3 on the same event harness: the measured int8
-    tensor-core rate of this GPU, as a burst (L2 flushed, launches timed one by one, best) and sustained
-    (back to back for about a second).  Returns a dict, or one with "error" if the library declines."""
+    tensor-core rate of this GPU.  Burst: L2 flushed, launches timed one by one, best of 10.  With
+    `sustained_seconds` > 0 also back to back for about that long (the GPU settles under its power cap, so this is run
+    after every other measurement).  Returns a dict, or one with "error" if the library declines."""
     try:
         n = 8192
         a = torch.randint(-127, 128, (n, n), dtype=torch.int8, device=device)
         b = torch.randint(-127, 128, (n, n), dtype=torch.int8, device=device)
         bt = b.t()  # [K, N] view with K contiguous: the layout the weights of this path have
         ts = time_steps(lambda: torch._int_mm(a, bt), 10, 3, flush_buf)
-        burst = 2.0 * n ** 3 / (min(ts) * 1e-3) / 1e12
-        torch.cuda.synchronize()
-        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-        reps = max(20, int(1.0 / (statistics.median(ts) * 1e-3)))
-        e0.record()
-        for _ in range(reps):
-            torch._int_mm(a, bt)
-        e1.record()
-        torch.cuda.synchronize()
-        sustained = 2.0 * n ** 3 * reps / (e0.elapsed_time(e1) * 1e-3) / 1e12
-        return dict(burst_tops=round(burst, 1), sustained_tops=round(sustained, 1), shape="8192^3",
-                    how="torch._int_mm (cuBLASLt int8), CUDA events; burst = best of 10 with L2 flushed, sustained = "
-                        f"{reps} launches back to back")
+        out = dict(burst_tops=round(2.0 * n ** 3 / (min(ts) * 1e-3) / 1e12, 1), shape="8192^3",
+                   how="torch._int_mm (cuBLASLt int8), CUDA events; burst = best of 10 launches with L2 flushed")
+        if sustained_seconds > 0:
+            e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            reps = max(20, int(sustained_seconds / (statistics.median(ts) * 1e-3)))
+            e0.record()
+            for _ in range(reps):
+                torch._int_mm(a, bt)
+            e1.record()
+            torch.cuda.synchronize()
+            out["sustained_tops"] = round(2.0 * n ** 3 * reps / (e0.elapsed_time(e1) * 1e-3) / 1e12, 1)
+            out["how"] += f"; sustained = {reps} launches back to back"
+        return out
     except Exception as e:
         return dict(error=f"{type(e).__name__}: {e}")
 
@@ -440,9 +441,9 @@ def run_native(args):
     line = None
     if rank == 0:
         # ---- per-kernel figures (rank 0's shard), each timed alone with CUDA events ----
-        yard = int8_yardstick(device, flush_buf)
         qx, sx = shard.dq(shard.x)
         gu_ms = statistics.median(time_steps(lambda: shard.gemm(qx, shard.w_gu, sx, shard.col_gu), 10, 3, flush_buf))
+        yard = int8_yardstick(device, flush_buf)
         gu_ops = W.a8w8_ops(TOKENS, shard.n_gu, HIDDEN)
         achieved = gu_ops / (gu_ms * 1e-3) / 1e12
         # a launch timed alone is held against a burst figure: the measured int8 library GEMM when it ran, else twice
@@ -478,6 +479,11 @@ def run_native(args):
             extra.update(extra_shapes(device, flush_buf, peaks))
             if not args.no_triton_reference:
                 extra["reference_triton"] = reference_triton_figures()
+            # last of all: a second of back-to-back library GEMMs leaves the GPU at its power-capped clocks
+            sus = int8_yardstick(device, flush_buf, sustained_seconds=1.0)
+            if "sustained_tops" in sus:
+                yard["sustained_tops"] = sus["sustained_tops"]
+                yard["how"] = sus["how"]
         # ---- CPU baseline: the reference's torch path on the host cores ----
         cpu = None
         if world == 1:
@@ -787,6 +793,15 @@ def run_case(args):
         w = W.a16w8_prefill(m, n, k)
         x, qw, sc = w["x"].to(device), w["w"].to(device), w["scale"].to(device)
         op = flashnn_b200.GemmWeightOnly(torch.float16)
+        fn = lambda: op(x, qw, sc)
+        work, unit = 2.0 * m * n * k / 1e12, "TFLOP/s"
+    elif name == "wog":
+        # A16W4 prefill with group-wise scales (group 128): the decode config's weight at prefill batch sizes
+        m, n, k = args.m or 2048, args.n or 28672, args.k or 8192
+        w = W.a16w4_decode(1, n, k)
+        x = W.rand_normal((m, k), 0, torch.bfloat16).to(device)
+        qw, sc = w["qw"].to(device), w["scale"].to(device)
+        op = flashnn_b200.GemmWeightOnly(torch.bfloat16)
         fn = lambda: op(x, qw, sc)
         work, unit = 2.0 * m * n * k / 1e12, "TFLOP/s"
     elif name == "dq":

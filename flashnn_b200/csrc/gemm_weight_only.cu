@@ -1,5 +1,6 @@
-// Prefill-shaped weight-only GEMM (M > 16), per-channel scales: fp16/bf16 activations x int8 or
-// packed-int4 weights on the tcgen05 tensor cores (kind::f16, fp32 accumulators in TMEM).
+// Prefill-shaped weight-only GEMM (M > 16): fp16/bf16 activations x int8 or packed-int4 weights on the tcgen05
+// tensor cores (kind::f16, fp32 accumulators in TMEM), per-channel scales (described here) or group-wise scales
+// (second kernel, described where it is defined).
 //
 // The weights stay packed in HBM and on the way into the SM.  Per K block of 64:
 //   warp 0       TMA: this CTA's 128 activation rows (16-bit, 128-byte swizzle) and the raw weight bytes
@@ -39,7 +40,7 @@ struct PfParams {
   const void* scale;  // [N], or [K / group, N] for group-wise scales
   const void* zp;     // nullptr or like scale
   const void* bias;   // nullptr or [N]
-  const float* xsum;  // [M] row sums of the activations (only with zero-points)
+  const float* xsum;  // row sums of the activations (only with zero-points): [M], or [K / group, M] per scale group
   void* out;
   int64_t ldo;
   int scale_dtype, bias_dtype;
@@ -55,9 +56,9 @@ template <int BITS> struct PfSmem {
   static constexpr int kWBytes = (kTN / 2) * kTK * 2;                                // 16 KB converted weights
   static constexpr int kStageBytes = kXBytes + kRawBytes;                            // one TMA stage
   static constexpr int kConvOff = kPfStages * kStageBytes;                           // converted-tile ring
-  static constexpr int kVecOff = kConvOff + kPfConvStages * kWBytes;                 // [4 warps][3][kTN] float
+  static constexpr int kVecOff = kConvOff + kPfConvStages * kWBytes;                 // [4 warps][3][kTN] float (group-wise kernel: [3][2][kTN])
   static constexpr int kBarOff = kVecOff + 4 * 3 * kTN * 4;
-  static constexpr int kNumBars = 2 * kPfStages + 3 * kPfConvStages + 4 + 1;
+  static constexpr int kNumBars = 2 * kPfStages + 3 * kPfConvStages + 4 + 1 + 4;
   static constexpr int kTmemSlotOff = kBarOff + kNumBars * 8;
   static constexpr int kAbortOff = kTmemSlotOff + 8;
   static constexpr int kTotal = kAbortOff + 8;
@@ -91,21 +92,6 @@ __device__ __forceinline__ uint32_t pf_sub2(uint32_t a, uint32_t b, __half) {
 __device__ __forceinline__ uint32_t pf_sub2(uint32_t a, uint32_t b, __nv_bfloat16) {
   __nv_bfloat162 r = __hsub2(*reinterpret_cast<__nv_bfloat162*>(&a), *reinterpret_cast<__nv_bfloat162*>(&b));
   return *reinterpret_cast<uint32_t*>(&r);
-}
-
-__device__ __forceinline__ uint32_t pf_mul2(uint32_t a, uint32_t b, __half) {
-  __half2 r = __hmul2(*reinterpret_cast<__half2*>(&a), *reinterpret_cast<__half2*>(&b));
-  return *reinterpret_cast<uint32_t*>(&r);
-}
-__device__ __forceinline__ uint32_t pf_mul2(uint32_t a, uint32_t b, __nv_bfloat16) {
-  __nv_bfloat162 r = __hmul2(*reinterpret_cast<__nv_bfloat162*>(&a), *reinterpret_cast<__nv_bfloat162*>(&b));
-  return *reinterpret_cast<uint32_t*>(&r);
-}
-// group-wise dequantisation of two exact integer values: T((n - zp) * s), the value the reference's torch path
-// stores (flashnn/quant_gemm.py:20-36); n - zp is exact for integer zero-points, so this is one rounding
-template <typename T> __device__ __forceinline__ uint32_t pf_dequant2(uint32_t n2, uint32_t s2, uint32_t z2, bool has_zp) {
-  if (has_zp) n2 = pf_sub2(n2, z2, T());
-  return pf_mul2(n2, s2, T());
 }
 
 // four int8 -> four exact T values (two registers, k order preserved)
@@ -152,27 +138,253 @@ __device__ __forceinline__ void umma_f16_pair(uint32_t tmem_d, uint64_t desc_a, 
 // byte offset of 16-byte chunk `kc` (0..7) of row `row` in a K-major tile with 128-byte rows and 128-byte swizzle
 __device__ __forceinline__ uint32_t sw128(uint32_t row, uint32_t kc) { return row * 128u + ((kc ^ (row & 7u)) << 4); }
 
-// GRP: group-wise scales.  The converter warps then write T((n - zp) * s[k / group, n]) instead of the bare integer
-// and the epilogue only adds the bias.
-template <typename T, int BITS, bool GRP>
+// ---------------------------------------------------------------------------------------------------------
+// Roles shared by the per-channel kernel and the group-wise kernel.  `bars` layout: raw_full[S], empty[S],
+// conv_full[C], conv_empty[C], conv_done[C], tmem_full[2], tmem_empty[2], drain, then (group-wise kernel only)
+// scale_full[2][2].
+// ---------------------------------------------------------------------------------------------------------
+struct PfBars {
+  uint64_t *raw_full, *empty, *conv_full, *conv_empty, *conv_done, *tmem_full, *tmem_empty, *drain, *scale_full;
+};
+__device__ __forceinline__ PfBars pf_bars(uint64_t* bars) {
+  PfBars b;
+  b.raw_full = bars;
+  b.empty = bars + kPfStages;
+  b.conv_full = bars + 2 * kPfStages;
+  b.conv_empty = b.conv_full + kPfConvStages;
+  b.conv_done = b.conv_empty + kPfConvStages;  // peer CTA only: its four converter warps
+  b.tmem_full = b.conv_done + kPfConvStages;
+  b.tmem_empty = b.tmem_full + 2;
+  b.drain = b.tmem_full + 4;
+  b.scale_full = b.tmem_full + 5;
+  return b;
+}
+
+// Thread 0 of each CTA: barrier counts.  `epi_arrivals` = epilogue warps of both CTAs that free an accumulator.
+__device__ __forceinline__ void pf_init_bars(const PfBars& b, int epi_arrivals, bool grp) {
+  for (int s = 0; s < kPfStages; ++s) {
+    mbar_init(&b.raw_full[s], 1);
+    mbar_init(&b.empty[s], 1);
+  }
+  for (int s = 0; s < kPfConvStages; ++s) {
+    mbar_init(&b.conv_full[s], 5);  // leader: its 4 converter warps + the peer's relay
+    mbar_init(&b.conv_done[s], 4);
+    mbar_init(&b.conv_empty[s], 1);
+  }
+  for (int i = 0; i < 2; ++i) {
+    mbar_init(&b.tmem_full[i], 1);
+    mbar_init(&b.tmem_empty[i], epi_arrivals);
+  }
+  mbar_init(b.drain, 1);
+  if (grp)
+    for (int i = 0; i < 4; ++i) mbar_init(&b.scale_full[i], 4);  // the four epilogue warps of one column half
+  mbar_fence_init();
+}
+
+// warp 0 of both CTAs: TMA loads of this CTA's 128 activation rows and its raw weight bytes, one K block per stage
+template <int BITS>
+__device__ __forceinline__ void pf_producer(uint8_t* smem, const PfBars& b, const CUtensorMap* tmap_x,
+                                            const CUtensorMap* tmap_w, const PfParams& p, uint32_t rank, int pair_id,
+                                            int num_pairs, volatile int* abort_flag) {
+  using L = PfSmem<BITS>;
+  const int num_tiles = p.tiles_m * p.tiles_n;
+  const bool leader_lane = elect_one();
+  int stage = 0;
+  uint32_t phase = 0;
+  long long issued = 0;
+  bool ok = true;
+  for (int t = pair_id; t < num_tiles && ok; t += num_pairs) {
+    int mb, nb;
+    pf_tile_coords(t, p.tiles_m, p.tiles_n, mb, nb);
+    const int w_row = (BITS == 8) ? nb * kTN + int(rank) * (kTN / 2) : (nb * kTN + int(rank) * (kTN / 2)) / 2;
+    for (int kb = 0; kb < p.k_blocks; ++kb) {
+      ok = mbar_wait_bounded(&b.empty[stage], phase ^ 1, abort_flag);
+      ok = __all_sync(0xffffffffu, ok);
+      if (!ok) {
+        if (leader_lane) pf_report(p.status, abort_flag, DEV_TIMEOUT_PRODUCER);
+        break;
+      }
+      if (leader_lane) {
+        uint8_t* sx = smem + stage * L::kStageBytes;
+        mbar_expect_tx(&b.raw_full[stage], L::kXBytes + L::kRawBytes);
+        tma_load_2d(sx, tmap_x, &b.raw_full[stage], kb * kTK, mb * 256 + int(rank) * kTM);
+        tma_load_2d(sx + L::kXBytes, tmap_w, &b.raw_full[stage], kb * kTK, w_row);
+        ++issued;
+      }
+      __syncwarp();
+      if (++stage == kPfStages) { stage = 0; phase ^= 1; }
+    }
+  }
+  if (leader_lane) {  // the last stages issued have been consumed (or the CTA is aborting) before exit
+    const long long first = issued > kPfStages ? issued - kPfStages : 0;
+    for (long long i = first; i < issued; ++i)
+      if (!mbar_wait_bounded(&b.empty[i % kPfStages], uint32_t((i / kPfStages) & 1), abort_flag)) break;
+  }
+}
+
+// warp 1 of the leader CTA: issues the MMAs of both CTAs.  An accumulator (one of the two TMEM buffers) collects
+// `kb_per_acc` K blocks and is then handed to the epilogue: the whole K range for per-channel scales, one scale
+// group for group-wise scales.
+template <typename T, int BITS>
+__device__ __forceinline__ void pf_mma(uint8_t* smem, const PfBars& b, const PfParams& p, uint32_t tmem_base, int pair_id,
+                                       int num_pairs, int kb_per_acc, volatile int* abort_flag) {
+  using L = PfSmem<BITS>;
+  constexpr uint32_t idesc = umma_idesc(/*f32*/ 1, std::is_same<T, __half>::value ? 0u : 1u, 256, kTN);
+  const int num_tiles = p.tiles_m * p.tiles_n;
+  const bool leader_lane = elect_one();
+  int stage = 0, cstage = 0;
+  uint32_t cphase = 0;
+  int seg = 0;  // accumulators started so far
+  bool ok = true;
+  bool issued_any = false;
+  for (int t = pair_id; t < num_tiles && ok; t += num_pairs) {
+    for (int kb0 = 0; kb0 < p.k_blocks && ok; kb0 += kb_per_acc, ++seg) {
+      const int buf = seg & 1;
+      const uint32_t acc_phase = (seg >> 1) & 1;
+      ok = mbar_wait_bounded(&b.tmem_empty[buf], acc_phase ^ 1, abort_flag);
+      ok = __all_sync(0xffffffffu, ok);
+      if (!ok) {
+        if (leader_lane) pf_report(p.status, abort_flag, DEV_TIMEOUT_MMA);
+        break;
+      }
+      tc_fence_after();
+      const uint32_t tmem_d = tmem_base + buf * kTN;
+      const int kb1 = min(kb0 + kb_per_acc, p.k_blocks);
+      for (int kb = kb0; kb < kb1; ++kb) {
+        ok = mbar_wait_bounded(&b.conv_full[cstage], cphase, abort_flag);
+        ok = __all_sync(0xffffffffu, ok);
+        if (!ok) {
+          if (leader_lane) pf_report(p.status, abort_flag, DEV_TIMEOUT_MMA);
+          break;
+        }
+        tc_fence_after();
+        if (leader_lane) {
+          const uint32_t sx = smem_u32(smem + stage * L::kStageBytes);
+          const uint32_t sw = smem_u32(smem + L::kConvOff + cstage * L::kWBytes);
+#pragma unroll
+          for (int k = 0; k < kTK / 16; ++k)
+            umma_f16_pair(tmem_d, umma_desc_k_sw128(sx + k * 32), umma_desc_k_sw128(sw + k * 32), idesc,
+                          (kb != kb0 || k != 0) ? 1u : 0u);
+          tc_commit_pair(&b.empty[stage], 0x3);        // activations + raw bytes of this stage, both CTAs
+          tc_commit_pair(&b.conv_empty[cstage], 0x3);  // converted tile, both CTAs
+          issued_any = true;
+        }
+        __syncwarp();
+        if (++stage == kPfStages) stage = 0;
+        if (++cstage == kPfConvStages) { cstage = 0; cphase ^= 1; }
+      }
+      if (ok && leader_lane) tc_commit_pair(&b.tmem_full[buf], 0x3);
+      __syncwarp();
+    }
+  }
+  if (leader_lane && issued_any) {
+    int none = 0;
+    tc_commit_pair(b.drain, 0x1);
+    if (!mbar_wait_bounded(b.drain, 0, &none)) pf_report(p.status, abort_flag, DEV_TIMEOUT_DRAIN);
+  }
+}
+
+// warp 1 of the peer CTA: relays "this CTA's converted tile is ready" to the leader's barrier, one remote arrive per
+// K block, so the converter warps themselves only ever signal locally
+__device__ __forceinline__ void pf_relay(const PfBars& b, const PfParams& p, int pair_id, int num_pairs,
+                                         volatile int* abort_flag) {
+  const int num_tiles = p.tiles_m * p.tiles_n;
+  const bool leader_lane = elect_one();
+  int cstage = 0;
+  uint32_t cphase = 0;
+  bool ok = true;
+  for (int t = pair_id; t < num_tiles && ok; t += num_pairs) {
+    for (int kb = 0; kb < p.k_blocks; ++kb) {
+      ok = mbar_wait_bounded(&b.conv_done[cstage], cphase, abort_flag);
+      ok = __all_sync(0xffffffffu, ok);
+      if (!ok) {
+        if (leader_lane) pf_report(p.status, abort_flag, DEV_TIMEOUT_MMA);
+        break;
+      }
+      if (leader_lane) mbar_arrive_cluster(map_to_cta(smem_u32(&b.conv_full[cstage]), 0));
+      __syncwarp();
+      if (++cstage == kPfConvStages) { cstage = 0; cphase ^= 1; }
+    }
+  }
+}
+
+// four converter warps of both CTAs (ct = 0..127): raw bytes of a K block -> exact 16-bit integers in the K-major
+// 128-byte-swizzled operand tile
+template <typename T, int BITS>
+__device__ __forceinline__ void pf_converters(uint8_t* smem, const PfBars& b, const PfParams& p, uint32_t rank, int pair_id,
+                                              int num_pairs, int ct, volatile int* abort_flag) {
+  using L = PfSmem<BITS>;
+  const int num_tiles = p.tiles_m * p.tiles_n;
+  const int lane = ct & 31;
+  int stage = 0, cstage = 0;
+  uint32_t phase = 0, cphase = 0;
+  bool ok = true;
+  for (int t = pair_id; t < num_tiles && ok; t += num_pairs) {
+    for (int kb = 0; kb < p.k_blocks; ++kb) {
+      ok = mbar_wait_bounded(&b.conv_empty[cstage], cphase ^ 1, abort_flag) &&
+           mbar_wait_bounded(&b.raw_full[stage], phase, abort_flag);
+      ok = __all_sync(0xffffffffu, ok);
+      if (!ok) {
+        if (lane == 0) pf_report(p.status, abort_flag, DEV_TIMEOUT_EPILOGUE);
+        break;
+      }
+      uint8_t* sw = smem + L::kConvOff + cstage * L::kWBytes;           // converted tile: 128 rows x 128 B, swizzled
+      const uint8_t* raw = smem + stage * L::kStageBytes + L::kXBytes;  // raw tile: rows of 64 B, not swizzled
+      if (BITS == 8) {
+        // 128 rows x 4 chunks of 16 bytes; chunk id -> (row = id / 4, c = id % 4): 16 k -> 32 bytes out
+#pragma unroll
+        for (int i = 0; i < 4; ++i) {
+          const int id = ct + i * 128;
+          const uint32_t row = id >> 2, c = id & 3;
+          const uint4 w = *reinterpret_cast<const uint4*>(raw + id * 16);
+          uint4 o0, o1;
+          cvt_int8x4<T>(w.x, o0.x, o0.y);
+          cvt_int8x4<T>(w.y, o0.z, o0.w);
+          cvt_int8x4<T>(w.z, o1.x, o1.y);
+          cvt_int8x4<T>(w.w, o1.z, o1.w);
+          *reinterpret_cast<uint4*>(sw + sw128(row, 2 * c)) = o0;
+          *reinterpret_cast<uint4*>(sw + sw128(row, 2 * c + 1)) = o1;
+        }
+      } else {
+        // 64 packed rows x 4 chunks; packed row j carries channel rows 2j (low nibbles) and 2j+1 (high)
+#pragma unroll
+        for (int i = 0; i < 2; ++i) {
+          const int id = ct + i * 128;
+          const uint32_t prow = id >> 2, c = id & 3;
+          const uint4 w = *reinterpret_cast<const uint4*>(raw + id * 16);
+          uint4 l0, l1, h0, h1;
+          cvt_int4x8<T>(w.x, l0.x, l0.y, h0.x, h0.y);
+          cvt_int4x8<T>(w.y, l0.z, l0.w, h0.z, h0.w);
+          cvt_int4x8<T>(w.z, l1.x, l1.y, h1.x, h1.y);
+          cvt_int4x8<T>(w.w, l1.z, l1.w, h1.z, h1.w);
+          *reinterpret_cast<uint4*>(sw + sw128(2 * prow, 2 * c)) = l0;
+          *reinterpret_cast<uint4*>(sw + sw128(2 * prow, 2 * c + 1)) = l1;
+          *reinterpret_cast<uint4*>(sw + sw128(2 * prow + 1, 2 * c)) = h0;
+          *reinterpret_cast<uint4*>(sw + sw128(2 * prow + 1, 2 * c + 1)) = h1;
+        }
+      }
+      fence_proxy_async_smem();  // the tensor core reads these bytes through the async proxy
+      __syncwarp();
+      if (lane == 0) mbar_arrive(rank == 0 ? &b.conv_full[cstage] : &b.conv_done[cstage]);
+      if (++stage == kPfStages) { stage = 0; phase ^= 1; }
+      if (++cstage == kPfConvStages) { cstage = 0; cphase ^= 1; }
+    }
+  }
+}
+
+// ---------------------------------------------------------------------------------------------------------
+// Per-channel scales: ten warps (TMA, MMA, four epilogue, four converters); the accumulator of a tile is read
+// once, out = acc * s[n] - xsum[m] * s[n] zp[n] + bias[n].
+// ---------------------------------------------------------------------------------------------------------
+template <typename T, int BITS>
 __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(kPfThreads, 1)
 wo_umma_pair_kernel(const __grid_constant__ CUtensorMap tmap_x, const __grid_constant__ CUtensorMap tmap_w,
                     const PfParams p) {
   using L = PfSmem<BITS>;
-  constexpr int STAGES = kPfStages;
-  constexpr int CSTAGES = kPfConvStages;
   extern __shared__ uint8_t smem_raw[];
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
   float* vec_smem = reinterpret_cast<float*>(smem + L::kVecOff);
-  uint64_t* bars = reinterpret_cast<uint64_t*>(smem + L::kBarOff);
-  uint64_t* raw_full = bars;
-  uint64_t* empty_bar = bars + STAGES;
-  uint64_t* conv_full = bars + 2 * STAGES;
-  uint64_t* conv_empty = bars + 2 * STAGES + CSTAGES;
-  uint64_t* conv_done = bars + 2 * STAGES + 2 * CSTAGES;  // peer CTA only: its four converter warps
-  uint64_t* tmem_full_bar = bars + 2 * STAGES + 3 * CSTAGES;
-  uint64_t* tmem_empty_bar = tmem_full_bar + 2;
-  uint64_t* drain_bar = tmem_full_bar + 4;
+  const PfBars b = pf_bars(reinterpret_cast<uint64_t*>(smem + L::kBarOff));
   uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(smem + L::kTmemSlotOff);
   volatile int* abort_flag = reinterpret_cast<volatile int*>(smem + L::kAbortOff);
 
@@ -186,21 +398,7 @@ wo_umma_pair_kernel(const __grid_constant__ CUtensorMap tmap_x, const __grid_con
 
   if (threadIdx.x == 0) {
     *abort_flag = 0;
-    for (int s = 0; s < STAGES; ++s) {
-      mbar_init(&raw_full[s], 1);
-      mbar_init(&empty_bar[s], 1);
-    }
-    for (int s = 0; s < CSTAGES; ++s) {
-      mbar_init(&conv_full[s], 5);  // leader: its 4 converter warps + the peer's relay
-      mbar_init(&conv_done[s], 4);
-      mbar_init(&conv_empty[s], 1);
-    }
-    for (int b = 0; b < 2; ++b) {
-      mbar_init(&tmem_full_bar[b], 1);
-      mbar_init(&tmem_empty_bar[b], 8);
-    }
-    mbar_init(drain_bar, 1);
-    mbar_fence_init();
+    pf_init_bars(b, 8, false);
     tma_prefetch_desc(&tmap_x);
     tma_prefetch_desc(&tmap_w);
   }
@@ -215,111 +413,10 @@ wo_umma_pair_kernel(const __grid_constant__ CUtensorMap tmap_x, const __grid_con
   const uint32_t tmem_base = *tmem_slot;
 
   if (warp == 0) {
-    // ------------------------------ TMA producer (both CTAs) ------------------------------
-    const bool leader_lane = elect_one();
-    int stage = 0;
-    uint32_t phase = 0;
-    long long issued = 0;
-    bool ok = true;
-    for (int t = pair_id; t < num_tiles && ok; t += num_pairs) {
-      int mb, nb;
-      pf_tile_coords(t, p.tiles_m, p.tiles_n, mb, nb);
-      const int w_row = (BITS == 8) ? nb * kTN + int(rank) * (kTN / 2) : (nb * kTN + int(rank) * (kTN / 2)) / 2;
-      for (int kb = 0; kb < p.k_blocks; ++kb) {
-        ok = mbar_wait_bounded(&empty_bar[stage], phase ^ 1, abort_flag);
-        ok = __all_sync(0xffffffffu, ok);
-        if (!ok) {
-          if (leader_lane) pf_report(p.status, abort_flag, DEV_TIMEOUT_PRODUCER);
-          break;
-        }
-        if (leader_lane) {
-          uint8_t* sx = smem + stage * L::kStageBytes;
-          mbar_expect_tx(&raw_full[stage], L::kXBytes + L::kRawBytes);
-          tma_load_2d(sx, &tmap_x, &raw_full[stage], kb * kTK, mb * 256 + int(rank) * kTM);
-          tma_load_2d(sx + L::kXBytes, &tmap_w, &raw_full[stage], kb * kTK, w_row);
-          ++issued;
-        }
-        __syncwarp();
-        if (++stage == STAGES) { stage = 0; phase ^= 1; }
-      }
-    }
-    if (leader_lane) {  // the last stages issued have been consumed (or the CTA is aborting) before exit
-      const long long first = issued > STAGES ? issued - STAGES : 0;
-      for (long long i = first; i < issued; ++i)
-        if (!mbar_wait_bounded(&empty_bar[i % STAGES], uint32_t((i / STAGES) & 1), abort_flag)) break;
-    }
+    pf_producer<BITS>(smem, b, &tmap_x, &tmap_w, p, rank, pair_id, num_pairs, abort_flag);
   } else if (warp == 1) {
-    // ------------------------------- MMA issuer (leader only) -------------------------------
-    const bool leader_lane = elect_one();
-    if (rank == 0) {
-      constexpr uint32_t idesc = umma_idesc(/*f32*/ 1, std::is_same<T, __half>::value ? 0u : 1u, 256, kTN);
-      int stage = 0, cstage = 0;
-      uint32_t phase = 0, cphase = 0;
-      int local = 0;
-      bool ok = true;
-      bool issued_any = false;
-      for (int t = pair_id; t < num_tiles && ok; t += num_pairs, ++local) {
-        const int buf = local & 1;
-        const uint32_t acc_phase = (local >> 1) & 1;
-        ok = mbar_wait_bounded(&tmem_empty_bar[buf], acc_phase ^ 1, abort_flag);
-        ok = __all_sync(0xffffffffu, ok);
-        if (!ok) {
-          if (leader_lane) pf_report(p.status, abort_flag, DEV_TIMEOUT_MMA);
-          break;
-        }
-        tc_fence_after();
-        const uint32_t tmem_d = tmem_base + buf * kTN;
-        for (int kb = 0; kb < p.k_blocks; ++kb) {
-          ok = mbar_wait_bounded(&conv_full[cstage], cphase, abort_flag);
-          ok = __all_sync(0xffffffffu, ok);
-          if (!ok) {
-            if (leader_lane) pf_report(p.status, abort_flag, DEV_TIMEOUT_MMA);
-            break;
-          }
-          tc_fence_after();
-          if (leader_lane) {
-            const uint32_t sx = smem_u32(smem + stage * L::kStageBytes);
-            const uint32_t sw = smem_u32(smem + L::kConvOff + cstage * L::kWBytes);
-#pragma unroll
-            for (int k = 0; k < kTK / 16; ++k)
-              umma_f16_pair(tmem_d, umma_desc_k_sw128(sx + k * 32), umma_desc_k_sw128(sw + k * 32), idesc,
-                            (kb | k) != 0 ? 1u : 0u);
-            tc_commit_pair(&empty_bar[stage], 0x3);     // activations + raw bytes of this stage, both CTAs
-            tc_commit_pair(&conv_empty[cstage], 0x3);   // converted tile, both CTAs
-            issued_any = true;
-          }
-          __syncwarp();
-          if (++stage == STAGES) { stage = 0; phase ^= 1; }
-          if (++cstage == CSTAGES) { cstage = 0; cphase ^= 1; }
-        }
-        if (ok && leader_lane) tc_commit_pair(&tmem_full_bar[buf], 0x3);
-        __syncwarp();
-      }
-      if (leader_lane && issued_any) {
-        int none = 0;
-        tc_commit_pair(drain_bar, 0x1);
-        if (!mbar_wait_bounded(drain_bar, 0, &none)) pf_report(p.status, abort_flag, DEV_TIMEOUT_DRAIN);
-      }
-    } else {
-      // peer CTA: relay "this CTA's converted tile is ready" to the leader's barrier, one remote arrive per
-      // K block, so the converter warps themselves only ever signal locally
-      int cstage = 0;
-      uint32_t cphase = 0;
-      bool ok = true;
-      for (int t = pair_id; t < num_tiles && ok; t += num_pairs) {
-        for (int kb = 0; kb < p.k_blocks; ++kb) {
-          ok = mbar_wait_bounded(&conv_done[cstage], cphase, abort_flag);
-          ok = __all_sync(0xffffffffu, ok);
-          if (!ok) {
-            if (leader_lane) pf_report(p.status, abort_flag, DEV_TIMEOUT_MMA);
-            break;
-          }
-          if (leader_lane) mbar_arrive_cluster(map_to_cta(smem_u32(&conv_full[cstage]), 0));
-          __syncwarp();
-          if (++cstage == CSTAGES) { cstage = 0; cphase ^= 1; }
-        }
-      }
-    }
+    if (rank == 0) pf_mma<T, BITS>(smem, b, p, tmem_base, pair_id, num_pairs, p.k_blocks, abort_flag);
+    else pf_relay(b, p, pair_id, num_pairs, abort_flag);
   } else if (warp < 6) {
     // -------------------------------- epilogue (both CTAs) --------------------------------
     const int quarter = warp & 3;
@@ -339,15 +436,15 @@ wo_umma_pair_kernel(const __grid_constant__ CUtensorMap tmap_x, const __grid_con
       const int n0 = nb * kTN;
       for (int j = lane; j < kTN; j += 32) {
         const bool in = n0 + j < p.N;
-        const float s = GRP ? 1.f : (in ? load_as_f32(p.scale, p.scale_dtype, n0 + j) : 0.f);
+        const float s = in ? load_as_f32(p.scale, p.scale_dtype, n0 + j) : 0.f;
         cs[j] = s;
-        cz[j] = (!GRP && in && p.zp) ? s * load_as_f32(p.zp, p.scale_dtype, n0 + j) : 0.f;
+        cz[j] = (in && p.zp) ? s * load_as_f32(p.zp, p.scale_dtype, n0 + j) : 0.f;
         cb[j] = (in && p.bias) ? load_as_f32(p.bias, p.bias_dtype, n0 + j) : 0.f;
       }
-      const float xs = (!GRP && p.zp && row < p.M) ? p.xsum[row] : 0.f;
+      const float xs = (p.zp && row < p.M) ? p.xsum[row] : 0.f;
       __syncwarp();
 
-      ok = mbar_wait_bounded(&tmem_full_bar[buf], acc_phase, abort_flag);
+      ok = mbar_wait_bounded(&b.tmem_full[buf], acc_phase, abort_flag);
       ok = __all_sync(0xffffffffu, ok);
       if (!ok) {
         if (lane == 0) pf_report(p.status, abort_flag, DEV_TIMEOUT_EPILOGUE);
@@ -382,99 +479,212 @@ wo_umma_pair_kernel(const __grid_constant__ CUtensorMap tmap_x, const __grid_con
       }
       tc_fence_before();
       __syncwarp();
-      if (lane == 0) mbar_arrive_cluster(map_to_cta(smem_u32(&tmem_empty_bar[buf]), 0));
+      if (lane == 0) mbar_arrive_cluster(map_to_cta(smem_u32(&b.tmem_empty[buf]), 0));
     }
   } else {
-    // -------------------------------- converters (both CTAs) --------------------------------
-    const int ct = threadIdx.x - 6 * 32;  // 0..127
-    int stage = 0, cstage = 0;
-    uint32_t phase = 0, cphase = 0;
-    bool ok = true;
-    // group-wise scales: packed (s, s) and (zp, zp) of the four channels this thread converts, reloaded per K group
-    uint32_t gs2[4] = {0, 0, 0, 0}, gz2[4] = {0, 0, 0, 0};
-    const bool has_zp = p.zp != nullptr;
-    const int kb_per_group = GRP ? p.group / kTK : 1;
-    for (int t = pair_id; t < num_tiles && ok; t += num_pairs) {
-      int mb_c, nb_c;
-      pf_tile_coords(t, p.tiles_m, p.tiles_n, mb_c, nb_c);
-      const int ch_base = nb_c * kTN + int(rank) * (kTN / 2);  // first channel of this CTA's half of the tile
-      for (int kb = 0; kb < p.k_blocks; ++kb) {
-        if (GRP && kb % kb_per_group == 0) {
-          const int64_t grow = int64_t(kb / kb_per_group) * p.N;
+    pf_converters<T, BITS>(smem, b, p, rank, pair_id, num_pairs, threadIdx.x - 6 * 32, abort_flag);
+  }
+
+  // -------------------------------- teardown --------------------------------
+  tc_fence_before();
+  __syncthreads();
+  cluster_sync_all();
+  if (warp == 1) {
+    tc_fence_after();
+    tmem_dealloc_pair(tmem_base, kTmemCols);
+  }
+}
+
+// ---------------------------------------------------------------------------------------------------------
+// Group-wise scales, exact in fp32.  The converted weight is the bare integer; the MMA warp gives every scale group
+// (group / 64 K blocks) an accumulator of its own in one of the two TMEM buffers, and the epilogue warps promote it
+// while the next group accumulates in the other buffer:
+//     total[m, n] += s[g, n] * acc_g[m, n] - (s[g, n] zp[g, n]) * xsum_g[m]        (fp32 registers)
+// so w * s is never rounded to 16 bits and the result differs from the fp32 dequant-matmul only by the order of
+// fp32 additions.  A thread owns one token row and 128 channels (128 running sums), so the CTA needs eight
+// epilogue warps (two per TMEM lane quarter, one per column half) and more registers per epilogue thread than an
+// even split of the register file gives: sixteen warps, and the warpgroups re-balance their registers at the start
+// (producer/MMA warpgroup 40, converter warpgroup 56, the two epilogue warpgroups 208 each: 512 x 128 in all).
+//   warps 0-3   TMA producer, MMA issuer / relay, two idle        warps 4-7   converters
+//   warps 8-15  epilogue: quarter = warp % 4, column half = (warp - 8) / 4
+// Per group the 256 epilogue threads stage that group's 256 scales (and s * zp) as fp32 in shared memory, double
+// buffered, handing over through an mbarrier per buffer and column half (every wait in this kernel is bounded).
+// ---------------------------------------------------------------------------------------------------------
+constexpr int kPgThreads = 512;
+
+__device__ __forceinline__ void ffma2(uint64_t& d, uint32_t a0, uint32_t a1, float b0, float b1) {
+  uint64_t a, b;
+  asm("mov.b64 %0, {%1, %2};" : "=l"(a) : "r"(a0), "r"(a1));
+  asm("mov.b64 %0, {%1, %2};" : "=l"(b) : "f"(b0), "f"(b1));
+  asm("fma.rn.f32x2 %0, %1, %2, %0;" : "+l"(d) : "l"(a), "l"(b));
+}
+__device__ __forceinline__ void unpack2(uint64_t v, float& lo, float& hi) {
+  asm("mov.b64 {%0, %1}, %2;" : "=f"(lo), "=f"(hi) : "l"(v));
+}
+
+template <typename T, int BITS, bool HAS_ZP>
+__global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(kPgThreads, 1)
+wo_umma_pair_group_kernel(const __grid_constant__ CUtensorMap tmap_x, const __grid_constant__ CUtensorMap tmap_w,
+                          const PfParams p) {
+  using L = PfSmem<BITS>;
+  extern __shared__ uint8_t smem_raw[];
+  uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
+  float* vec_smem = reinterpret_cast<float*>(smem + L::kVecOff);
+  const PfBars b = pf_bars(reinterpret_cast<uint64_t*>(smem + L::kBarOff));
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(smem + L::kTmemSlotOff);
+  volatile int* abort_flag = reinterpret_cast<volatile int*>(smem + L::kAbortOff);
+
+  const int warp = threadIdx.x >> 5;
+  const int lane = threadIdx.x & 31;
+  const uint32_t rank = cluster_ctarank();
+  const int pair_id = blockIdx.x >> 1;
+  const int num_pairs = gridDim.x >> 1;
+  const int num_tiles = p.tiles_m * p.tiles_n;
+  constexpr uint32_t kTmemCols = 2 * kTN;
+
+  if (threadIdx.x == 0) {
+    *abort_flag = 0;
+    pf_init_bars(b, 16, true);
+    tma_prefetch_desc(&tmap_x);
+    tma_prefetch_desc(&tmap_w);
+  }
+  if (warp == 1) {
+    tmem_alloc_pair(tmem_slot, kTmemCols);
+    tmem_relinquish_pair();
+  }
+  tc_fence_before();
+  __syncthreads();
+  cluster_sync_all();
+  tc_fence_after();
+  const uint32_t tmem_base = *tmem_slot;
+  const int kb_per_group = p.group / kTK;
+
+  if (warp < 4) {
+    asm volatile("setmaxnreg.dec.sync.aligned.u32 40;");
+    if (warp == 0) {
+      pf_producer<BITS>(smem, b, &tmap_x, &tmap_w, p, rank, pair_id, num_pairs, abort_flag);
+    } else if (warp == 1) {
+      if (rank == 0) pf_mma<T, BITS>(smem, b, p, tmem_base, pair_id, num_pairs, kb_per_group, abort_flag);
+      else pf_relay(b, p, pair_id, num_pairs, abort_flag);
+    }
+  } else if (warp < 8) {
+    asm volatile("setmaxnreg.dec.sync.aligned.u32 56;");
+    pf_converters<T, BITS>(smem, b, p, rank, pair_id, num_pairs, threadIdx.x - 4 * 32, abort_flag);
+  } else {
+    asm volatile("setmaxnreg.inc.sync.aligned.u32 208;");
+    // -------------------------------- epilogue (both CTAs) --------------------------------
+    const int e = threadIdx.x - 8 * 32;  // 0..255: the tile column whose scale, zero-point and bias this thread stages
+    const int quarter = warp & 3;
+    const int half = (warp - 8) >> 2;
+    float* sS = vec_smem;            // [2][kTN] scale of the group in flight
+    float* sZ = sS + 2 * kTN;        // [2][kTN] scale * zero-point
+    float* sB = sZ + 2 * kTN;        // [2][kTN] bias, by tile parity
+    T* out = reinterpret_cast<T*>(p.out);
+    const bool vec_ok = (p.ldo % 8 == 0) && (reinterpret_cast<uintptr_t>(out) % 16 == 0);
+    const int groups = p.K / p.group;
+    uint64_t sum2[64];
 #pragma unroll
-          for (int i = 0; i < 4; ++i) {
-            // int8: rows ct/4 + 32 i; int4: packed rows ct/4 + 32 (i / 2), channel 2 * prow + (i & 1)
-            const int ch = ch_base + ((BITS == 8) ? (ct >> 2) + 32 * i : 2 * ((ct >> 2) + 32 * (i >> 1)) + (i & 1));
-            const float sv = ch < p.N ? load_as_f32(p.scale, p.scale_dtype, grow + ch) : 0.f;
-            const float zv = (has_zp && ch < p.N) ? load_as_f32(p.zp, p.scale_dtype, grow + ch) : 0.f;
-            gs2[i] = pack2<T>(sv, sv);
-            gz2[i] = pack2<T>(zv, zv);
-          }
-        }
-        ok = mbar_wait_bounded(&conv_empty[cstage], cphase ^ 1, abort_flag) &&
-             mbar_wait_bounded(&raw_full[stage], phase, abort_flag);
+    for (int i = 0; i < 64; ++i) sum2[i] = 0ull;
+    // scale (and scale * zero-point) of column e for (tile column block nb, group g)
+    auto load_scale = [&](int nb, int g, float& s, float& z) {
+      const int ch = nb * kTN + e;
+      const bool in = ch < p.N;
+      const int64_t at = int64_t(g) * p.N + ch;
+      s = in ? load_as_f32(p.scale, p.scale_dtype, at) : 0.f;
+      z = (HAS_ZP && in) ? s * load_as_f32(p.zp, p.scale_dtype, at) : 0.f;
+    };
+    float ps = 0.f, pz = 0.f;  // prefetched for the segment about to start
+    if (pair_id < num_tiles) {
+      int mb0, nb0;
+      pf_tile_coords(pair_id, p.tiles_m, p.tiles_n, mb0, nb0);
+      load_scale(nb0, 0, ps, pz);
+    }
+    int seg = 0, local = 0;
+    bool ok = true;
+    for (int t = pair_id; t < num_tiles && ok; t += num_pairs, ++local) {
+      int mb, nb;
+      pf_tile_coords(t, p.tiles_m, p.tiles_n, mb, nb);
+      int nb_next = -1;
+      if (t + num_pairs < num_tiles) {
+        int mbn;
+        pf_tile_coords(t + num_pairs, p.tiles_m, p.tiles_n, mbn, nb_next);
+      }
+      const int row = mb * 256 + int(rank) * kTM + quarter * 32 + lane;
+      const int n0 = nb * kTN;
+      sB[(local & 1) * kTN + e] = (p.bias && n0 + e < p.N) ? load_as_f32(p.bias, p.bias_dtype, n0 + e) : 0.f;
+      for (int g = 0; g < groups; ++g, ++seg) {
+        const int buf = seg & 1;
+        const uint32_t seg_phase = (seg >> 1) & 1;
+        sS[buf * kTN + e] = ps;
+        if (HAS_ZP) sZ[buf * kTN + e] = pz;
+        __syncwarp();
+        if (lane == 0) mbar_arrive(&b.scale_full[buf * 2 + half]);
+        if (g + 1 < groups) load_scale(nb, g + 1, ps, pz);
+        else if (nb_next >= 0) load_scale(nb_next, 0, ps, pz);
+        float nxg = 0.f;
+        if (HAS_ZP && row < p.M) nxg = -p.xsum[int64_t(g) * p.M + row];
+        ok = mbar_wait_bounded(&b.scale_full[buf * 2 + half], seg_phase, abort_flag) &&
+             mbar_wait_bounded(&b.tmem_full[buf], seg_phase, abort_flag);
         ok = __all_sync(0xffffffffu, ok);
         if (!ok) {
           if (lane == 0) pf_report(p.status, abort_flag, DEV_TIMEOUT_EPILOGUE);
           break;
         }
-        uint8_t* sw = smem + L::kConvOff + cstage * L::kWBytes;                // converted tile: 128 rows x 128 B, swizzled
-        const uint8_t* raw = smem + stage * L::kStageBytes + L::kXBytes;       // raw tile: rows of 64 B, not swizzled
-        if (BITS == 8) {
-          // 128 rows x 4 chunks of 16 bytes; chunk id -> (row = id / 4, c = id % 4): 16 k -> 32 bytes out
+        tc_fence_after();
+        const uint32_t taddr = tmem_base + (uint32_t(quarter * 32) << 16) + buf * kTN + half * 128;
+        const float4* s4 = reinterpret_cast<const float4*>(sS + buf * kTN + half * 128);
+        const float4* z4 = reinterpret_cast<const float4*>(sZ + buf * kTN + half * 128);
 #pragma unroll
-          for (int i = 0; i < 4; ++i) {
-            const int id = ct + i * 128;
-            const uint32_t row = id >> 2, c = id & 3;
-            const uint4 w = *reinterpret_cast<const uint4*>(raw + id * 16);
-            uint4 o0, o1;
-            cvt_int8x4<T>(w.x, o0.x, o0.y);
-            cvt_int8x4<T>(w.y, o0.z, o0.w);
-            cvt_int8x4<T>(w.z, o1.x, o1.y);
-            cvt_int8x4<T>(w.w, o1.z, o1.w);
-            if (GRP) {
-              o0.x = pf_dequant2<T>(o0.x, gs2[i], gz2[i], has_zp); o0.y = pf_dequant2<T>(o0.y, gs2[i], gz2[i], has_zp);
-              o0.z = pf_dequant2<T>(o0.z, gs2[i], gz2[i], has_zp); o0.w = pf_dequant2<T>(o0.w, gs2[i], gz2[i], has_zp);
-              o1.x = pf_dequant2<T>(o1.x, gs2[i], gz2[i], has_zp); o1.y = pf_dequant2<T>(o1.y, gs2[i], gz2[i], has_zp);
-              o1.z = pf_dequant2<T>(o1.z, gs2[i], gz2[i], has_zp); o1.w = pf_dequant2<T>(o1.w, gs2[i], gz2[i], has_zp);
-            }
-            *reinterpret_cast<uint4*>(sw + sw128(row, 2 * c)) = o0;
-            *reinterpret_cast<uint4*>(sw + sw128(row, 2 * c + 1)) = o1;
-          }
-        } else {
-          // 64 packed rows x 4 chunks; packed row j carries channel rows 2j (low nibbles) and 2j+1 (high)
+        for (int c = 0; c < 4; ++c) {
+          uint32_t r[32];
+          tmem_ld_32x32(taddr + c * 32, r);
+          tc_wait_ld();
 #pragma unroll
-          for (int i = 0; i < 2; ++i) {
-            const int id = ct + i * 128;
-            const uint32_t prow = id >> 2, c = id & 3;
-            const uint4 w = *reinterpret_cast<const uint4*>(raw + id * 16);
-            uint4 l0, l1, h0, h1;
-            cvt_int4x8<T>(w.x, l0.x, l0.y, h0.x, h0.y);
-            cvt_int4x8<T>(w.y, l0.z, l0.w, h0.z, h0.w);
-            cvt_int4x8<T>(w.z, l1.x, l1.y, h1.x, h1.y);
-            cvt_int4x8<T>(w.w, l1.z, l1.w, h1.z, h1.w);
-            if (GRP) {
-              const uint32_t sl = gs2[2 * i], zl = gz2[2 * i], sh = gs2[2 * i + 1], zh = gz2[2 * i + 1];
-              l0.x = pf_dequant2<T>(l0.x, sl, zl, has_zp); l0.y = pf_dequant2<T>(l0.y, sl, zl, has_zp);
-              l0.z = pf_dequant2<T>(l0.z, sl, zl, has_zp); l0.w = pf_dequant2<T>(l0.w, sl, zl, has_zp);
-              l1.x = pf_dequant2<T>(l1.x, sl, zl, has_zp); l1.y = pf_dequant2<T>(l1.y, sl, zl, has_zp);
-              l1.z = pf_dequant2<T>(l1.z, sl, zl, has_zp); l1.w = pf_dequant2<T>(l1.w, sl, zl, has_zp);
-              h0.x = pf_dequant2<T>(h0.x, sh, zh, has_zp); h0.y = pf_dequant2<T>(h0.y, sh, zh, has_zp);
-              h0.z = pf_dequant2<T>(h0.z, sh, zh, has_zp); h0.w = pf_dequant2<T>(h0.w, sh, zh, has_zp);
-              h1.x = pf_dequant2<T>(h1.x, sh, zh, has_zp); h1.y = pf_dequant2<T>(h1.y, sh, zh, has_zp);
-              h1.z = pf_dequant2<T>(h1.z, sh, zh, has_zp); h1.w = pf_dequant2<T>(h1.w, sh, zh, has_zp);
+          for (int j = 0; j < 32; j += 4) {
+            const float4 sv = s4[(c * 32 + j) >> 2];
+            ffma2(sum2[(c * 32 + j) >> 1], r[j], r[j + 1], sv.x, sv.y);
+            ffma2(sum2[((c * 32 + j) >> 1) + 1], r[j + 2], r[j + 3], sv.z, sv.w);
+            if (HAS_ZP) {
+              const float4 zv = z4[(c * 32 + j) >> 2];
+              const uint32_t nx = __float_as_uint(nxg);
+              ffma2(sum2[(c * 32 + j) >> 1], nx, nx, zv.x, zv.y);
+              ffma2(sum2[((c * 32 + j) >> 1) + 1], nx, nx, zv.z, zv.w);
             }
-            *reinterpret_cast<uint4*>(sw + sw128(2 * prow, 2 * c)) = l0;
-            *reinterpret_cast<uint4*>(sw + sw128(2 * prow, 2 * c + 1)) = l1;
-            *reinterpret_cast<uint4*>(sw + sw128(2 * prow + 1, 2 * c)) = h0;
-            *reinterpret_cast<uint4*>(sw + sw128(2 * prow + 1, 2 * c + 1)) = h1;
           }
         }
-        fence_proxy_async_smem();  // the tensor core reads these bytes through the async proxy
+        tc_fence_before();
         __syncwarp();
-        if (lane == 0) mbar_arrive(rank == 0 ? &conv_full[cstage] : &conv_done[cstage]);
-        if (++stage == STAGES) { stage = 0; phase ^= 1; }
-        if (++cstage == CSTAGES) { cstage = 0; cphase ^= 1; }
+        if (lane == 0) mbar_arrive_cluster(map_to_cta(smem_u32(&b.tmem_empty[buf]), 0));
+      }
+      if (!ok) break;
+      // the tile's sums are complete: add the bias, round once, store, and clear the sums for the next tile
+      const float* cb = sB + (local & 1) * kTN + half * 128;
+      T* orow0 = out + int64_t(row) * p.ldo + n0 + half * 128;
+#pragma unroll
+      for (int c = 0; c < 4; ++c) {
+        float v[32];
+#pragma unroll
+        for (int j = 0; j < 32; j += 2) {
+          unpack2(sum2[(c * 32 + j) >> 1], v[j], v[j + 1]);
+          v[j] += cb[c * 32 + j];
+          v[j + 1] += cb[c * 32 + j + 1];
+          sum2[(c * 32 + j) >> 1] = 0ull;
+        }
+        const int col0 = n0 + half * 128 + c * 32;
+        if (row < p.M && col0 < p.N) {
+          T* orow = orow0 + c * 32;
+          if (col0 + 32 <= p.N && vec_ok) {
+#pragma unroll
+            for (int j = 0; j < 32; j += 8)
+              *reinterpret_cast<uint4*>(orow + j) =
+                  make_uint4(pack2<T>(v[j], v[j + 1]), pack2<T>(v[j + 2], v[j + 3]), pack2<T>(v[j + 4], v[j + 5]),
+                             pack2<T>(v[j + 6], v[j + 7]));
+          } else {
+#pragma unroll
+            for (int j = 0; j < 32; ++j)
+              if (col0 + j < p.N) orow[j] = from_f32<T>(v[j]);
+          }
+        }
       }
     }
   }
@@ -503,23 +713,48 @@ __global__ void row_sum_kernel(const T* __restrict__ act, int64_t lda, float* __
   if (lane == 0) xsum[row] = s;
 }
 
-template <typename T, int BITS, bool GRP>
-int launch_prefill_g(const T* act, int64_t lda, const uint8_t* qw, PfParams p, float* xsum_ws, cudaStream_t st) {
-  using L = PfSmem<BITS>;
-  static_assert(L::kDynamicBytes <= 227 * 1024, "shared memory budget");
-  static_assert(L::kStageBytes % 1024 == 0 && L::kWBytes % 1024 == 0 && L::kConvOff % 1024 == 0, "tile alignment");
-  auto kern = wo_umma_pair_kernel<T, BITS, GRP>;
-  static std::once_flag once[64];
-  static cudaError_t attr_err[64];  // per device, so that a failure is reported on every call and not only the first
+// xsum[g, m] = sum of x[m, k] over the k of scale group g, in fp32; one warp per row, group after group
+template <typename T>
+__global__ void row_group_sum_kernel(const T* __restrict__ act, int64_t lda, float* __restrict__ xsum, int M, int K,
+                                     int group) {
+  const int64_t row = (int64_t(blockIdx.x) * blockDim.x + threadIdx.x) >> 5;
+  const int lane = threadIdx.x & 31;
+  if (row >= M) return;
+  const T* x = act + row * lda;
+  for (int g = 0; g * group < K; ++g) {
+    float s = 0.f;
+    for (int i = lane; i < group; i += 32) s += to_f32(x[g * group + i]);
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) s += __shfl_xor_sync(0xffffffffu, s, o);
+    if (lane == 0) xsum[int64_t(g) * M + row] = s;
+  }
+}
+
+template <typename KernT>
+int pf_configure(KernT kern, int bytes, cudaError_t (&attr_err)[64], std::once_flag (&once)[64]) {
   int dev = 0;
   cudaGetDevice(&dev);
   dev &= 63;
-  std::call_once(once[dev], [&] {
-    attr_err[dev] = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, L::kDynamicBytes);
-  });
-  if (attr_err[dev] != cudaSuccess) return check_cuda(attr_err[dev], "cudaFuncSetAttribute(weight-only prefill)");
-  if (p.zp && !GRP) {
-    row_sum_kernel<T><<<unsigned((int64_t(p.M) * 32 + 255) / 256), 256, 0, st>>>(act, lda, xsum_ws, p.M, p.K);
+  std::call_once(once[dev], [&] { attr_err[dev] = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, bytes); });
+  return attr_err[dev] == cudaSuccess ? FNN_OK : check_cuda(attr_err[dev], "cudaFuncSetAttribute(weight-only prefill)");
+}
+
+template <typename T, int BITS>
+int launch_prefill(const T* act, int64_t lda, const uint8_t* qw, PfParams p, float* xsum_ws, cudaStream_t st) {
+  using L = PfSmem<BITS>;
+  static_assert(L::kDynamicBytes <= 227 * 1024, "shared memory budget");
+  static_assert(L::kStageBytes % 1024 == 0 && L::kWBytes % 1024 == 0 && L::kConvOff % 1024 == 0, "tile alignment");
+  // per device, so that a failure is reported on every call and not only the first
+  static std::once_flag once[3][64];
+  static cudaError_t attr_err[3][64];
+  const int which = p.group == 0 ? 0 : (p.zp ? 2 : 1);
+  if (which == 0) { if (int e = pf_configure(wo_umma_pair_kernel<T, BITS>, L::kDynamicBytes, attr_err[0], once[0])) return e; }
+  else if (which == 1) { if (int e = pf_configure(wo_umma_pair_group_kernel<T, BITS, false>, L::kDynamicBytes, attr_err[1], once[1])) return e; }
+  else { if (int e = pf_configure(wo_umma_pair_group_kernel<T, BITS, true>, L::kDynamicBytes, attr_err[2], once[2])) return e; }
+  if (p.zp) {
+    const unsigned blocks = unsigned((int64_t(p.M) * 32 + 255) / 256);
+    if (p.group == 0) row_sum_kernel<T><<<blocks, 256, 0, st>>>(act, lda, xsum_ws, p.M, p.K);
+    else row_group_sum_kernel<T><<<blocks, 256, 0, st>>>(act, lda, xsum_ws, p.M, p.K, p.group);
     if (int e = check_cuda(cudaGetLastError(), "row_sum launch")) return e;
     p.xsum = xsum_ws;
   }
@@ -532,14 +767,10 @@ int launch_prefill_g(const T* act, int64_t lda, const uint8_t* qw, PfParams p, f
   p.k_blocks = (p.K + kTK - 1) / kTK;
   const int tiles = p.tiles_m * p.tiles_n;
   const int pairs = tiles < sm_count() / 2 ? tiles : sm_count() / 2;
-  kern<<<2 * pairs, kPfThreads, L::kDynamicBytes, st>>>(tx, tw, p);
+  if (which == 0) wo_umma_pair_kernel<T, BITS><<<2 * pairs, kPfThreads, L::kDynamicBytes, st>>>(tx, tw, p);
+  else if (which == 1) wo_umma_pair_group_kernel<T, BITS, false><<<2 * pairs, kPgThreads, L::kDynamicBytes, st>>>(tx, tw, p);
+  else wo_umma_pair_group_kernel<T, BITS, true><<<2 * pairs, kPgThreads, L::kDynamicBytes, st>>>(tx, tw, p);
   return check_cuda(cudaGetLastError(), "weight-only prefill launch");
-}
-
-template <typename T, int BITS>
-int launch_prefill(const T* act, int64_t lda, const uint8_t* qw, PfParams p, float* xsum_ws, cudaStream_t st) {
-  return p.group > 0 ? launch_prefill_g<T, BITS, true>(act, lda, qw, p, xsum_ws, st)
-                     : launch_prefill_g<T, BITS, false>(act, lda, qw, p, xsum_ws, st);
 }
 
 }  // namespace
@@ -554,8 +785,8 @@ int weight_only_prefill(const void* act, int act_dtype, int64_t lda, const void*
   if (reinterpret_cast<uintptr_t>(qweight) % 16 != 0 || K % 16 != 0) return -1;
   if (bits == 4 && N % 2 != 0) return -1;
   float* xsum = nullptr;
-  if (zp && group == 0) {
-    const size_t need = size_t(M) * sizeof(float);
+  if (zp) {
+    const size_t need = size_t(M) * sizeof(float) * (group == 0 ? 1 : size_t(K / group));
     if (!workspace || workspace_bytes < need)
       return fail(FNN_ERR_WORKSPACE, "gemm_weight_only: zero-points need %zu bytes of workspace, got %zu", need, workspace_bytes);
     if (reinterpret_cast<uintptr_t>(workspace) % 256 != 0) return fail(FNN_ERR_ALIGNMENT, "gemm_weight_only: workspace must be 256-byte aligned");

@@ -810,9 +810,11 @@ int launch_wo(WoParams p, void* workspace, size_t workspace_bytes, cudaStream_t 
 }  // namespace fnn
 
 extern "C" size_t fnn_gemm_weight_only_workspace_bytes(int64_t M, int64_t N, int64_t K, int weight_bits, int64_t group_size) {
-  (void)N; (void)K; (void)weight_bits;
-  // prefill kernel (M > 16, per-channel scales): row sums of the activations, read when zero-points are given
+  (void)N; (void)weight_bits;
+  // prefill kernels (M > 16): row sums of the activations, one per row or one per row and scale group, read when
+  // zero-points are given
   if (M > 16 && group_size == 0) return (size_t(M) * sizeof(float) + 255) / 256 * 256;
+  if (M > 16 && group_size > 0 && K > 0) return (size_t(M) * size_t((K + group_size - 1) / group_size) * sizeof(float) + 255) / 256 * 256;
   return 0;  // neither the decode kernel nor the generic kernel uses scratch
 }
 
