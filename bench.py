@@ -772,6 +772,9 @@ def run_case(args):
         op = flashnn_b200.GemmA8W8(torch.bfloat16)
         fn = lambda: op(a, b, row, col)
         work, unit = W.a8w8_ops(m, n, k) / 1e12, "TOPS"
+        if args.tile:
+            from flashnn_b200 import _lib
+            _lib.set_option(_lib.OPT_A8W8_PAIR_TILE, args.tile)
     elif name == "gemv":
         m, n, k = args.m or 1, args.n or 28672, args.k or 8192
         w = W.a16w4_decode(m, n, k)
@@ -848,6 +851,7 @@ def main():
     ap.add_argument("--no-triton-reference", action="store_true", help="skip timing the reference's Triton kernels (extra.reference_triton)")
     ap.add_argument("--case", choices=["a8w8", "gemv", "gemv8", "dq", "wo", "wog", "rmsdq", "lndq", "moe", "ref_triton", "sweep"],
                     help="run one kernel only (profiling / A-B timing), the reference's Triton kernels, or the reference's shape sweep")
+    ap.add_argument("--tile", type=int, default=0, help="with --case a8w8: force this CTA-pair tile width (tuning)")
     ap.add_argument("--m", type=int)
     ap.add_argument("--n", type=int)
     ap.add_argument("--k", type=int)

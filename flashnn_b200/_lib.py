@@ -94,6 +94,7 @@ def check(status: int):
 
 OPT_STATIC_WEIGHTS = 1
 OPT_TEST_STALL_US = 2  # test hook, see include/flashnn_b200.h
+OPT_A8W8_PAIR_TILE = 3  # tuning hook
 
 
 def set_option(option: int, value: int) -> None:

@@ -54,7 +54,9 @@ int check_cuda(cudaError_t e, const char* what) {
 namespace {
 std::atomic<int> g_opt_static_weights{0};
 std::atomic<int> g_opt_test_stall_us{0};
+std::atomic<int> g_opt_a8w8_pair_tile{0};
 }
+int opt_a8w8_pair_tile() { return g_opt_a8w8_pair_tile.load(std::memory_order_relaxed); }
 bool opt_static_weights() { return g_opt_static_weights.load(std::memory_order_relaxed) != 0; }
 int opt_test_stall_us() { return g_opt_test_stall_us.load(std::memory_order_relaxed); }
 
@@ -119,12 +121,19 @@ extern "C" int fnn_set_option(int option, int value) {
     fnn::g_opt_test_stall_us.store(value, std::memory_order_relaxed);
     return FNN_OK;
   }
+  if (option == FNN_OPT_A8W8_PAIR_TILE) {
+    if (value != 0 && value != 256 && value != 224 && value != 192 && value != 160 && value != 128)
+      return fnn::fail(FNN_ERR_UNSUPPORTED, "fnn_set_option: FNN_OPT_A8W8_PAIR_TILE takes 0, 128, 160, 192, 224 or 256 (got %d)", value);
+    fnn::g_opt_a8w8_pair_tile.store(value, std::memory_order_relaxed);
+    return FNN_OK;
+  }
   return fnn::fail(FNN_ERR_UNSUPPORTED, "fnn_set_option: unknown option %d", option);
 }
 
 extern "C" int fnn_get_option(int option) {
   if (option == FNN_OPT_STATIC_WEIGHTS) return fnn::g_opt_static_weights.load(std::memory_order_relaxed);
   if (option == FNN_OPT_TEST_STALL_US) return fnn::g_opt_test_stall_us.load(std::memory_order_relaxed);
+  if (option == FNN_OPT_A8W8_PAIR_TILE) return fnn::g_opt_a8w8_pair_tile.load(std::memory_order_relaxed);
   return -1;
 }
 

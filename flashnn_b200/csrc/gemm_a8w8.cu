@@ -19,6 +19,7 @@
 
 #include <type_traits>
 
+#include "a8w8_plan.h"
 #include "common.cuh"
 #include "weight_only.cuh"
 
@@ -377,8 +378,9 @@ a8w8_umma_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_consta
 }
 
 // ---------------------------------------------------------------------------
-// CTA-pair variant (cluster of 2, tcgen05 cta_group::2): one 256 x 256 output tile per pair.
-// CTA r of the pair loads rows [128 r, 128 r + 128) of the A tile and of the B tile (no multicast:
+// CTA-pair variant (cluster of 2, tcgen05 cta_group::2): one 256 x BN output tile per pair (BN = 256 unless a
+// narrower tile fills the last wave better, see pick_pair_bn).
+// CTA r of the pair loads rows [128 r, 128 r + 128) of the A tile and its half of the B tile's rows (no multicast:
 // every CTA fetches exactly the bytes that end up in its own shared memory), so each stage is
 // 32 KB per CTA for the same MMA work that takes 48 KB in the single-CTA kernel: a third less
 // L2->SM traffic and a deeper ring in the same shared memory.  The leader CTA (rank 0) issues
@@ -390,10 +392,10 @@ a8w8_umma_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_consta
 //   tmem_full[b]   in each CTA; signalled the same way when a tile's accumulator is complete
 //   tmem_empty[b]  in the leader; 8 arrivals (4 epilogue warps of each CTA, the peer's remotely)
 // ---------------------------------------------------------------------------
-template <int STAGES> struct PairSmem {
-  static constexpr int kBN = 256;
+template <int BN, int STAGES> struct PairSmem {
+  static constexpr int kBN = BN;                        // output columns of a pair tile (a multiple of 32, at most 256)
   static constexpr int kABytes = kBM * kBK;             // this CTA's 128 rows of A
-  static constexpr int kBBytes = (kBN / 2) * kBK;       // this CTA's 128 rows of B
+  static constexpr int kBBytes = (kBN / 2) * kBK;       // this CTA's BN / 2 rows of B
   static constexpr int kStageBytes = kABytes + kBBytes;
   static constexpr int kColScaleOff = STAGES * kStageBytes;  // [4][kBN] float
   static constexpr int kBarOff = kColScaleOff + 4 * kBN * 4;
@@ -404,12 +406,12 @@ template <int STAGES> struct PairSmem {
   static constexpr int kDynamicBytes = kTotal + 1024;
 };
 
-template <typename OutT, int STAGES>
+template <typename OutT, int BN, int STAGES>
 __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(kThreads, 1)
 a8w8_umma_pair_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ CUtensorMap tmap_b,
                       const A8W8Params p) {
-  using L = PairSmem<STAGES>;
-  constexpr int BN = L::kBN;
+  using L = PairSmem<BN, STAGES>;
+  constexpr int kAccStride = 256;  // TMEM columns between the two accumulators (512 are allocated whatever BN is)
   extern __shared__ uint8_t smem_raw[];
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
   float* col_scale_smem = reinterpret_cast<float*>(smem + L::kColScaleOff);
@@ -427,8 +429,8 @@ a8w8_umma_pair_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_c
   const uint32_t rank = cluster_ctarank();  // 0 = leader
   const int pair_id = blockIdx.x >> 1;
   const int num_pairs = gridDim.x >> 1;
-  const int num_tiles = p.tiles_m * p.tiles_n;  // 256 x 256 tiles
-  constexpr uint32_t kTmemCols = 2 * BN;
+  const int num_tiles = p.tiles_m * p.tiles_n;  // 256 x BN tiles
+  constexpr uint32_t kTmemCols = 2 * kAccStride;
 
   if (threadIdx.x == 0) {
     *abort_flag = 0;
@@ -477,7 +479,7 @@ a8w8_umma_pair_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_c
           const uint32_t full_in_leader = map_to_cta(smem_u32(&full_bar[stage]), 0);
           if (rank == 0) mbar_expect_tx(&full_bar[stage], 2 * L::kStageBytes);
           tma_load_2d_pair(sa, &tmap_a, full_in_leader, kb * kBK, mb * 256 + int(rank) * 128);
-          tma_load_2d_pair(sa + L::kABytes, &tmap_b, full_in_leader, kb * kBK, nb * BN + int(rank) * 128);
+          tma_load_2d_pair(sa + L::kABytes, &tmap_b, full_in_leader, kb * kBK, nb * BN + int(rank) * (BN / 2));
           ++issued;
         }
         __syncwarp();
@@ -511,7 +513,7 @@ a8w8_umma_pair_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_c
           break;
         }
         tc_fence_after();
-        const uint32_t tmem_d = tmem_base + buf * BN;
+        const uint32_t tmem_d = tmem_base + buf * kAccStride;
         for (int kb = 0; kb < p.k_blocks; ++kb) {
           ok = mbar_wait_bounded(&full_bar[stage], phase, abort_flag);
           ok = __all_sync(0xffffffffu, ok);
@@ -571,7 +573,7 @@ a8w8_umma_pair_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_c
         break;
       }
       tc_fence_after();
-      const uint32_t taddr = tmem_base + (uint32_t(quarter * 32) << 16) + buf * BN;
+      const uint32_t taddr = tmem_base + (uint32_t(quarter * 32) << 16) + buf * kAccStride;
 #pragma unroll 1
       for (int c = 0; c < BN / 32; ++c) {
         uint32_t r[32];
@@ -662,11 +664,15 @@ int launch_umma_rows(const int8_t* a, int64_t lda, const int8_t* b, int64_t ldb,
   return launch_umma<OutT, BN, kBudget / ((kBM + BN) * kBK) < 8 ? kBudget / ((kBM + BN) * kBK) : 8, kBM>(a, lda, b, ldb, p, st);
 }
 
-template <typename OutT, int STAGES>
+template <typename OutT, int BN>
 int launch_pair(const int8_t* a, int64_t lda, const int8_t* b, int64_t ldb, A8W8Params p, cudaStream_t st) {
-  using L = PairSmem<STAGES>;
+  constexpr int kBudget = 212 * 1024;
+  constexpr int STAGES = kBudget / (kBM * kBK + (BN / 2) * kBK) < 8 ? kBudget / (kBM * kBK + (BN / 2) * kBK) : 8;
+  using L = PairSmem<BN, STAGES>;
   static_assert(L::kDynamicBytes <= 227 * 1024, "shared memory budget");
-  auto kern = a8w8_umma_pair_kernel<OutT, STAGES>;
+  static_assert(L::kStageBytes % 1024 == 0 && L::kABytes % 1024 == 0, "tiles must stay 1024-byte aligned");
+  static_assert(BN % 32 == 0 && BN <= 256, "pair tile width");
+  auto kern = a8w8_umma_pair_kernel<OutT, BN, STAGES>;
   static std::once_flag once[64];
   static cudaError_t attr_err[64];  // per device, so that a failure is reported on every call and not only the first
   int dev = 0;
@@ -678,14 +684,59 @@ int launch_pair(const int8_t* a, int64_t lda, const int8_t* b, int64_t ldb, A8W8
   if (attr_err[dev] != cudaSuccess) return check_cuda(attr_err[dev], "cudaFuncSetAttribute(a8w8 pair)");
   CUtensorMap ta, tb;
   if (int e = make_tmap_i8(&ta, a, p.M, p.K, lda, kBM)) return e;
-  if (int e = make_tmap_i8(&tb, b, p.N, p.K, ldb, L::kBN / 2)) return e;
+  if (int e = make_tmap_i8(&tb, b, p.N, p.K, ldb, BN / 2)) return e;
   p.tiles_m = (p.M + 255) / 256;
-  p.tiles_n = (p.N + L::kBN - 1) / L::kBN;
+  p.tiles_n = (p.N + BN - 1) / BN;
   p.k_blocks = (p.K + kBK - 1) / kBK;
   const int tiles = p.tiles_m * p.tiles_n;
   const int pairs = tiles < sm_count() / 2 ? tiles : sm_count() / 2;
   kern<<<2 * pairs, kThreads, L::kDynamicBytes, st>>>(ta, tb, p);
   return check_cuda(cudaGetLastError(), "a8w8 tcgen05 (CTA pair) launch");
+}
+
+// ---------------------------------------------------------------------------
+// Shape -> kernel and tile (the static counterpart of the reference's autotune cache,
+// flashnn/triton_kernels/triton_utils.py:84-151).  Both tensor-core kernels are persistent, so the time of a launch
+// is waves x time of one tile; the plan with the least column-work per SM wins:
+//   CTA pair, tile 256 x BN, BN in kPairWidths:  ceil(tiles / (SMs / 2)) * BN * kPairColumnCost[BN]
+//   single CTA, tile 128 x BN, BN in {256, 128, 64}:  ceil(tiles / SMs) * BN * kSingleCtaPenalty
+// The constants are measured (a8w8_plan.h, generated by flashnn_b200/tune_a8w8.py): a narrower pair tile re-reads
+// the A rows for fewer output columns, and the single-CTA kernel moves half as many output columns per byte of
+// operand traffic; it wins where the problem is too small to give every CTA pair a tile.  Problems of at
+// most 128 rows are bound by the weight stream instead and keep their own rule.
+// ---------------------------------------------------------------------------
+struct A8W8Plan {
+  bool pair;
+  int bn;
+  double cost;  // column-work per SM, in columns of a 128-row tile
+};
+
+A8W8Plan plan_a8w8(int M, int N, int sms) {
+  A8W8Plan best{false, 64, 1e30};
+  const int tiles_m1 = (M + kBM - 1) / kBM;
+  if (M <= kBM) {
+    // one row of tiles (decode shapes): bound by the weight stream, not by the tensor pipe; the widest tile that
+    // still gives every SM work keeps the most bytes in flight per CTA
+    if (((N + 255) / 256) >= sms) return A8W8Plan{false, 256, 0.0};
+    if (((N + 127) / 128) >= sms) return A8W8Plan{false, 128, 0.0};
+    return A8W8Plan{false, 64, 0.0};
+  }
+  for (int bn : {256, 128, 64}) {
+    const long long tiles = 1ll * tiles_m1 * ((N + bn - 1) / bn);
+    const double cost = double((tiles + sms - 1) / sms) * bn * kSingleCtaPenalty;
+    if (cost < best.cost) best = A8W8Plan{false, bn, cost};
+  }
+  if (M > kBM) {
+    const int pairs = sms / 2;
+    const int tiles_m2 = (M + 255) / 256;
+    for (int i = 0; i < 5; ++i) {
+      const int bn = kPairWidths[i];
+      const long long tiles = 1ll * tiles_m2 * ((N + bn - 1) / bn);
+      const double cost = double((tiles + pairs - 1) / pairs) * bn * kPairColumnCost[i];
+      if (cost < best.cost) best = A8W8Plan{true, bn, cost};  // ties keep the wider tile (listed first)
+    }
+  }
+  return best;
 }
 
 template <typename OutT>
@@ -700,19 +751,27 @@ int dispatch(const int8_t* a, int64_t lda, const int8_t* b, int64_t ldb, const A
   // Up to 8 tokens against a wide weight matrix: the weight stream is all that matters, and the per-lane streaming
   // kernel of the weight-only decode path moves it 6-10 % faster than tile copies do (it declines shapes it does
   // not cover; with fewer row groups than a few per SM, or more tokens, the tile kernel is the faster one).
-  if (p.M <= 8 && p.N >= 8192) {
+  if (p.M <= 8 && p.N >= 8192 && opt_test_stall_us() == 0) {
     const int r = gemv_a8w8_imma(a, lda, b, ldb, p.alpha_row, p.row_dtype, p.alpha_col, p.col_dtype, p.out,
                                  std::is_same<OutT, __half>::value ? FNN_F16 : FNN_BF16, p.ldo, p.M, p.N, p.K, p.acc_out,
                                  p.ldacc, st);
     if (r >= 0) return r;
   }
-  // Large problems: one 256 x 256 tile per CTA pair.  Otherwise the widest single-CTA tile that
-  // still gives every SM work.
-  const int sms = sm_count();
-  if (p.M > kBM && ((p.M + 255) / 256) * ((p.N + 255) / 256) >= sms / 2) return launch_pair<OutT, 6>(a, lda, b, ldb, p, st);
-  const int tiles_m = (p.M + kBM - 1) / kBM;
-  if (tiles_m * ((p.N + 255) / 256) >= sms) return launch_umma_rows<OutT, 256>(a, lda, b, ldb, p, st);
-  if (tiles_m * ((p.N + 127) / 128) >= sms) return launch_umma_rows<OutT, 128>(a, lda, b, ldb, p, st);
+  A8W8Plan plan = opt_test_stall_us() != 0 ? A8W8Plan{false, 64, 0.0} : plan_a8w8(p.M, p.N, sm_count());
+  if (const int forced = opt_a8w8_pair_tile()) {  // tuning hook: a given pair-tile width wherever the pair kernel can run
+    if (p.M > kBM) plan = A8W8Plan{true, forced, 0.0};
+  }
+  if (plan.pair) {
+    switch (plan.bn) {
+      case 256: return launch_pair<OutT, 256>(a, lda, b, ldb, p, st);
+      case 224: return launch_pair<OutT, 224>(a, lda, b, ldb, p, st);
+      case 192: return launch_pair<OutT, 192>(a, lda, b, ldb, p, st);
+      case 160: return launch_pair<OutT, 160>(a, lda, b, ldb, p, st);
+      default: return launch_pair<OutT, 128>(a, lda, b, ldb, p, st);
+    }
+  }
+  if (plan.bn == 256) return launch_umma_rows<OutT, 256>(a, lda, b, ldb, p, st);
+  if (plan.bn == 128) return launch_umma_rows<OutT, 128>(a, lda, b, ldb, p, st);
   return launch_umma_rows<OutT, 64>(a, lda, b, ldb, p, st);
 }
 

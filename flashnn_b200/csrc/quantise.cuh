@@ -60,17 +60,42 @@ __device__ __forceinline__ uint32_t min2_127(uint32_t t2, __nv_bfloat16) {
   return *reinterpret_cast<const uint32_t*>(&r);
 }
 
+// Packed fp32 arithmetic (two independent IEEE operations per instruction, half the issue slots).
+__device__ __forceinline__ uint64_t f32x2(float lo, float hi) {
+  uint64_t r;
+  asm("mov.b64 %0, {%1, %2};" : "=l"(r) : "f"(lo), "f"(hi));
+  return r;
+}
+__device__ __forceinline__ uint64_t mul_f32x2(uint64_t a, uint64_t b) {
+  uint64_t r;
+  asm("mul.rn.f32x2 %0, %1, %2;" : "=l"(r) : "l"(a), "l"(b));
+  return r;
+}
+__device__ __forceinline__ uint64_t add_f32x2(uint64_t a, uint64_t b) {
+  uint64_t r;
+  asm("add.rn.f32x2 %0, %1, %2;" : "=l"(r) : "l"(a), "l"(b));
+  return r;
+}
+__device__ __forceinline__ void split_f32x2(uint64_t v, float& lo, float& hi) {
+  asm("mov.b64 {%0, %1}, %2;" : "=f"(lo), "=f"(hi) : "l"(v));
+}
+
 // Two elements at once: returns the two quantised bytes in bits 0-7 and 8-15.  Both ends of the bracket are
 // rounded to T (one packed conversion each); rounding is monotonic, so where the two agree the exact quotient rounds
 // to the same T value.  Where they differ a bit is ORed into `amb` and the caller redoes the chunk with the exact
-// division (about one element in 5000).
+// division (about one element in 5000).  The two multiplications per end and the two magic additions are packed
+// fp32 instructions.
 template <typename T> __device__ __forceinline__ uint32_t quantise_pair(uint32_t w, const InvBracket& inv, uint32_t& amb) {
-  const float x0 = lo_of<T>(w), x1 = hi_of<T>(w);
-  const uint32_t t2 = pack2<T>(__fmul_rn(x0, inv.lo), __fmul_rn(x1, inv.lo));
-  amb |= t2 ^ pack2<T>(__fmul_rn(x0, inv.hi), __fmul_rn(x1, inv.hi));
+  const uint64_t x = f32x2(lo_of<T>(w), hi_of<T>(w));
+  float a0, a1, b0, b1;
+  split_f32x2(mul_f32x2(x, f32x2(inv.lo, inv.lo)), a0, a1);
+  split_f32x2(mul_f32x2(x, f32x2(inv.hi, inv.hi)), b0, b1);
+  const uint32_t t2 = pack2<T>(a0, a1);
+  amb |= t2 ^ pack2<T>(b0, b1);
   const uint32_t tc = min2_127(t2, T());  // |t| <= 128; only +128 needs the clamp (one packed instruction)
-  const uint32_t q0 = __float_as_uint(__fadd_rn(lo_of<T>(tc), 12582912.f)), q1 = __float_as_uint(__fadd_rn(hi_of<T>(tc), 12582912.f));
-  return __byte_perm(q0, q1, 0x0040);  // low bytes of q0, q1 in bytes 0 and 1
+  float q0, q1;
+  split_f32x2(add_f32x2(f32x2(lo_of<T>(tc), hi_of<T>(tc)), f32x2(12582912.f, 12582912.f)), q0, q1);
+  return __byte_perm(__float_as_uint(q0), __float_as_uint(q1), 0x0040);  // low bytes of q0, q1 in bytes 0 and 1
 }
 
 // Same result as quantise_one for s > 0, returned in the low byte (two's complement).

@@ -64,10 +64,15 @@ typedef enum fnn_dtype {
  * seconds.  The wait for the missing block then runs out: the kernel records its time-out code, drains what it has in
  * flight, frees what it holds and returns without a result, and the next fnn_device_status reports
  * FNN_ERR_DEVICE_TIMEOUT.  This is how the give-up path of the kernels is exercised without faulting the GPU.
+ *
+ * FNN_OPT_A8W8_PAIR_TILE (default 0 = chosen from the problem shape; a tuning hook).  128, 160, 192, 224 or 256 forces
+ * that output-tile width in fnn_gemm_a8w8 wherever the CTA-pair tensor-core kernel can run (more than 128 rows).  The
+ * shape-to-tile table in the library was measured with it; results do not depend on the tile.
  */
 typedef enum fnn_option {
   FNN_OPT_STATIC_WEIGHTS = 1,
-  FNN_OPT_TEST_STALL_US = 2
+  FNN_OPT_TEST_STALL_US = 2,
+  FNN_OPT_A8W8_PAIR_TILE = 3
 } fnn_option;
 
 /* Sets an option; FNN_ERR_UNSUPPORTED for an unknown one.  fnn_get_option returns the value, or -1 if unknown. */
