@@ -756,6 +756,55 @@ def run_reference(args):
     }), flush=True)
 
 
+def run_sweep(args):
+    """The reference's own benchmark sweeps on one GPU: GemmA8W8 over M x 20 (N, K) pairs
+    (benchmark/benchmark_gemm_a8w8.py:13-44, fp16 scales and output as there) and DynamicQuantize over M x 6 row
+    lengths (benchmark/benchmark_dynamic_quant.py:11).  Prints two markdown tables (TOPS; GB/s) and one JSON line."""
+    import flashnn_b200
+    from flashnn_b200 import _lib
+    from flashnn_b200 import workloads as W
+    device = torch.device("cuda", 0)
+    torch.cuda.set_device(device)
+    flush_buf = torch.empty(256 << 20, dtype=torch.uint8, device=device)
+    nk, ms_list = W.reference_sweep_shapes()
+    gemm = flashnn_b200.GemmA8W8(torch.float16)
+    g = torch.Generator(device=device).manual_seed(0)
+    rows = []
+    print("### GemmA8W8, TOPS (2 M N K / time), fp16 scales and output, CUDA events, L2 flushed, median of 5\n")
+    print("| N | K | " + " | ".join(f"M={m}" for m in ms_list) + " |")
+    print("|---|---|" + "---|" * len(ms_list))
+    for n, k in nk:
+        b = torch.randint(-128, 127, (n, k), dtype=torch.int8, device=device, generator=g)
+        col = torch.rand(1, n, device=device, generator=g).half()
+        cells = []
+        for m in ms_list:
+            a = torch.randint(-128, 127, (m, k), dtype=torch.int8, device=device, generator=g)
+            row = torch.rand(m, 1, device=device, generator=g).half()
+            ms = statistics.median(time_steps(lambda: gemm(a, b, row, col), 5, 2, flush_buf))
+            tops = W.a8w8_ops(m, n, k) / ms / 1e9
+            rows.append(dict(op="a8w8", m=m, n=n, k=k, ms=round(ms, 5), tops=round(tops, 1),
+                             gbs=round(W.a8w8_bytes(m, n, k) / ms / 1e6, 1)))
+            cells.append(f"{tops:.0f}" if m > 40 else f"{tops:.1f} ({W.a8w8_bytes(m, n, k) / ms / 1e6:.0f} GB/s)")
+        print(f"| {n} | {k} | " + " | ".join(cells) + " |", flush=True)
+        del b
+    dq = flashnn_b200.DynamicQuantize()
+    print("\n### DynamicQuantize, GB/s (3 M K + 2 M bytes / time), fp16 input\n")
+    print("| K | " + " | ".join(f"M={m}" for m in ms_list) + " |")
+    print("|---|" + "---|" * len(ms_list))
+    for k in W.DYNAMIC_QUANT_SWEEP_K:
+        cells = []
+        for m in ms_list:
+            x = torch.rand(m, k, device=device, generator=g).half()
+            ms = statistics.median(time_steps(lambda: dq(x), 5, 2, flush_buf))
+            gbs = W.dynamic_quant_bytes(m, k) / ms / 1e6
+            rows.append(dict(op="dq", m=m, k=k, ms=round(ms, 5), gbs=round(gbs, 1)))
+            cells.append(f"{gbs:.0f} ({ms * 1e3:.1f} us)")
+        print(f"| {k} | " + " | ".join(cells) + " |", flush=True)
+    assert _lib.device_status() == 0
+    print()
+    print(json.dumps({"case": "sweep", "points": rows}), flush=True)
+
+
 def run_case(args):
     """One kernel of the path on one GPU, launched `steps` times after `warmup` (used for profiler
     captures and quick A/B timing).  Prints one small JSON line."""
@@ -858,6 +907,8 @@ def main():
     args = ap.parse_args()
     if args.case == "ref_triton":
         run_ref_triton(args)
+    elif args.case == "sweep":
+        run_sweep(args)
     elif args.case:
         run_case(args)
     elif args.impl == "reference":

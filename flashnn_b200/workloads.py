@@ -95,6 +95,22 @@ def ffn_layer(m, rank=0, world=1, hidden=8192, inter=28672, weights=True):
         out_ty=torch.bfloat16)
 
 
+def reference_sweep_shapes():
+    """The (N, K) pairs and the M values of the reference's own A8W8 benchmark sweep
+    (benchmark/benchmark_gemm_a8w8.py:13-44): four projections (FFN layer 1, FFN layer 2, attention output, QKV) of
+    five tensor-parallel model configurations.  Returns (list of (N, K), list of M)."""
+    nk = []
+    for hidden, inter, tp, heads, kv_heads in [(13312, 71168, 8, 104, 8), (13312, 71168, 4, 104, 4), (8192, 29568, 4, 64, 8),
+                                               (8192, 29568, 2, 64, 8), (3584, 18944, 1, 28, 4)]:
+        gqa = heads // kv_heads
+        nk += [(hidden, inter // tp), ((inter // tp) * 2, hidden), (hidden, hidden // tp),
+               ((hidden // tp) + ((hidden // tp) // gqa) * 2, hidden)]
+    return nk, [1, 10, 20, 30, 40, 764, 1024, 2048, 4096, 8192]
+
+
+DYNAMIC_QUANT_SWEEP_K = [1664, 3328, 8896, 13312, 17792, 35584]  # benchmark/benchmark_dynamic_quant.py:11
+
+
 # Algorithmic work of each op (what the roofline figures are computed from).
 def a8w8_ops(m, n, k) -> int:
     return 2 * m * n * k

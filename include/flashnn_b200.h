@@ -176,6 +176,34 @@ int fnn_fused_moe_a8w8(const int8_t* a, int64_t lda, const int8_t* b, int64_t E,
 size_t fnn_fused_moe_a8w8_workspace_bytes(int64_t EM, int64_t K);
 
 /*
+ * Fused mixture-of-experts weight-only GEMM over expert-sorted token slots, packed-int4 expert weights.
+ * Replaces `fused_moe_a16w4_forward(A, B, C, scale_b, zero_points, topk_weights, topk_ids, sorted_token_ids, expert_ids,
+ * num_tokens_post_padded, mul_routed_weight, top_k, BM)` (flashnn/triton_kernels/fused_moe_a16w4.py:326-466; kernels at
+ * :50-183 per channel and :186-323 per K group).  For every slot s < *num_tokens_post_padded whose flat index
+ * f = sorted_token_ids[s] is below num_valid_tokens, with e = expert_ids[s / block_m]:
+ *     out[f, n] = cast( (sum_k a[f / top_k, k] * (W[e, n, k] - zp) * scale) * (mul_routed_weight ? topk_weights[f] : 1) )
+ * with scale, zp taken per (e, n) (group_size == 0) or per (e, n, k / group_size).  Products and sums are fp32 and the
+ * dequantised weight is never rounded to 16 bits (the reference's per-group kernel rounds (W - zp) * scale to 16 bits
+ * per weight; as for fnn_gemm_weight_only the bar here is the fp32 dequant-matmul).  Rows of `out` that no slot names
+ * are left untouched.  No workspace: the token rows are gathered inside the kernel.
+ *
+ *   a                 [M, K] f16 or bf16 (a_dtype), lda a multiple of 8; K a multiple of 16; 16-byte aligned
+ *   b                 [E, N/2, K] bytes, contiguous: byte (e, j, k) holds channel 2j in its low nibble and channel
+ *                     2j+1 in its high nibble, two's complement (packing along N, fused_moe_a16w4.py:137,151)
+ *   scale             [E, N] (group_size == 0) or [E, N, K/group_size], contiguous, scale_dtype; zero_points NULL or alike
+ *   group_size        0, or a multiple of 64 that divides K
+ *   topk_weights      [M * top_k] topk_dtype;  sorted_token_ids [EM] int32;  expert_ids [EM / block_m] int32;
+ *                     num_tokens_post_padded [1] int32 (device memory) -- as for fnn_fused_moe_a8w8
+ *   out               [M * top_k, N] in a_dtype, ldo
+ *   block_m           at most 64, or a multiple of 64
+ */
+int fnn_fused_moe_a16w4(const void* a, int a_dtype, int64_t lda, const void* b, int64_t E, int64_t N, int64_t K,
+                        const void* scale, const void* zero_points, int scale_dtype, int64_t group_size,
+                        const void* topk_weights, int topk_dtype, const int32_t* sorted_token_ids, int64_t EM,
+                        const int32_t* expert_ids, const int32_t* num_tokens_post_padded, int64_t num_valid_tokens,
+                        int top_k, int block_m, int mul_routed_weight, void* out, int out_dtype, int64_t ldo, void* stream);
+
+/*
  * Weight-only GEMM / GEMV:  out = act . dequant(W)^T (+ bias), W int8 or packed int4.
  * Replaces `triton_gemm_a16w8_forward` (flashnn/triton_kernels/gemm_a16w8.py:275-338)
  * and `triton_gemm_a16w4_forward` (flashnn/triton_kernels/gemm_a16w4.py:336-406).
