@@ -551,18 +551,36 @@ def sharded_decode_extras(rank, world, device, flush_buf, peaks, barrier, layer)
     del qws, scs
     out["a16w4_gemv_timing"] = (f"{copies} rotating weight copies per rank (> L2 together), calls captured in one CUDA graph "
                                 "and replayed, best of 5, max over ranks")
-    # decode-shaped A8W8 FFN layer on this rank's shard: DynamicQuant + gate/up, DynamicQuant + down
+    # decode-shaped A8W8 FFN layer on this rank's shard: DynamicQuant + gate/up, DynamicQuant + down.  A decode loop
+    # replays a CUDA graph, so the steps are captured (over rotating copies of the weights that together exceed L2)
+    # and replayed; the eager figure (four launches per step issued from Python) is host-bound and reported beside it.
+    per_rank_bytes = layer.w_gu.numel() + layer.w_dn.numel()
+    ncopy = max(2, min(8, -(-(300 << 20) // per_rank_bytes)))
+    weights = [(layer.w_gu, layer.w_dn)] + [(layer.w_gu.clone(), layer.w_dn.clone()) for _ in range(ncopy - 1)]
     for m_ in (1, 64):
         shard = FfnShard(rank, world, device, tokens=m_, share=layer)
+
+        def step_with(wg, wd):
+            qx, sx = shard.dq(shard.x)
+            shard.gemm(qx, wg, sx, shard.col_gu)
+            qh, sh = shard.dq(shard.h)
+            shard.gemm(qh, wd, sh, shard.col_dn)
+
+        calls = [(lambda wg=wg, wd=wd: step_with(wg, wd)) for wg, wd in weights]
         barrier()
-        ts = time_steps(shard.step, 10, 3, flush_buf)
-        ms = max_over_ranks(statistics.median(ts))
+        ms = max_over_ranks(time_rotating_graph(calls, rounds=max(2, 16 // ncopy)))
+        barrier()
+        eager = max_over_ranks(statistics.median(time_steps(shard.step, 10, 3, flush_buf)))
         byts = world * (W.a8w8_bytes(m_, shard.n_gu, HIDDEN) + W.a8w8_bytes(m_, shard.n_dn, INTER)
                         + W.dynamic_quant_bytes(m_, HIDDEN) + W.dynamic_quant_bytes(m_, INTER))
         out[f"a8w8_ffn_m{m_}"] = dict(ms=round(ms, 4), gbs_whole_job=round(byts / ms / 1e6, 1),
                                       frac_of_measured_hbm=round(byts / ms / 1e6 / world / peaks["hbm"], 4),
-                                      note="four launches per step from Python with L2 flushed before each step, max over ranks")
+                                      eager_python_calls_ms=round(eager, 4),
+                                      note=f"steps of four launches over {ncopy} rotating weight copies captured in one CUDA graph "
+                                           "and replayed, best of 5, max over ranks; eager = the same step issued from Python "
+                                           "with L2 flushed before it")
         del shard
+    del weights
     return out
 
 
@@ -850,9 +868,11 @@ def run_case(args):
     elif name == "wog":
         # A16W4 prefill with group-wise scales (group 128): the decode config's weight at prefill batch sizes
         m, n, k = args.m or 2048, args.n or 28672, args.k or 8192
-        w = W.a16w4_decode(1, n, k)
+        w = W.a16w4_decode(1, n, k, group=args.group or 128)
         x = W.rand_normal((m, k), 0, torch.bfloat16).to(device)
         qw, sc = w["qw"].to(device), w["scale"].to(device)
+        if args.group == -1:  # per-channel scales on the same weights
+            sc = sc[0].contiguous()
         op = flashnn_b200.GemmWeightOnly(torch.bfloat16)
         fn = lambda: op(x, qw, sc)
         work, unit = 2.0 * m * n * k / 1e12, "TFLOP/s"
@@ -875,6 +895,20 @@ def run_case(args):
             work, unit = (e * n * k + m * top_k * n * 2 + m * k) / 1e9, "GB/s"
         else:
             work, unit = 2.0 * m * top_k * n * k / 1e12, "TOPS"
+    elif name == "moe4":
+        # the same expert layer with packed-int4 weights and per-group (128) bf16 scales
+        from flashnn_b200.workloads import make_moe_w4_case
+        m, n, k = args.m or 64, args.n or 28672, args.k or 4096
+        e, top_k, bm = 8, 2, (16 if m <= 64 else 64)
+        c = {kk: (None if v is None else v.to(device)) for kk, v in
+             make_moe_w4_case(m, e, n, k, top_k, bm, seed=0, dtype=torch.bfloat16, group=128).items() if kk != "w4"}
+        out = torch.empty(m, top_k, n, dtype=torch.bfloat16, device=device)
+        fn = lambda: flashnn_b200.fused_moe_a16w4_forward(c["a"], c["b"], out, c["scale"], None, c["topk_w"], c["topk_ids"],
+                                                          c["sorted_ids"], c["expert_ids"], c["npp"], True, top_k, bm)
+        if m <= 256:
+            work, unit = (e * n * k // 2 + e * n * (k // 128) * 2 + m * top_k * n * 2 + m * k * 2) / 1e9, "GB/s"
+        else:
+            work, unit = 2.0 * m * top_k * n * k / 1e12, "TFLOP/s"
     elif name in ("rmsdq", "lndq"):
         m, k = args.m or 4096, args.k or 8192
         x = W.rand_normal((m, k), 0, torch.bfloat16, outliers=True).to(device)
@@ -898,9 +932,10 @@ def main():
     ap.add_argument("--impl", choices=["native", "reference"], default="native")
     ap.add_argument("--cpu-rows", type=int, default=TOKENS, help="tokens in the CPU-baseline sample (default: the whole workload)")
     ap.add_argument("--no-triton-reference", action="store_true", help="skip timing the reference's Triton kernels (extra.reference_triton)")
-    ap.add_argument("--case", choices=["a8w8", "gemv", "gemv8", "dq", "wo", "wog", "rmsdq", "lndq", "moe", "ref_triton", "sweep"],
+    ap.add_argument("--case", choices=["a8w8", "gemv", "gemv8", "dq", "wo", "wog", "rmsdq", "lndq", "moe", "moe4", "ref_triton", "sweep"],
                     help="run one kernel only (profiling / A-B timing), the reference's Triton kernels, or the reference's shape sweep")
     ap.add_argument("--tile", type=int, default=0, help="with --case a8w8: force this CTA-pair tile width (tuning)")
+    ap.add_argument("--group", type=int, default=0, help="with --case wog: scale group size (-1: per channel)")
     ap.add_argument("--m", type=int)
     ap.add_argument("--n", type=int)
     ap.add_argument("--k", type=int)

@@ -5,7 +5,7 @@ with per-channel or per-group scales), optionally scaled by the routing weight, 
 import torch
 
 from . import _lib
-from .quant_gemm import _DT, _require_cuda, _stream, _workspace
+from .quant_gemm import _DT, _on_device, _require_cuda, _stream, _workspace
 
 
 def _i32(t: torch.Tensor) -> torch.Tensor:
@@ -37,7 +37,7 @@ def fused_moe_a8w8_forward(A, B, C, alpha_row_ptr, alpha_col_ptr, topk_weights, 
         tw = tw.float()
     sid, eid, npp = _i32(sorted_token_ids), _i32(expert_ids), _i32(num_tokens_post_padded)
     em = sid.shape[0]
-    with torch.cuda.device(A.device):
+    with _on_device(A):
         need = _lib.lib().fnn_fused_moe_a8w8_workspace_bytes(em, K)
         ws = _workspace(A.device, need)
         _lib.check(_lib.lib().fnn_fused_moe_a8w8(
@@ -83,7 +83,7 @@ def fused_moe_a16w4_forward(A, B, C, scale_b, zero_points, topk_weights, topk_id
     if tw.dtype not in _DT:
         tw = tw.float()
     sid, eid, npp = _i32(sorted_token_ids), _i32(expert_ids), _i32(num_tokens_post_padded)
-    with torch.cuda.device(A.device):
+    with _on_device(A):
         _lib.check(_lib.lib().fnn_fused_moe_a16w4(
             a2.data_ptr(), _DT[A.dtype], a2.stride(0), b.data_ptr(), E, N, K, scale.data_ptr(),
             zp.data_ptr() if zp is not None else None, _DT[scale.dtype], group, tw.data_ptr(), _DT[tw.dtype],

@@ -7,7 +7,7 @@ import torch
 
 from . import _lib
 from .kernel_backend import BackendKernel
-from .quant_gemm import _DT, _require_cuda, _stream
+from .quant_gemm import _DT, _on_device, _require_cuda, _stream
 
 
 def _rows(x):
@@ -19,10 +19,27 @@ def _rows(x):
     return x2, k
 
 
+_affine_cache = {}
+
+
 def _affine(x, *params):
-    """Norm parameters on x's device in a dtype the kernel reads: x's own, or fp32."""
+    """Norm parameters on x's device in a dtype the kernel reads: x's own, or fp32.  Parameters that already are
+    (the usual case) are passed as they are; a converted copy is made once per parameter version and kept."""
     dt = x.dtype if params[0].dtype in (torch.float16, torch.bfloat16) else torch.float32
-    return [p.detach().to(device=x.device, dtype=dt).contiguous() for p in params]
+    out = []
+    for p in params:
+        if p.device == x.device and p.dtype == dt and p.is_contiguous():
+            out.append(p.detach())
+            continue
+        key = (id(p), p._version, p.data_ptr(), x.device, dt)
+        t = _affine_cache.get(key)
+        if t is None:
+            for stale in [k for k in _affine_cache if k[0] == id(p)]:
+                del _affine_cache[stale]
+            t = p.detach().to(device=x.device, dtype=dt).contiguous()
+            _affine_cache[key] = t
+        out.append(t)
+    return out
 
 
 class RMSNormDquant(BackendKernel):
@@ -41,7 +58,7 @@ class RMSNormDquant(BackendKernel):
         (w,) = _affine(x, self.weight)
         q = torch.empty(x2.shape, dtype=torch.int8, device=x.device)
         scale = torch.empty(x2.shape[0], dtype=x.dtype, device=x.device)
-        with torch.cuda.device(x.device):
+        with _on_device(x):
             _lib.check(_lib.lib().fnn_rms_norm_dquant(
                 x2.data_ptr(), _DT[x.dtype], x2.shape[0], k, k, w.data_ptr(), _DT[w.dtype], float(self.eps),
                 q.data_ptr(), k, scale.data_ptr(), _stream(x)))
@@ -71,7 +88,7 @@ class LayernormDquant(BackendKernel):
         w, b = _affine(x, self.weight, self.bias)
         q = torch.empty(x2.shape, dtype=torch.int8, device=x.device)
         scale = torch.empty(x2.shape[0], dtype=x.dtype, device=x.device)
-        with torch.cuda.device(x.device):
+        with _on_device(x):
             _lib.check(_lib.lib().fnn_layer_norm_dquant(
                 x2.data_ptr(), _DT[x.dtype], x2.shape[0], k, k, w.data_ptr(), b.data_ptr(), _DT[w.dtype],
                 float(self.eps), q.data_ptr(), k, scale.data_ptr(), _stream(x)))
