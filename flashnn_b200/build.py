@@ -16,7 +16,7 @@ HERE = os.path.dirname(os.path.abspath(__file__))
 CSRC = os.path.join(HERE, "csrc")
 INCLUDE = os.path.join(os.path.dirname(HERE), "include")
 LIB_PATH = os.path.join(HERE, "libflashnn_b200.so")
-SOURCES = ["capi.cu", "dynamic_quant.cu", "gemm_a8w8.cu", "gemv_weight_only.cu", "gemv_w4_imma.cu", "gemm_weight_only.cu", "norm_dquant.cu", "fused_moe_a16w4.cu"]
+SOURCES = ["capi.cu", "dynamic_quant.cu", "gemm_a8w8.cu", "gemv_weight_only.cu", "gemv_w4_imma.cu", "gemm_weight_only.cu", "norm_dquant.cu", "fused_moe_a16w4.cu", "gemv_w4_tok.cu"]
 ARCH_FLAGS = ["-gencode", "arch=compute_100a,code=sm_100a"]
 
 

@@ -738,6 +738,11 @@ int launch_wo(WoParams p, void* workspace, size_t workspace_bytes, cudaStream_t 
     // one to five tokens: integer tensor-pipe kernel (declines shapes it does not cover)
     const int r = gemv_w4_imma(p, BITS, std::is_same<T, __half>::value ? FNN_F16 : FNN_BF16, st);
     if (r >= 0) return r;
+    // six to sixteen tokens of packed int4: the kernel that keeps the activations on the SM
+    if (BITS == 4 && p.M >= 6) {
+      const int r2 = gemv_w4_tok(p, std::is_same<T, __half>::value ? FNN_F16 : FNN_BF16, st);
+      if (r2 >= 0) return r2;
+    }
   }
   const int spu = gemv_spu(p, BITS, std::is_same<T, __half>::value ? FNN_F16 : FNN_BF16);
   if (spu < 0) {

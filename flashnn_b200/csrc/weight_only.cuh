@@ -30,6 +30,10 @@ __device__ __forceinline__ float nan_to_inf(float v) { return v != v ? __int_as_
 // Returns an fnn_status, or -1 when the shape or alignment is outside what that kernel handles.
 int gemv_w4_imma(const WoParams& p, int bits, int act_dtype, cudaStream_t st);
 
+// Packed-int4 decode for 6 to 16 tokens with the activations resident on the SM (gemv_w4_tok.cu).  Returns an
+// fnn_status, or -1 when the shape or alignment is outside what that kernel handles.
+int gemv_w4_tok(const WoParams& p, int act_dtype, cudaStream_t st);
+
 // A8W8 GEMM for at most 16 tokens on the same kernel (int8 activations are the MMA's column operand as they are,
 // exact int32 sums, the A8W8 scaling rule in the write-out).  b must be [N, K] with pitch K.  Returns an
 // fnn_status, or -1 when the shape or alignment is outside what the kernel handles.

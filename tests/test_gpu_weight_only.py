@@ -291,6 +291,40 @@ def test_int4_six_to_sixteen_tokens(dt, m, n, k, group, use_bias):
     assert torch.equal(out[1].float(), want.to(dt).float())
 
 
+# The same token counts at K = 4096 and 8192 run the kernel that keeps the activations on the SM (tokens as the MMA's
+# row operand, fragments in registers and shared memory): every group size it takes, zero-points, bias, both dtypes.
+@pytest.mark.parametrize("dt", [torch.bfloat16, torch.float16])
+@pytest.mark.parametrize("m", [6, 8, 11, 16])
+@pytest.mark.parametrize("n,k,group,use_bias,use_zp", [
+    (272, 8192, 128, True, True), (64, 8192, 64, False, False), (1024, 8192, 256, True, False), (48, 4096, 0, True, True),
+    (160, 4096, 64, False, True), (3584, 8192, 128, False, False), (32, 4096, 256, True, False), (96, 8192, 0, False, True)])
+def test_int4_resident_activations(dt, m, n, k, group, use_bias, use_zp):
+    act, qw, scale, bias, zp = make(4, m, n, k, dt, group, use_bias, use_zp, seed=m + n + k + group)
+    g = torch.Generator().manual_seed(k + 3)
+    act = torch.where(torch.rand(m, k, generator=g) < 0.002, act * 30, act)  # outliers
+    act[1] = 0  # a row of zeros gives the bias (or 0)
+    act[2] = act[2] * (1e-3 if dt == torch.float16 else 1e-30)  # a tiny row
+    out = run(act, qw, scale, bias, zp)
+    ref = O.gemm_weight_only_fp32(act, qw, scale, bias, zp)
+    assert_rows_within_bound(out, ref)
+    exact = ref.to(dt)
+    assert int((out != exact).sum()) <= max(3, 0.02 * out.numel())
+    want = torch.zeros(n) if bias is None else bias.float()
+    assert torch.equal(out[1].float(), want.to(dt).float())
+
+
+def test_int4_sixteen_tokens_non_finite_row_resident():
+    act, qw, scale, bias, zp = make(4, 16, 256, 8192, torch.bfloat16, 128, False, False, seed=5)
+    clean = run(act, qw, scale)
+    for bad in (float("nan"), float("inf")):
+        act2 = act.clone()
+        act2[7, 5000] = bad
+        out = run(act2, qw, scale)
+        assert bool(torch.isnan(out[7].float()).all())
+        keep = [i for i in range(16) if i != 7]
+        assert torch.equal(out[keep].view(torch.int16), clean[keep].view(torch.int16))
+
+
 def test_int4_sixteen_tokens_non_finite_row():
     act, qw, scale, bias, zp = make(4, 16, 256, 2048, torch.bfloat16, 128, False, False, seed=5)
     clean = run(act, qw, scale)
