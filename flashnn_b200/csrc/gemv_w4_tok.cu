@@ -70,6 +70,12 @@ template <> struct TkFrag<__nv_bfloat16> {
                  : "+f"(d[0]), "+f"(d[1]), "+f"(d[2]), "+f"(d[3])
                  : "r"(a.x), "r"(a.y), "r"(a.z), "r"(a.w), "r"(b0), "r"(b1));
   }
+  // d = a * b: the first MMA of a fold starts a fresh accumulator without clearing registers
+  static __device__ __forceinline__ void mma0(float (&d)[4], const uint4& a, uint32_t b0, uint32_t b1) {
+    asm volatile("mma.sync.aligned.m16n8k16.row.col.f32.bf16.bf16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%10,%10,%10,%10};"
+                 : "=f"(d[0]), "=f"(d[1]), "=f"(d[2]), "=f"(d[3])
+                 : "r"(a.x), "r"(a.y), "r"(a.z), "r"(a.w), "r"(b0), "r"(b1), "f"(0.f));
+  }
 };
 template <> struct TkFrag<__half> {
   static constexpr float kInvAlpha = 0.0625f, kOffset = 72.f;  // byte ((n ^ 8) << 4) under 0x64: 1024 + 16 (n ^ 8)
@@ -83,6 +89,11 @@ template <> struct TkFrag<__half> {
     asm volatile("mma.sync.aligned.m16n8k16.row.col.f32.f16.f16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};"
                  : "+f"(d[0]), "+f"(d[1]), "+f"(d[2]), "+f"(d[3])
                  : "r"(a.x), "r"(a.y), "r"(a.z), "r"(a.w), "r"(b0), "r"(b1));
+  }
+  static __device__ __forceinline__ void mma0(float (&d)[4], const uint4& a, uint32_t b0, uint32_t b1) {
+    asm volatile("mma.sync.aligned.m16n8k16.row.col.f32.f16.f16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%10,%10,%10,%10};"
+                 : "=f"(d[0]), "=f"(d[1]), "=f"(d[2]), "=f"(d[3])
+                 : "r"(a.x), "r"(a.y), "r"(a.z), "r"(a.w), "r"(b0), "r"(b1), "f"(0.f));
   }
 };
 
@@ -141,6 +152,10 @@ __global__ void __launch_bounds__(kTkThreads, 1) gemv_w4_tok_kernel(const WoPara
     if (w) cp_async16(fifo + v * 512, w);
     cp_async_commit();
   }
+  // the chunk that goes into the slot consumed next: kTkSlots chunks ahead, as a running (row group, chunk, pointer)
+  int fill_rg = rg + (kTkSlots / CHUNKS) * int(gridDim.x), fill_c = kTkSlots % CHUNKS;
+  const uint8_t* fill_ptr = wlane + int64_t(fill_rg) * rg_bytes + fill_c * 64;
+  const int64_t rg_jump = int64_t(gridDim.x) * rg_bytes - (CHUNKS - 1) * 64;  // from the last chunk of a row group to the next one's first
 
   // ---- activations: this warp's slice of the 16 token rows, as A fragments (rows g and g + 8 of this lane) ----
   const T* act = reinterpret_cast<const T*>(p.act);
@@ -203,7 +218,7 @@ __global__ void __launch_bounds__(kTkThreads, 1) gemv_w4_tok_kernel(const WoPara
     float tot[8];
 #pragma unroll
     for (int i = 0; i < 8; ++i) tot[i] = 0.f;
-    float accl[4] = {0.f, 0.f, 0.f, 0.f}, acch[4] = {0.f, 0.f, 0.f, 0.f};
+    float accl[4], acch[4];
 #pragma unroll
     for (int c = 0; c < CHUNKS; ++c) {
       // chunk c has landed.  The scales of this row group were committed one row group (CHUNKS commits) ago; where
@@ -219,14 +234,20 @@ __global__ void __launch_bounds__(kTkThreads, 1) gemv_w4_tok_kernel(const WoPara
         uint4 a;
         if (c < REG_CHUNKS) a = areg[c * 4 + s];
         else a = lds128(a_lane + ((c - REG_CHUNKS) * 4 + s) * 512);
-        TkFrag<T>::mma(accl, a, bl[0], bl[1]);
-        TkFrag<T>::mma(acch, a, bh[0], bh[1]);
+        if (c % CPF == 0 && s == 0) {
+          TkFrag<T>::mma0(accl, a, bl[0], bl[1]);
+          TkFrag<T>::mma0(acch, a, bh[0], bh[1]);
+        } else {
+          TkFrag<T>::mma(accl, a, bl[0], bl[1]);
+          TkFrag<T>::mma(acch, a, bh[0], bh[1]);
+        }
       }
       {  // refill this slot with the chunk kTkSlots ahead
-        const uint8_t* w = chunk_ptr(rg, c + kTkSlots);
-        if (w) cp_async16(fifo + slot * 512, w);
+        if (fill_rg < num_rg) cp_async16(fifo + slot * 512, fill_ptr);
         cp_async_commit();
         slot = slot + 1 == kTkSlots ? 0 : slot + 1;
+        if (++fill_c == CHUNKS) { fill_c = 0; fill_rg += int(gridDim.x); fill_ptr += rg_jump; }
+        else fill_ptr += 64;
       }
       if ((c + 1) % CPF == 0) {
         // end of a fold: total += s * (acc / alpha - (offset + zp) * sum_k x), channels 4t .. 4t + 3
@@ -236,11 +257,13 @@ __global__ void __launch_bounds__(kTkThreads, 1) gemv_w4_tok_kernel(const WoPara
         float zo[4] = {kZ0, kZ0, kZ0, kZ0};
         const uint32_t at = ring + sslot * 256 + ((fold / FPG) * 4 + t) * 8;
         if (!PERCH) {
-          const uint32_t s01 = lds32(at), s23 = lds32(at + 4);
+          uint32_t s01, s23;
+          asm volatile("ld.shared.v2.u32 {%0, %1}, [%2];" : "=r"(s01), "=r"(s23) : "r"(at));
           sc[0] *= lo_half<T>(s01); sc[1] *= hi_half<T>(s01); sc[2] *= lo_half<T>(s23); sc[3] *= hi_half<T>(s23);
         }
         if (has_zp) {
-          const uint32_t z01 = lds32(at + 128), z23 = lds32(at + 132);
+          uint32_t z01, z23;
+          asm volatile("ld.shared.v2.u32 {%0, %1}, [%2];" : "=r"(z01), "=r"(z23) : "r"(at + 128));
           zo[0] += lo_half<T>(z01) / kInvAlpha; zo[1] += hi_half<T>(z01) / kInvAlpha;
           zo[2] += lo_half<T>(z23) / kInvAlpha; zo[3] += hi_half<T>(z23) / kInvAlpha;
         }
@@ -254,8 +277,6 @@ __global__ void __launch_bounds__(kTkThreads, 1) gemv_w4_tok_kernel(const WoPara
         tot[5] = fmaf(sc[1], fmaf(-zo[1], x1, acch[2]), tot[5]);
         tot[6] = fmaf(sc[2], fmaf(-zo[2], x1, accl[3]), tot[6]);
         tot[7] = fmaf(sc[3], fmaf(-zo[3], x1, acch[3]), tot[7]);
-#pragma unroll
-        for (int i = 0; i < 4; ++i) accl[i] = acch[i] = 0.f;
       }
     }
     sslot ^= 1;
