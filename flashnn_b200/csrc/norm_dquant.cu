@@ -65,14 +65,21 @@ struct NdParams {
   float eps;
 };
 
-// fp32 quotient n / s rounded half-to-even and saturated, in the low byte.  Both ends of the bracketed reciprocal are
-// multiplied in and rounded to an integer by the magic addition; rounding is monotonic, so where the two agree the
-// exact quotient rounds to the same integer.  Where they differ (the quotient is within a few ulp of a half-integer,
-// or is not finite) a bit is ORed into `amb` and the caller redoes the chunk with quantise_f32_exact.
-__device__ __forceinline__ uint32_t quantise_f32(float n, const InvBracket& inv, uint32_t& amb) {
-  const uint32_t m = __float_as_uint(__fadd_rn(fminf(__fmul_rn(n, inv.lo), 127.f), kRintMagic));
-  amb |= m ^ __float_as_uint(__fadd_rn(__fmul_rn(n, inv.hi), kRintMagic));
-  return m;
+// fp32 quotients n / s of two elements, rounded half-to-even and saturated, in the low bytes of the two results.
+// Both ends of the bracketed reciprocal are multiplied in and rounded to an integer by the magic addition (packed fp32
+// instructions: two elements per issue slot); rounding is monotonic, so where the two agree the exact quotient rounds
+// to the same integer.  Where they differ (the quotient is within a few ulp of a half-integer, or is not finite) a
+// bit is ORed into `amb` and the caller redoes the chunk with quantise_f32_exact.
+__device__ __forceinline__ void quantise_f32_pair(float n0, float n1, const InvBracket& inv, uint32_t& amb, uint32_t& q0, uint32_t& q1) {
+  const uint64_t n2 = f32x2(n0, n1);
+  float a0, a1, b0, b1;
+  split_f32x2(mul_f32x2(n2, f32x2(inv.lo, inv.lo)), a0, a1);
+  split_f32x2(add_f32x2(mul_f32x2(n2, f32x2(inv.hi, inv.hi)), f32x2(kRintMagic, kRintMagic)), b0, b1);
+  float m0, m1;
+  split_f32x2(add_f32x2(f32x2(fminf(a0, 127.f), fminf(a1, 127.f)), f32x2(kRintMagic, kRintMagic)), m0, m1);
+  q0 = __float_as_uint(m0);
+  q1 = __float_as_uint(m1);
+  amb |= (q0 ^ __float_as_uint(b0)) | (q1 ^ __float_as_uint(b1));
 }
 __device__ __forceinline__ uint32_t quantise_f32_exact(float n, float s) {
   return __float_as_uint(__fadd_rn(fminf(__fdiv_rn(n, s), 127.f), kRintMagic));
@@ -184,9 +191,10 @@ norm_dquant_kernel(const NdParams p) {
         float w[8];
         load_param8<W>(p.weight, i, w);
 #pragma unroll
-        for (int j = 0; j < 8; ++j) {
-          v[c][j] = __fmul_rn(__fmul_rn(v[c][j], rstd), w[j]);
-          amax = max_keep_nan(amax, v[c][j]);
+        for (int j = 0; j < 8; j += 2) {
+          // (x * rstd) * w, two elements per instruction
+          split_f32x2(mul_f32x2(mul_f32x2(f32x2(v[c][j], v[c][j + 1]), f32x2(rstd, rstd)), f32x2(w[j], w[j + 1])), v[c][j], v[c][j + 1]);
+          amax = max_keep_nan(max_keep_nan(amax, v[c][j]), v[c][j + 1]);
         }
       }
     }
@@ -207,8 +215,9 @@ norm_dquant_kernel(const NdParams p) {
           uint32_t amb = amb0;
 #pragma unroll
           for (int h = 0; h < 2; ++h) {
-            const uint32_t q0 = quantise_f32(v[c][4 * h], inv2, amb), q1 = quantise_f32(v[c][4 * h + 1], inv2, amb);
-            const uint32_t q2 = quantise_f32(v[c][4 * h + 2], inv2, amb), q3 = quantise_f32(v[c][4 * h + 3], inv2, amb);
+            uint32_t q0, q1, q2, q3;
+            quantise_f32_pair(v[c][4 * h], v[c][4 * h + 1], inv2, amb, q0, q1);
+            quantise_f32_pair(v[c][4 * h + 2], v[c][4 * h + 3], inv2, amb, q2, q3);
             o[h] = __byte_perm(__byte_perm(q0, q1, 0x0040), __byte_perm(q2, q3, 0x0040), 0x5410);
           }
           if (amb != 0) {

@@ -120,11 +120,12 @@ __device__ __forceinline__ uint32_t absmax2(uint32_t m, uint32_t w, __nv_bfloat1
   return *reinterpret_cast<const uint32_t*>(&r);
 }
 
-// Maximum of non-negative fp32 values that keeps a NaN: for sign-cleared values the IEEE bit patterns order like
-// unsigned integers, with every NaN pattern above infinity, so an unsigned max of the bits returns a NaN whenever
-// one of the operands is a NaN (fmaxf would drop it).
+// Maximum that keeps a NaN (fmaxf would drop it): one instruction, max.NaN.f32.  `max_keep_nan(a, b)` takes |b|,
+// so a running maximum that starts at 0 stays non-negative.
 __device__ __forceinline__ float max_keep_nan(float a, float b) {
-  return __uint_as_float(max(__float_as_uint(a) & 0x7fffffffu, __float_as_uint(b) & 0x7fffffffu));
+  float r;
+  asm("max.NaN.f32 %0, %1, %2;" : "=f"(r) : "f"(a), "f"(fabsf(b)));
+  return r;
 }
 // max_keep_nan over the whole block; `red` holds 32 floats.  Every thread gets the result.
 __device__ __forceinline__ float block_absmax_keep_nan(float v, float* red) {
