@@ -26,6 +26,7 @@ SIGNATURES = {
                                  _c.c_void_p, _c.c_int, _c.c_int64, _c.c_int64, _c.c_int64, _c.c_int64,
                                  _c.c_void_p, _c.c_int64, _c.c_void_p, _c.c_size_t, _c.c_void_p]),
     "fnn_gemm_a8w8_workspace_bytes": (_c.c_size_t, [_c.c_int64, _c.c_int64, _c.c_int64]),
+    "fnn_gemm_a8w8_plan": (_c.c_int, [_c.c_int64, _c.c_int64, _c.c_int64, _c.POINTER(_c.c_int), _c.POINTER(_c.c_int)]),
     "fnn_gemm_weight_only": (_c.c_int, [_c.c_void_p, _c.c_int, _c.c_int64, _c.c_void_p, _c.c_int,
                                         _c.c_void_p, _c.c_void_p, _c.c_int, _c.c_int64,
                                         _c.c_void_p, _c.c_int, _c.c_void_p, _c.c_int, _c.c_int64,
@@ -111,3 +112,10 @@ def device_status() -> int:
     code = ctypes.c_int(0)
     check(lib().fnn_device_status(ctypes.byref(code)))
     return code.value
+
+
+def a8w8_plan(m: int, n: int, k: int):
+    """(kernel, tile width) fnn_gemm_a8w8 picks for this shape: kernel 0 = single CTA, 1 = CTA pair, 2 = streaming decode."""
+    kern, tile = ctypes.c_int(0), ctypes.c_int(0)
+    check(lib().fnn_gemm_a8w8_plan(m, n, k, ctypes.byref(kern), ctypes.byref(tile)))
+    return kern.value, tile.value

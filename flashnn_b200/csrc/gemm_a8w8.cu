@@ -894,6 +894,21 @@ extern "C" int fnn_fused_moe_a8w8(const int8_t* a, int64_t lda, const int8_t* b,
 
 extern "C" size_t fnn_gemm_a8w8_workspace_bytes(int64_t, int64_t, int64_t) { return 0; }
 
+extern "C" int fnn_gemm_a8w8_plan(int64_t M, int64_t N, int64_t K, int* kernel, int* tile_n) {
+  using namespace fnn;
+  if (!kernel || !tile_n) return fail(FNN_ERR_NULL_POINTER, "gemm_a8w8_plan: null output pointer");
+  if (M <= 0 || N <= 0 || K <= 0 || M > INT32_MAX || N > INT32_MAX) return fail(FNN_ERR_SHAPE, "gemm_a8w8_plan: M, N, K must be positive");
+  if (M <= 8 && N >= 8192 && K % 4096 == 0) {  // the streaming decode kernel takes these when its own shape rules hold
+    *kernel = 2;
+    *tile_n = 16;
+    return FNN_OK;
+  }
+  const A8W8Plan plan = plan_a8w8(int(M), int(N), sm_count());
+  *kernel = plan.pair ? 1 : 0;
+  *tile_n = plan.bn;
+  return FNN_OK;
+}
+
 extern "C" int fnn_gemm_a8w8(const int8_t* a, int64_t lda, const int8_t* b, int64_t ldb, const void* alpha_row,
                              int row_dtype, const void* alpha_col, int col_dtype, void* out, int out_dtype,
                              int64_t ldo, int64_t M, int64_t N, int64_t K, int32_t* acc_out, int64_t ldacc,

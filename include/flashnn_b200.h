@@ -147,6 +147,16 @@ int fnn_gemm_a8w8(const int8_t* a, int64_t lda, const int8_t* b, int64_t ldb,
 size_t fnn_gemm_a8w8_workspace_bytes(int64_t M, int64_t N, int64_t K);
 
 /*
+ * Which kernel and output-tile width fnn_gemm_a8w8 picks for a problem with 16-byte-aligned operands on the current
+ * device (148 SMs are assumed when there is none): *kernel = 0 single-CTA tensor-core kernel (tile 128 x *tile_n),
+ * 1 CTA-pair tensor-core kernel (tile 256 x *tile_n), 2 the streaming decode kernel (16 output channels per step).
+ * This is the shape -> configuration table that takes the place of the reference's autotune cache
+ * (flashnn/triton_kernels/triton_utils.py:84-151); its constants are measured (flashnn_b200/csrc/a8w8_plan.h).
+ * Needs no GPU.
+ */
+int fnn_gemm_a8w8_plan(int64_t M, int64_t N, int64_t K, int* kernel, int* tile_n);
+
+/*
  * Fused mixture-of-experts A8W8 GEMM over expert-sorted token slots.
  * Replaces `fused_moe_a8w8_forward(A, B, C, alpha_row, alpha_col, topk_weights, topk_ids, sorted_token_ids, expert_ids,
  * num_tokens_post_padded, mul_routed_weight, top_k, BM)` (flashnn/triton_kernels/fused_moe_a8w8.py:176-290; arithmetic

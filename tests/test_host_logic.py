@@ -90,3 +90,23 @@ def test_options_round_trip_without_a_gpu():
     assert _lib.lib().fnn_get_option(12345) == -1
     with pytest.raises(_lib.FlashNNError):
         _lib.set_option(12345, 1)
+
+
+def test_a8w8_shape_to_tile_plan():
+    """The shape -> kernel / tile table (needs no GPU: 148 SMs are assumed without a device).  The cases are the ones
+    the plan was introduced for: shards of the FFN layer over 8 GPUs, the headline shape, decode shapes."""
+    import torch
+    from flashnn_b200 import _lib
+    if torch.cuda.is_available() and torch.cuda.get_device_properties(0).multi_processor_count != 148:
+        pytest.skip("the expected tiles are for 148 SMs")
+    assert _lib.a8w8_plan(8192, 8192, 8192) == (1, 256)
+    assert _lib.a8w8_plan(4096, 57344, 8192) == (1, 256)
+    assert _lib.a8w8_plan(4096, 7168, 8192) == (1, 224)     # 512 tiles = 6.92 waves instead of 448 = 6.05 -> 7
+    assert _lib.a8w8_plan(4096, 1024, 28672) == (1, 256)    # 64 pair tiles in one wave, not 256 single-CTA tiles
+    assert _lib.a8w8_plan(764, 8192, 8192) == (1, 192)
+    assert _lib.a8w8_plan(256, 512, 4096) == (0, 64)        # too small for the pair kernel to fill the GPU
+    assert _lib.a8w8_plan(64, 57344, 8192) == (0, 256)      # decode: the widest tile that still gives every SM work
+    assert _lib.a8w8_plan(16, 4096, 4096) == (0, 64)
+    assert _lib.a8w8_plan(1, 57344, 8192) == (2, 16)
+    with pytest.raises(_lib.FlashNNError):
+        _lib.a8w8_plan(0, 16, 16)
