@@ -107,12 +107,22 @@ __device__ __forceinline__ void store_chunk(const uint32_t (&r)[32], int row, in
         if (col0 + j < p.N) arow[j] = int32_t(r[j]);
     }
   }
+  // s = fl32(row scale * column scale) (rounded to the scales' dtype when both share a 16-bit one), out = fl32(acc * s):
+  // four column scales per shared-memory read, two products per packed fp32 multiply
   float v[32];
+  const uint64_t rs2 = pack_f32x2(rs, rs);
 #pragma unroll
-  for (int j = 0; j < 32; ++j) {
-    float s = __fmul_rn(rs, cs[j]);
-    if (same16) s = round_through(s, p.row_dtype);
-    v[j] = __fmul_rn(float(int32_t(r[j])), s);
+  for (int j = 0; j < 32; j += 4) {
+    const float4 c4 = *reinterpret_cast<const float4*>(cs + j);
+    float s0, s1, s2, s3;
+    unpack_f32x2(fmul2_rn(rs2, pack_f32x2(c4.x, c4.y)), s0, s1);
+    unpack_f32x2(fmul2_rn(rs2, pack_f32x2(c4.z, c4.w)), s2, s3);
+    if (same16) {
+      s0 = round_through(s0, p.row_dtype); s1 = round_through(s1, p.row_dtype);
+      s2 = round_through(s2, p.row_dtype); s3 = round_through(s3, p.row_dtype);
+    }
+    unpack_f32x2(fmul2_rn(pack_f32x2(float(int32_t(r[j])), float(int32_t(r[j + 1]))), pack_f32x2(s0, s1)), v[j], v[j + 1]);
+    unpack_f32x2(fmul2_rn(pack_f32x2(float(int32_t(r[j + 2])), float(int32_t(r[j + 3]))), pack_f32x2(s2, s3)), v[j + 2], v[j + 3]);
   }
   OutT* orow = reinterpret_cast<OutT*>(p.out) + int64_t(row) * p.ldo + col0;
   if (full && vec_ok) {
@@ -748,10 +758,12 @@ int dispatch(const int8_t* a, int64_t lda, const int8_t* b, int64_t ldb, const A
     a8w8_generic_kernel<OutT><<<unsigned((total + 255) / 256), 256, 0, st>>>(a, lda, b, ldb, p);
     return check_cuda(cudaGetLastError(), "a8w8 generic launch");
   }
-  // Up to 8 tokens against a wide weight matrix: the weight stream is all that matters, and the per-lane streaming
-  // kernel of the weight-only decode path moves it 6-10 % faster than tile copies do (it declines shapes it does
-  // not cover; with fewer row groups than a few per SM, or more tokens, the tile kernel is the faster one).
-  if (p.M <= 8 && p.N >= 8192 && opt_test_stall_us() == 0) {
+  // Up to 8 tokens: the weight stream is all that matters, and the per-lane streaming kernel of the weight-only
+  // decode path moves it faster than tile copies do: 6-10 % on wide matrices, and 2-3x on narrow, long ones
+  // (N = 1024 .. 4096 at K = 28672: 57 us -> 16 .. 33 us), where 64-column tiles leave most SMs without work while
+  // the streaming kernel has a CTA per 16 channels.  It declines shapes it does not cover (K not a multiple of its
+  // block, activations that do not fit its shared memory).
+  if (p.M <= 8 && p.N >= 512 && opt_test_stall_us() == 0) {
     const int r = gemv_a8w8_imma(a, lda, b, ldb, p.alpha_row, p.row_dtype, p.alpha_col, p.col_dtype, p.out,
                                  std::is_same<OutT, __half>::value ? FNN_F16 : FNN_BF16, p.ldo, p.M, p.N, p.K, p.acc_out,
                                  p.ldacc, st);
@@ -898,7 +910,7 @@ extern "C" int fnn_gemm_a8w8_plan(int64_t M, int64_t N, int64_t K, int* kernel, 
   using namespace fnn;
   if (!kernel || !tile_n) return fail(FNN_ERR_NULL_POINTER, "gemm_a8w8_plan: null output pointer");
   if (M <= 0 || N <= 0 || K <= 0 || M > INT32_MAX || N > INT32_MAX) return fail(FNN_ERR_SHAPE, "gemm_a8w8_plan: M, N, K must be positive");
-  if (M <= 8 && N >= 8192 && K % 4096 == 0) {  // the streaming decode kernel takes these when its own shape rules hold
+  if (M <= 8 && N >= 512 && N % 16 == 0 && K % 4096 == 0) {  // the streaming decode kernel takes these when its own shape rules hold
     *kernel = 2;
     *tile_n = 16;
     return FNN_OK;
