@@ -868,7 +868,7 @@ def run_case(args):
     elif name == "wog":
         # A16W4 prefill with group-wise scales (group 128): the decode config's weight at prefill batch sizes
         m, n, k = args.m or 2048, args.n or 28672, args.k or 8192
-        w = W.a16w4_decode(1, n, k, group=args.group or 128)
+        w = W.a16w4_decode(1, n, k, group=args.group if args.group > 0 else 128)
         x = W.rand_normal((m, k), 0, torch.bfloat16).to(device)
         qw, sc = w["qw"].to(device), w["scale"].to(device)
         if args.group == -1:  # per-channel scales on the same weights

@@ -182,7 +182,7 @@ __device__ __forceinline__ void pf_init_bars(const PfBars& b, int epi_arrivals, 
 }
 
 // warp 0 of both CTAs: TMA loads of this CTA's 128 activation rows and its raw weight bytes, one K block per stage
-template <int BITS>
+template <int BITS, int BN = kTN>
 __device__ __forceinline__ void pf_producer(uint8_t* smem, const PfBars& b, const CUtensorMap* tmap_x,
                                             const CUtensorMap* tmap_w, const PfParams& p, uint32_t rank, int pair_id,
                                             int num_pairs, volatile int* abort_flag) {
@@ -196,7 +196,7 @@ __device__ __forceinline__ void pf_producer(uint8_t* smem, const PfBars& b, cons
   for (int t = pair_id; t < num_tiles && ok; t += num_pairs) {
     int mb, nb;
     pf_tile_coords(t, p.tiles_m, p.tiles_n, mb, nb);
-    const int w_row = (BITS == 8) ? nb * kTN + int(rank) * (kTN / 2) : (nb * kTN + int(rank) * (kTN / 2)) / 2;
+    const int w_row = (BITS == 8) ? nb * BN + int(rank) * (BN / 2) : (nb * BN + int(rank) * (BN / 2)) / 2;
     for (int kb = 0; kb < p.k_blocks; ++kb) {
       ok = mbar_wait_bounded(&b.empty[stage], phase ^ 1, abort_flag);
       ok = __all_sync(0xffffffffu, ok);
@@ -206,7 +206,7 @@ __device__ __forceinline__ void pf_producer(uint8_t* smem, const PfBars& b, cons
       }
       if (leader_lane) {
         uint8_t* sx = smem + stage * L::kStageBytes;
-        mbar_expect_tx(&b.raw_full[stage], L::kXBytes + L::kRawBytes);
+        mbar_expect_tx(&b.raw_full[stage], L::kXBytes + ((BITS == 8) ? (BN / 2) * kTK : (BN / 4) * kTK));
         tma_load_2d(sx, tmap_x, &b.raw_full[stage], kb * kTK, mb * 256 + int(rank) * kTM);
         tma_load_2d(sx + L::kXBytes, tmap_w, &b.raw_full[stage], kb * kTK, w_row);
         ++issued;
@@ -225,11 +225,11 @@ __device__ __forceinline__ void pf_producer(uint8_t* smem, const PfBars& b, cons
 // warp 1 of the leader CTA: issues the MMAs of both CTAs.  An accumulator (one of the two TMEM buffers) collects
 // `kb_per_acc` K blocks and is then handed to the epilogue: the whole K range for per-channel scales, one scale
 // group for group-wise scales.
-template <typename T, int BITS>
+template <typename T, int BITS, int BN = kTN>
 __device__ __forceinline__ void pf_mma(uint8_t* smem, const PfBars& b, const PfParams& p, uint32_t tmem_base, int pair_id,
                                        int num_pairs, int kb_per_acc, volatile int* abort_flag) {
   using L = PfSmem<BITS>;
-  constexpr uint32_t idesc = umma_idesc(/*f32*/ 1, std::is_same<T, __half>::value ? 0u : 1u, 256, kTN);
+  constexpr uint32_t idesc = umma_idesc(/*f32*/ 1, std::is_same<T, __half>::value ? 0u : 1u, 256, BN);
   const int num_tiles = p.tiles_m * p.tiles_n;
   const bool leader_lane = elect_one();
   int stage = 0, cstage = 0;
@@ -310,7 +310,7 @@ __device__ __forceinline__ void pf_relay(const PfBars& b, const PfParams& p, int
 
 // four converter warps of both CTAs (ct = 0..127): raw bytes of a K block -> exact 16-bit integers in the K-major
 // 128-byte-swizzled operand tile
-template <typename T, int BITS>
+template <typename T, int BITS, int BN = kTN>
 __device__ __forceinline__ void pf_converters(uint8_t* smem, const PfBars& b, const PfParams& p, uint32_t rank, int pair_id,
                                               int num_pairs, int ct, volatile int* abort_flag) {
   using L = PfSmem<BITS>;
@@ -336,6 +336,7 @@ __device__ __forceinline__ void pf_converters(uint8_t* smem, const PfBars& b, co
         for (int i = 0; i < 4; ++i) {
           const int id = ct + i * 128;
           const uint32_t row = id >> 2, c = id & 3;
+          if (BN < kTN && row >= BN / 2) continue;  // a narrower tile brings fewer weight rows
           const uint4 w = *reinterpret_cast<const uint4*>(raw + id * 16);
           uint4 o0, o1;
           cvt_int8x4<T>(w.x, o0.x, o0.y);
@@ -351,6 +352,7 @@ __device__ __forceinline__ void pf_converters(uint8_t* smem, const PfBars& b, co
         for (int i = 0; i < 2; ++i) {
           const int id = ct + i * 128;
           const uint32_t prow = id >> 2, c = id & 3;
+          if (BN < kTN && prow >= BN / 4) continue;
           const uint4 w = *reinterpret_cast<const uint4*>(raw + id * 16);
           uint4 l0, l1, h0, h1;
           cvt_int4x8<T>(w.x, l0.x, l0.y, h0.x, h0.y);
@@ -376,7 +378,9 @@ __device__ __forceinline__ void pf_converters(uint8_t* smem, const PfBars& b, co
 // Per-channel scales: ten warps (TMA, MMA, four epilogue, four converters); the accumulator of a tile is read
 // once, out = acc * s[n] - xsum[m] * s[n] zp[n] + bias[n].
 // ---------------------------------------------------------------------------------------------------------
-template <typename T, int BITS>
+// BN: channels per pair tile (256, or narrower where that fills the last wave better; the shared-memory and TMEM
+// layout stays that of 256, a narrower tile simply uses fewer rows / columns of it).
+template <typename T, int BITS, int BN>
 __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(kPfThreads, 1)
 wo_umma_pair_kernel(const __grid_constant__ CUtensorMap tmap_x, const __grid_constant__ CUtensorMap tmap_w,
                     const PfParams p) {
@@ -413,9 +417,9 @@ wo_umma_pair_kernel(const __grid_constant__ CUtensorMap tmap_x, const __grid_con
   const uint32_t tmem_base = *tmem_slot;
 
   if (warp == 0) {
-    pf_producer<BITS>(smem, b, &tmap_x, &tmap_w, p, rank, pair_id, num_pairs, abort_flag);
+    pf_producer<BITS, BN>(smem, b, &tmap_x, &tmap_w, p, rank, pair_id, num_pairs, abort_flag);
   } else if (warp == 1) {
-    if (rank == 0) pf_mma<T, BITS>(smem, b, p, tmem_base, pair_id, num_pairs, p.k_blocks, abort_flag);
+    if (rank == 0) pf_mma<T, BITS, BN>(smem, b, p, tmem_base, pair_id, num_pairs, p.k_blocks, abort_flag);
     else pf_relay(b, p, pair_id, num_pairs, abort_flag);
   } else if (warp < 6) {
     // -------------------------------- epilogue (both CTAs) --------------------------------
@@ -433,8 +437,8 @@ wo_umma_pair_kernel(const __grid_constant__ CUtensorMap tmap_x, const __grid_con
       const int buf = local & 1;
       const uint32_t acc_phase = (local >> 1) & 1;
       const int row = mb * 256 + int(rank) * kTM + quarter * 32 + lane;
-      const int n0 = nb * kTN;
-      for (int j = lane; j < kTN; j += 32) {
+      const int n0 = nb * BN;
+      for (int j = lane; j < BN; j += 32) {
         const bool in = n0 + j < p.N;
         const float s = in ? load_as_f32(p.scale, p.scale_dtype, n0 + j) : 0.f;
         cs[j] = s;
@@ -453,7 +457,7 @@ wo_umma_pair_kernel(const __grid_constant__ CUtensorMap tmap_x, const __grid_con
       tc_fence_after();
       const uint32_t taddr = tmem_base + (uint32_t(quarter * 32) << 16) + buf * kTN;
 #pragma unroll 1
-      for (int c = 0; c < kTN / 32; ++c) {
+      for (int c = 0; c < BN / 32; ++c) {
         uint32_t r[32];
         tmem_ld_32x32(taddr + c * 32, r);
         tc_wait_ld();
@@ -482,7 +486,7 @@ wo_umma_pair_kernel(const __grid_constant__ CUtensorMap tmap_x, const __grid_con
       if (lane == 0) mbar_arrive_cluster(map_to_cta(smem_u32(&b.tmem_empty[buf]), 0));
     }
   } else {
-    pf_converters<T, BITS>(smem, b, p, rank, pair_id, num_pairs, threadIdx.x - 6 * 32, abort_flag);
+    pf_converters<T, BITS, BN>(smem, b, p, rank, pair_id, num_pairs, threadIdx.x - 6 * 32, abort_flag);
   }
 
   // -------------------------------- teardown --------------------------------
@@ -739,18 +743,46 @@ int pf_configure(KernT kern, int bytes, cudaError_t (&attr_err)[64], std::once_f
   return attr_err[dev] == cudaSuccess ? FNN_OK : check_cuda(attr_err[dev], "cudaFuncSetAttribute(weight-only prefill)");
 }
 
+// Tile width of the per-channel kernel: waves x width x a small per-width cost (a narrower tile re-reads the
+// activation rows for fewer channels); ties keep the wider tile.
+inline int pf_pick_bn(int M, int N, int pairs) {
+  const int widths[3] = {256, 224, 192};
+  const double cost_of[3] = {1.0, 1.03, 1.06};
+  const int tiles_m = (M + 255) / 256;
+  int best = 256;
+  double best_cost = 1e30;
+  for (int i = 0; i < 3; ++i) {
+    const long long tiles = 1ll * tiles_m * ((N + widths[i] - 1) / widths[i]);
+    const double cost = double((tiles + pairs - 1) / pairs) * widths[i] * cost_of[i];
+    if (cost < best_cost) { best_cost = cost; best = widths[i]; }
+  }
+  return best;
+}
+
+template <typename T, int BITS, int BN>
+int launch_prefill_perch(const T* act, int64_t lda, const uint8_t* qw, PfParams p, cudaStream_t st) {
+  using L = PfSmem<BITS>;
+  static std::once_flag once[64];
+  static cudaError_t attr_err[64];  // per device, so that a failure is reported on every call and not only the first
+  if (int e = pf_configure(wo_umma_pair_kernel<T, BITS, BN>, L::kDynamicBytes, attr_err, once)) return e;
+  CUtensorMap tx, tw;
+  if (int e = make_tmap_2d(&tx, 2, act, p.M, p.K, lda * 2, kTK, kTM, true)) return e;
+  const int64_t w_rows = (BITS == 8) ? p.N : p.N / 2;
+  if (int e = make_tmap_2d(&tw, 1, qw, w_rows, p.K, p.K, kTK, (BITS == 8) ? BN / 2 : BN / 4, false)) return e;
+  p.tiles_m = (p.M + 255) / 256;
+  p.tiles_n = (p.N + BN - 1) / BN;
+  p.k_blocks = (p.K + kTK - 1) / kTK;
+  const int tiles = p.tiles_m * p.tiles_n;
+  const int pairs = tiles < sm_count() / 2 ? tiles : sm_count() / 2;
+  wo_umma_pair_kernel<T, BITS, BN><<<2 * pairs, kPfThreads, L::kDynamicBytes, st>>>(tx, tw, p);
+  return check_cuda(cudaGetLastError(), "weight-only prefill launch");
+}
+
 template <typename T, int BITS>
 int launch_prefill(const T* act, int64_t lda, const uint8_t* qw, PfParams p, float* xsum_ws, cudaStream_t st) {
   using L = PfSmem<BITS>;
   static_assert(L::kDynamicBytes <= 227 * 1024, "shared memory budget");
   static_assert(L::kStageBytes % 1024 == 0 && L::kWBytes % 1024 == 0 && L::kConvOff % 1024 == 0, "tile alignment");
-  // per device, so that a failure is reported on every call and not only the first
-  static std::once_flag once[3][64];
-  static cudaError_t attr_err[3][64];
-  const int which = p.group == 0 ? 0 : (p.zp ? 2 : 1);
-  if (which == 0) { if (int e = pf_configure(wo_umma_pair_kernel<T, BITS>, L::kDynamicBytes, attr_err[0], once[0])) return e; }
-  else if (which == 1) { if (int e = pf_configure(wo_umma_pair_group_kernel<T, BITS, false>, L::kDynamicBytes, attr_err[1], once[1])) return e; }
-  else { if (int e = pf_configure(wo_umma_pair_group_kernel<T, BITS, true>, L::kDynamicBytes, attr_err[2], once[2])) return e; }
   if (p.zp) {
     const unsigned blocks = unsigned((int64_t(p.M) * 32 + 255) / 256);
     if (p.group == 0) row_sum_kernel<T><<<blocks, 256, 0, st>>>(act, lda, xsum_ws, p.M, p.K);
@@ -758,6 +790,19 @@ int launch_prefill(const T* act, int64_t lda, const uint8_t* qw, PfParams p, flo
     if (int e = check_cuda(cudaGetLastError(), "row_sum launch")) return e;
     p.xsum = xsum_ws;
   }
+  if (p.group == 0) {
+    switch (pf_pick_bn(p.M, p.N, sm_count() / 2)) {
+      case 224: return launch_prefill_perch<T, BITS, 224>(act, lda, qw, p, st);
+      case 192: return launch_prefill_perch<T, BITS, 192>(act, lda, qw, p, st);
+      default: return launch_prefill_perch<T, BITS, 256>(act, lda, qw, p, st);
+    }
+  }
+  // per device, so that a failure is reported on every call and not only the first
+  static std::once_flag once[2][64];
+  static cudaError_t attr_err[2][64];
+  const int which = p.zp ? 1 : 0;
+  if (which == 0) { if (int e = pf_configure(wo_umma_pair_group_kernel<T, BITS, false>, L::kDynamicBytes, attr_err[0], once[0])) return e; }
+  else { if (int e = pf_configure(wo_umma_pair_group_kernel<T, BITS, true>, L::kDynamicBytes, attr_err[1], once[1])) return e; }
   CUtensorMap tx, tw;
   if (int e = make_tmap_2d(&tx, 2, act, p.M, p.K, lda * 2, kTK, kTM, true)) return e;
   const int64_t w_rows = (BITS == 8) ? p.N : p.N / 2;
@@ -767,8 +812,7 @@ int launch_prefill(const T* act, int64_t lda, const uint8_t* qw, PfParams p, flo
   p.k_blocks = (p.K + kTK - 1) / kTK;
   const int tiles = p.tiles_m * p.tiles_n;
   const int pairs = tiles < sm_count() / 2 ? tiles : sm_count() / 2;
-  if (which == 0) wo_umma_pair_kernel<T, BITS><<<2 * pairs, kPfThreads, L::kDynamicBytes, st>>>(tx, tw, p);
-  else if (which == 1) wo_umma_pair_group_kernel<T, BITS, false><<<2 * pairs, kPgThreads, L::kDynamicBytes, st>>>(tx, tw, p);
+  if (which == 0) wo_umma_pair_group_kernel<T, BITS, false><<<2 * pairs, kPgThreads, L::kDynamicBytes, st>>>(tx, tw, p);
   else wo_umma_pair_group_kernel<T, BITS, true><<<2 * pairs, kPgThreads, L::kDynamicBytes, st>>>(tx, tw, p);
   return check_cuda(cudaGetLastError(), "weight-only prefill launch");
 }
