@@ -839,9 +839,11 @@ def run_case(args):
         op = flashnn_b200.GemmA8W8(torch.bfloat16)
         fn = lambda: op(a, b, row, col)
         work, unit = W.a8w8_ops(m, n, k) / 1e12, "TOPS"
+        from flashnn_b200 import _lib
         if args.tile:
-            from flashnn_b200 import _lib
             _lib.set_option(_lib.OPT_A8W8_PAIR_TILE, args.tile)
+        if args.balanced:
+            _lib.set_option(_lib.OPT_A8W8_BALANCED, args.balanced)
     elif name == "gemv":
         m, n, k = args.m or 1, args.n or 28672, args.k or 8192
         w = W.a16w4_decode(m, n, k)
@@ -935,6 +937,7 @@ def main():
     ap.add_argument("--case", choices=["a8w8", "gemv", "gemv8", "dq", "wo", "wog", "rmsdq", "lndq", "moe", "moe4", "ref_triton", "sweep"],
                     help="run one kernel only (profiling / A-B timing), the reference's Triton kernels, or the reference's shape sweep")
     ap.add_argument("--tile", type=int, default=0, help="with --case a8w8: force this CTA-pair tile width (tuning)")
+    ap.add_argument("--balanced", type=int, default=0, help="with --case a8w8: 1 forces, 2 forbids the K-balanced mode of the CTA-pair kernel")
     ap.add_argument("--group", type=int, default=0, help="with --case wog: scale group size (-1: per channel)")
     ap.add_argument("--m", type=int)
     ap.add_argument("--n", type=int)

@@ -100,6 +100,7 @@ def check(status: int):
 OPT_STATIC_WEIGHTS = 1
 OPT_TEST_STALL_US = 2  # test hook, see include/flashnn_b200.h
 OPT_A8W8_PAIR_TILE = 3  # tuning hook
+OPT_A8W8_BALANCED = 4  # 0 by shape, 1 always where possible, 2 never
 
 
 def set_option(option: int, value: int) -> None:
@@ -115,7 +116,8 @@ def device_status() -> int:
 
 
 def a8w8_plan(m: int, n: int, k: int):
-    """(kernel, tile width) fnn_gemm_a8w8 picks for this shape: kernel 0 = single CTA, 1 = CTA pair, 2 = streaming decode."""
+    """(kernel, tile width) fnn_gemm_a8w8 picks for this shape: kernel 0 = single CTA, 1 = CTA pair, 2 = streaming decode,
+    3 = CTA pair with the K blocks dealt out evenly (needs the workspace)."""
     kern, tile = ctypes.c_int(0), ctypes.c_int(0)
     check(lib().fnn_gemm_a8w8_plan(m, n, k, ctypes.byref(kern), ctypes.byref(tile)))
     return kern.value, tile.value

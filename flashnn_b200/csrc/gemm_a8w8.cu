@@ -15,6 +15,8 @@
 // Every wait is bounded: a role that runs out of time records a code in the
 // device status word, raises the CTA's abort flag, and all roles fall through to
 // a common teardown that drains outstanding copies and MMAs and frees TMEM.
+#include <atomic>
+#include <chrono>
 #include <mutex>
 
 #include <type_traits>
@@ -52,6 +54,14 @@ struct A8W8Params {
   const void* topk_w;              // [num_valid] routing weights
   int topk_w_dtype, top_k, block_m, tile_rows, num_valid, mul_w;
   int64_t col_stride_e;            // elements between two experts' rows of alpha_col
+  // K-balanced mode of the CTA-pair kernel (template flag SK): the sk_tiles tiles of the ragged round are shared.
+  // Pair i < sk_tiles computes K blocks [0, sk_units) of tile i; the other pairs share the tails [sk_units, k_blocks)
+  // evenly (sk_tail_units consecutive blocks of the concatenated tails each), leave the int32 partial sums of each
+  // piece in a slot of sk_partials and raise the slot's flags to sk_epoch; the pair that holds a tile's head adds them.
+  unsigned long long* sk_flags;    // [slots][8] one word per epilogue warp of a pair
+  int32_t* sk_partials;            // [slots][256 * 256]
+  unsigned long long sk_epoch;     // never 0, different for every launch
+  int sk_tiles, sk_units, sk_tail_units, sk_slots;  // sk_slots: slots reserved per tail-sharing pair
 };
 
 // AROWS: rows of A one stage holds (16, 32, 64 or 128).  Decode shapes are bound by the weight stream, and what
@@ -402,6 +412,94 @@ a8w8_umma_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_consta
 //   tmem_full[b]   in each CTA; signalled the same way when a tile's accumulator is complete
 //   tmem_empty[b]  in the leader; 8 arrivals (4 epilogue warps of each CTA, the peer's remotely)
 // ---------------------------------------------------------------------------
+// Work list of one CTA pair; its three roles walk the same list.  Plain mode: whole tiles pair_id, pair_id +
+// num_pairs, ...  K-balanced mode: the tiles of the ragged round (the first sk_tiles) come first.  Pair i < sk_tiles
+// takes the head [0, sk_units) of tile i, so all heads advance through K in step, like whole tiles do (which is what
+// keeps the operand re-reads in L2); the remaining pairs walk their share of the tails and hand each piece over.
+// The whole rounds follow, for every pair alike, and hide the longer epilogue of a head behind their MMAs.
+template <bool SK> struct PairWork {
+  int tile, kb0, kb1;  // the current piece: K blocks [kb0, kb1) of a tile
+  int slot;            // workspace slot a tail piece is handed over in, -1 for any other piece
+  bool head;           // head of a shared tile: its epilogue adds the tail pieces
+  int next_plain, step, num_tiles, k_blocks;
+  int pair, units, tail, pos, pos_end, next_slot;
+  bool head_pending;
+  __device__ __forceinline__ PairWork(const A8W8Params& p, int pair_id, int num_pairs) {
+    k_blocks = p.k_blocks;
+    num_tiles = p.tiles_m * p.tiles_n;
+    step = num_pairs;
+    next_plain = pair_id;
+    tile = kb0 = kb1 = 0;
+    slot = -1;
+    head = head_pending = false;
+    pair = pair_id;
+    units = tail = pos = pos_end = next_slot = 0;
+    if (SK) {
+      next_plain += p.sk_tiles;
+      units = p.sk_units;
+      tail = k_blocks - units;
+      if (pair_id < p.sk_tiles) {
+        head_pending = true;
+      } else {
+        const int h = pair_id - p.sk_tiles;
+        pos = min(p.sk_tiles * tail, h * p.sk_tail_units);
+        pos_end = min(p.sk_tiles * tail, pos + p.sk_tail_units);
+        next_slot = h * p.sk_slots;
+      }
+    }
+  }
+  __device__ __forceinline__ bool next() {
+    slot = -1;
+    head = false;
+    if (SK && head_pending) {
+      head_pending = false;
+      tile = pair;
+      kb0 = 0;
+      kb1 = units;
+      head = tail > 0;
+      return true;
+    }
+    if (SK && pos < pos_end) {
+      tile = pos / tail;
+      const int off = pos - tile * tail;
+      const int len = min(tail - off, pos_end - pos);
+      kb0 = units + off;
+      kb1 = kb0 + len;
+      pos += len;
+      slot = next_slot++;
+      return true;
+    }
+    tile = next_plain;
+    next_plain += step;
+    kb0 = 0;
+    kb1 = k_blocks;
+    return tile < num_tiles;
+  }
+};
+
+__device__ __forceinline__ void flag_store_release(unsigned long long* f, unsigned long long v) {
+  asm volatile("st.release.gpu.global.u64 [%0], %1;" ::"l"(f), "l"(v) : "memory");
+}
+__device__ __forceinline__ unsigned long long flag_load_acquire(const unsigned long long* f) {
+  unsigned long long v;
+  asm volatile("ld.acquire.gpu.global.u64 %0, [%1];" : "=l"(v) : "l"(f) : "memory");
+  return v;
+}
+// Bounded wait (one lane) until *f == want; false when the limit ran out or another role reported a failure.
+__device__ __forceinline__ bool flag_wait_bounded(const unsigned long long* f, unsigned long long want,
+                                                  volatile int* abort_flag) {
+  if (flag_load_acquire(f) == want) return true;
+  const uint64_t t0 = global_timer_ns();
+  uint32_t spins = 0;
+  while (true) {
+    if (flag_load_acquire(f) == want) return true;
+    if ((++spins & 0x3f) == 0) {
+      if (*abort_flag != 0) return false;
+      if (global_timer_ns() - t0 > kWaitLimitNs) return false;
+    }
+  }
+}
+
 template <int BN, int STAGES> struct PairSmem {
   static constexpr int kBN = BN;                        // output columns of a pair tile (a multiple of 32, at most 256)
   static constexpr int kABytes = kBM * kBK;             // this CTA's 128 rows of A
@@ -416,7 +514,7 @@ template <int BN, int STAGES> struct PairSmem {
   static constexpr int kDynamicBytes = kTotal + 1024;
 };
 
-template <typename OutT, int BN, int STAGES>
+template <typename OutT, int BN, int STAGES, bool SK>
 __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(kThreads, 1)
 a8w8_umma_pair_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ CUtensorMap tmap_b,
                       const A8W8Params p) {
@@ -439,7 +537,6 @@ a8w8_umma_pair_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_c
   const uint32_t rank = cluster_ctarank();  // 0 = leader
   const int pair_id = blockIdx.x >> 1;
   const int num_pairs = gridDim.x >> 1;
-  const int num_tiles = p.tiles_m * p.tiles_n;  // 256 x BN tiles
   constexpr uint32_t kTmemCols = 2 * kAccStride;
 
   if (threadIdx.x == 0) {
@@ -474,10 +571,11 @@ a8w8_umma_pair_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_c
     uint32_t phase = 0;
     long long issued = 0;
     bool ok = true;
-    for (int t = pair_id; t < num_tiles && ok; t += num_pairs) {
+    PairWork<SK> w(p, pair_id, num_pairs);
+    while (ok && w.next()) {
       int mb, nb;
-      tile_coords(t, p.tiles_m, p.tiles_n, mb, nb);
-      for (int kb = 0; kb < p.k_blocks; ++kb) {
+      tile_coords(w.tile, p.tiles_m, p.tiles_n, mb, nb);
+      for (int kb = w.kb0; kb < w.kb1; ++kb) {
         ok = mbar_wait_bounded(&empty_bar[stage], phase ^ 1, abort_flag);
         ok = __all_sync(0xffffffffu, ok);
         if (!ok) {
@@ -513,7 +611,8 @@ a8w8_umma_pair_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_c
       int local = 0;
       bool ok = true;
       bool issued_any = false;
-      for (int t = pair_id; t < num_tiles && ok; t += num_pairs, ++local) {
+      PairWork<SK> w(p, pair_id, num_pairs);
+      for (; ok && w.next(); ++local) {
         const int buf = local & 1;
         const uint32_t acc_phase = (local >> 1) & 1;
         ok = mbar_wait_bounded(&tmem_empty_bar[buf], acc_phase ^ 1, abort_flag);
@@ -524,7 +623,7 @@ a8w8_umma_pair_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_c
         }
         tc_fence_after();
         const uint32_t tmem_d = tmem_base + buf * kAccStride;
-        for (int kb = 0; kb < p.k_blocks; ++kb) {
+        for (int kb = w.kb0; kb < w.kb1; ++kb) {
           ok = mbar_wait_bounded(&full_bar[stage], phase, abort_flag);
           ok = __all_sync(0xffffffffu, ok);
           if (!ok) {
@@ -538,7 +637,7 @@ a8w8_umma_pair_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_c
 #pragma unroll
             for (int k = 0; k < kBK / kUmmaK; ++k)
               umma_i8_pair(tmem_d, umma_desc_k_sw128(sa + k * kUmmaK), umma_desc_k_sw128(sb + k * kUmmaK), idesc,
-                           (kb | k) != 0 ? 1u : 0u);
+                           (kb != w.kb0 || k != 0) ? 1u : 0u);
             tc_commit_pair(&empty_bar[stage], 0x3);  // frees this stage in both CTAs
             issued_any = true;
           }
@@ -564,12 +663,24 @@ a8w8_umma_pair_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_c
     const bool acc_vec_ok = p.acc_out && (p.ldacc % 4 == 0) && (reinterpret_cast<uintptr_t>(p.acc_out) % 16 == 0);
     int local = 0;
     bool ok = true;
-    for (int t = pair_id; t < num_tiles && ok; t += num_pairs, ++local) {
+    PairWork<SK> w(p, pair_id, num_pairs);
+    const int my_flag = int(rank) * 4 + quarter;                        // this warp's flag word within a pair's eight
+    const int my_row = int(rank) * 128 + quarter * 32 + lane;           // this thread's row within a tile
+    for (; ok && w.next(); ++local) {
       int mb, nb;
-      tile_coords(t, p.tiles_m, p.tiles_n, mb, nb);
+      tile_coords(w.tile, p.tiles_m, p.tiles_n, mb, nb);
       const int buf = local & 1;
       const uint32_t acc_phase = (local >> 1) & 1;
-      const int row = mb * 256 + int(rank) * 128 + quarter * 32 + lane;
+      const int row = mb * 256 + my_row;
+      // K-balanced mode: a tail piece is handed over; a head adds the pieces of its tile's tail, which lie in the
+      // slots of the tail-sharing pairs first_h .. last_h
+      const bool hands_over = SK && w.slot >= 0;
+      const bool adds = SK && w.head;
+      const int tail_blocks = p.k_blocks - p.sk_units;
+      const int first_h = adds ? (w.tile * tail_blocks) / p.sk_tail_units : 0;
+      const int last_h = adds ? ((w.tile + 1) * tail_blocks - 1) / p.sk_tail_units : -1;
+      // slot of the piece of this tile that tail-sharing pair h computed: its pieces are of consecutive tiles
+      auto slot_of = [&](int h) { return h * p.sk_slots + (w.tile - (h * p.sk_tail_units) / tail_blocks); };
       const int n0 = nb * BN;
       for (int j = lane; j < BN; j += 32)
         cs[j] = (n0 + j < p.N) ? load_as_f32(p.alpha_col, p.col_dtype, n0 + j) : 0.f;
@@ -583,17 +694,81 @@ a8w8_umma_pair_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_c
         break;
       }
       tc_fence_after();
+      if (adds) {
+        // wait (bounded) until every piece of the tail has been delivered for this warp's rows
+        for (int h = first_h; h <= last_h && ok; ++h) {
+          if (lane == 0) ok = flag_wait_bounded(p.sk_flags + slot_of(h) * 8 + my_flag, p.sk_epoch, abort_flag);
+          ok = __shfl_sync(0xffffffffu, int(ok), 0) != 0;
+        }
+        __syncwarp();  // lane 0's acquire orders the other lanes' reads of the sums as well
+        if (!ok) {
+          if (lane == 0) report(p.status, abort_flag, DEV_TIMEOUT_EPILOGUE);
+          break;
+        }
+      }
       const uint32_t taddr = tmem_base + (uint32_t(quarter * 32) << 16) + buf * kAccStride;
+      // Partial sums in the workspace: slot of a pair = [chunk of 32 columns][epilogue warp of the pair][j][lane]
+      // 16-byte words, word j of a lane holding its row's columns 4j .. 4j+3 of the chunk: every warp access is 512
+      // contiguous bytes, and the warp that reads a word is the one (same CTA rank, same quarter) that wrote it.
+      auto slot_word = [&](int slot, int c) {
+        return reinterpret_cast<uint4*>(p.sk_partials + size_t(slot) * 256 * 256) + ((c * 8 + my_flag) * 8) * 32 + lane;
+      };
+      uint4 ahead[8];  // the first tail piece's sums of the chunk after the current one, fetched a chunk early
+      if (adds) {
+        const uint4* src = slot_word(slot_of(first_h), 0);
+#pragma unroll
+        for (int j = 0; j < 8; ++j) ahead[j] = __ldcg(src + j * 32);  // written by another SM in this launch: read through L2
+      }
 #pragma unroll 1
       for (int c = 0; c < BN / 32; ++c) {
         uint32_t r[32];
         tmem_ld_32x32(taddr + c * 32, r);
+        uint4 cur[8];
+        if (adds) {
+#pragma unroll
+          for (int j = 0; j < 8; ++j) cur[j] = ahead[j];
+          if (c + 1 < BN / 32) {
+            const uint4* src = slot_word(slot_of(first_h), c + 1);
+#pragma unroll
+            for (int j = 0; j < 8; ++j) ahead[j] = __ldcg(src + j * 32);
+          }
+        }
         tc_wait_ld();
+        if (hands_over) {
+          uint4* dst = slot_word(w.slot, c);  // the raw sums
+#pragma unroll
+          for (int j = 0; j < 8; ++j) dst[j * 32] = make_uint4(r[4 * j], r[4 * j + 1], r[4 * j + 2], r[4 * j + 3]);
+          continue;
+        }
+        if (adds) {
+          // int32 sums: exact in any order
+#pragma unroll
+          for (int j = 0; j < 8; ++j) {
+            r[4 * j] += cur[j].x; r[4 * j + 1] += cur[j].y; r[4 * j + 2] += cur[j].z; r[4 * j + 3] += cur[j].w;
+          }
+          for (int h = first_h + 1; h <= last_h; ++h) {  // a tail cut into more than one piece
+            const uint4* src = slot_word(slot_of(h), c);
+#pragma unroll
+            for (int j = 0; j < 8; ++j) {
+              const uint4 v = __ldcg(src + j * 32);
+              r[4 * j] += v.x; r[4 * j + 1] += v.y; r[4 * j + 2] += v.z; r[4 * j + 3] += v.w;
+            }
+          }
+        }
         store_chunk<OutT>(r, row, n0 + c * 32, rs, cs + c * 32, same16, p, vec_ok, acc_vec_ok);
       }
       tc_fence_before();
       __syncwarp();
-      if (lane == 0) mbar_arrive_cluster(map_to_cta(smem_u32(&tmem_empty_bar[buf]), 0));
+      if (lane == 0) mbar_arrive_cluster(map_to_cta(smem_u32(&tmem_empty_bar[buf]), 0));  // the accumulator is free again
+      if (hands_over) {
+        // the warp's stores are ordered before lane 0 by the barrier above, and its release makes them visible
+        // device-wide before the flag says so
+        if (lane == 0) flag_store_release(p.sk_flags + w.slot * 8 + my_flag, p.sk_epoch);
+      } else if (adds && lane == 0) {
+        // consumed: the words go back to 0, so that a replay of this launch (same epoch) waits again
+        for (int h = first_h; h <= last_h; ++h)
+          *reinterpret_cast<volatile unsigned long long*>(p.sk_flags + slot_of(h) * 8 + my_flag) = 0ull;
+      }
     }
   }
 
@@ -674,15 +849,57 @@ int launch_umma_rows(const int8_t* a, int64_t lda, const int8_t* b, int64_t ldb,
   return launch_umma<OutT, BN, kBudget / ((kBM + BN) * kBK) < 8 ? kBudget / ((kBM + BN) * kBK) : 8, kBM>(a, lda, b, ldb, p, st);
 }
 
-template <typename OutT, int BN>
-int launch_pair(const int8_t* a, int64_t lda, const int8_t* b, int64_t ldb, A8W8Params p, cudaStream_t st) {
+// Geometry of the K-balanced mode for `tiles` 256-wide tiles of `kbs` K blocks on `pairs` CTA pairs.
+struct SkSplit {
+  int tiles;       // shared tiles: the ragged round
+  int units;       // K blocks of a head
+  int tail_units;  // K blocks of the concatenated tails per tail-sharing pair
+  int slots;       // pieces a tail-sharing pair may hand over
+  bool valid;
+};
+inline SkSplit sk_split(long long tiles, int kbs, int pairs) {
+  SkSplit s{0, 0, 0, 0, false};
+  const int ragged = int(tiles % pairs);
+  if (ragged == 0 || kbs < 2) return s;
+  s.tiles = ragged;
+  // A pair that walks tail pieces is slower than one that computes a head: its operands are not being read by
+  // other pairs at the same moment (the heads advance through K together and meet in L2), and every piece has an
+  // epilogue of its own.  Measured: about 0.85 of the heads' rate, and 8 K blocks' time per share (less for short K).  The heads take
+  // that much more, so that both kinds finish together.
+  const int helpers = pairs - ragged;
+  const double head = (double(ragged) * kbs + helpers * (kbs < 64 ? kbs / 8.0 : 8.0)) / (ragged + helpers * 0.85);
+  s.units = int(head + 0.999);
+  if (s.units >= kbs) return s;
+  const int tail = kbs - s.units;
+  s.tail_units = int((1ll * ragged * tail + helpers - 1) / helpers);
+  s.slots = (s.tail_units + tail - 1) / tail + 1;
+  s.valid = true;
+  return s;
+}
+
+// Bytes of scratch the K-balanced mode needs: eight flag words and a 256 x 256 int32 slot per piece that can be
+// handed over; fewer than two pieces per CTA pair whatever the shape.
+constexpr size_t kSkFlagBytes = 16384;
+inline int sk_max_slots(int sms) { return 2 * (sms / 2); }
+inline size_t sk_workspace_bytes(int sms) { return kSkFlagBytes + size_t(sk_max_slots(sms)) * 256 * 256 * 4; }
+
+inline unsigned long long next_sk_epoch() {
+  static std::atomic<unsigned long long> epoch{
+      (static_cast<unsigned long long>(std::chrono::steady_clock::now().time_since_epoch().count()) * 0x9E3779B97F4A7C15ull) | 1ull};
+  unsigned long long e = epoch.fetch_add(2, std::memory_order_relaxed);  // stays odd: never 0
+  return e;
+}
+
+template <typename OutT, int BN, bool SK = false>
+int launch_pair(const int8_t* a, int64_t lda, const int8_t* b, int64_t ldb, A8W8Params p, cudaStream_t st,
+                void* workspace = nullptr) {
   constexpr int kBudget = 212 * 1024;
   constexpr int STAGES = kBudget / (kBM * kBK + (BN / 2) * kBK) < 8 ? kBudget / (kBM * kBK + (BN / 2) * kBK) : 8;
   using L = PairSmem<BN, STAGES>;
   static_assert(L::kDynamicBytes <= 227 * 1024, "shared memory budget");
   static_assert(L::kStageBytes % 1024 == 0 && L::kABytes % 1024 == 0, "tiles must stay 1024-byte aligned");
   static_assert(BN % 32 == 0 && BN <= 256, "pair tile width");
-  auto kern = a8w8_umma_pair_kernel<OutT, BN, STAGES>;
+  auto kern = a8w8_umma_pair_kernel<OutT, BN, STAGES, SK>;
   static std::once_flag once[64];
   static cudaError_t attr_err[64];  // per device, so that a failure is reported on every call and not only the first
   int dev = 0;
@@ -699,7 +916,20 @@ int launch_pair(const int8_t* a, int64_t lda, const int8_t* b, int64_t ldb, A8W8
   p.tiles_n = (p.N + BN - 1) / BN;
   p.k_blocks = (p.K + kBK - 1) / kBK;
   const int tiles = p.tiles_m * p.tiles_n;
-  const int pairs = tiles < sm_count() / 2 ? tiles : sm_count() / 2;
+  int pairs = tiles < sm_count() / 2 ? tiles : sm_count() / 2;
+  if (SK) {
+    pairs = sm_count() / 2;
+    const SkSplit split = sk_split(tiles, p.k_blocks, pairs);
+    if (!split.valid || (pairs - split.tiles) * split.slots > sk_max_slots(sm_count()))
+      return fail(FNN_ERR_UNSUPPORTED, "a8w8: the K-balanced mode does not apply to this shape");
+    p.sk_tiles = split.tiles;
+    p.sk_units = split.units;
+    p.sk_tail_units = split.tail_units;
+    p.sk_slots = split.slots;
+    p.sk_flags = static_cast<unsigned long long*>(workspace);
+    p.sk_partials = reinterpret_cast<int32_t*>(static_cast<uint8_t*>(workspace) + kSkFlagBytes);
+    p.sk_epoch = next_sk_epoch();
+  }
   kern<<<2 * pairs, kThreads, L::kDynamicBytes, st>>>(ta, tb, p);
   return check_cuda(cudaGetLastError(), "a8w8 tcgen05 (CTA pair) launch");
 }
@@ -719,7 +949,36 @@ struct A8W8Plan {
   bool pair;
   int bn;
   double cost;  // column-work per SM, in columns of a 128-row tile
+  bool balanced = false;  // CTA-pair kernel in its K-balanced mode (needs the workspace)
 };
+
+// K-balanced mode: 256-wide pair tiles, the (tile, K block) units dealt out evenly, so the cost is the exact share
+// of one pair plus what the hand-over of one partial tile costs, expressed in K blocks.
+constexpr int kSkMinKBlocks = 128;
+constexpr double kSkHandOverBlocks = 8.0;
+constexpr int kSkMinTailBlocks = 24;
+constexpr double kSkMinGain = 0.95;  // taken when at least 5 % cheaper than the best whole-tile plan
+
+A8W8Plan plan_a8w8(int M, int N, int sms);
+
+A8W8Plan plan_a8w8(int M, int N, int K, int sms, int balanced_mode /* 0 auto, 1 always where possible, 2 never */) {
+  A8W8Plan best = plan_a8w8(M, N, sms);
+  const int kbs = (K + kBK - 1) / kBK;
+  if (M <= kBM || balanced_mode == 2 || kbs < (balanced_mode == 1 ? 2 : kSkMinKBlocks)) return best;
+  const int pairs = sms / 2;
+  const long long tiles = 1ll * ((M + 255) / 256) * ((N + 255) / 256);
+  if (tiles * kbs > INT32_MAX) return best;
+  const SkSplit split = sk_split(tiles, kbs, pairs);
+  if (!split.valid || (pairs - split.tiles) * split.slots > sk_max_slots(sms)) return best;
+  // short tails make pieces whose hand-over takes longer than their MMAs, short heads make tails that are cut into
+  // many pieces, and with less than one whole round nothing follows the heads to hide their longer epilogue behind:
+  // left to the forced mode
+  if (balanced_mode != 1 && (kbs - split.units < kSkMinTailBlocks || split.units * 3 < kbs || tiles < pairs)) return best;
+  const double blocks = double(tiles / pairs) * kbs + double(split.units) + kSkHandOverBlocks;
+  const double cost = blocks / kbs * 256.0;
+  if (balanced_mode == 1 || cost < best.cost * kSkMinGain) return A8W8Plan{true, 256, cost, true};
+  return best;
+}
 
 A8W8Plan plan_a8w8(int M, int N, int sms) {
   A8W8Plan best{false, 64, 1e30};
@@ -750,7 +1009,8 @@ A8W8Plan plan_a8w8(int M, int N, int sms) {
 }
 
 template <typename OutT>
-int dispatch(const int8_t* a, int64_t lda, const int8_t* b, int64_t ldb, const A8W8Params& p, cudaStream_t st) {
+int dispatch(const int8_t* a, int64_t lda, const int8_t* b, int64_t ldb, const A8W8Params& p, cudaStream_t st,
+             void* workspace, size_t workspace_bytes) {
   const bool tma_ok = p.K > 0 && (reinterpret_cast<uintptr_t>(a) % 16 == 0) && (reinterpret_cast<uintptr_t>(b) % 16 == 0) &&
                       (lda % 16 == 0) && (ldb % 16 == 0);
   if (!tma_ok) {
@@ -769,10 +1029,14 @@ int dispatch(const int8_t* a, int64_t lda, const int8_t* b, int64_t ldb, const A
                                  p.ldacc, st);
     if (r >= 0) return r;
   }
-  A8W8Plan plan = opt_test_stall_us() != 0 ? A8W8Plan{false, 64, 0.0} : plan_a8w8(p.M, p.N, sm_count());
+  // the K-balanced mode needs scratch: without it (or with a misaligned one) the best whole-tile plan runs instead
+  const bool ws_ok = workspace && workspace_bytes >= sk_workspace_bytes(sm_count()) && reinterpret_cast<uintptr_t>(workspace) % 256 == 0;
+  A8W8Plan plan = opt_test_stall_us() != 0 ? A8W8Plan{false, 64, 0.0}
+                                           : plan_a8w8(p.M, p.N, p.K, sm_count(), ws_ok ? opt_a8w8_balanced() : 2);
   if (const int forced = opt_a8w8_pair_tile()) {  // tuning hook: a given pair-tile width wherever the pair kernel can run
     if (p.M > kBM) plan = A8W8Plan{true, forced, 0.0};
   }
+  if (plan.balanced) return launch_pair<OutT, 256, true>(a, lda, b, ldb, p, st, workspace);
   if (plan.pair) {
     switch (plan.bn) {
       case 256: return launch_pair<OutT, 256>(a, lda, b, ldb, p, st);
@@ -904,7 +1168,12 @@ extern "C" int fnn_fused_moe_a8w8(const int8_t* a, int64_t lda, const int8_t* b,
   return dispatch_moe<__nv_bfloat16>(a_sorted, EM, b, E, p, st);
 }
 
-extern "C" size_t fnn_gemm_a8w8_workspace_bytes(int64_t, int64_t, int64_t) { return 0; }
+extern "C" size_t fnn_gemm_a8w8_workspace_bytes(int64_t M, int64_t N, int64_t K) {
+  using namespace fnn;
+  if (M <= 0 || N <= 0 || K <= 0 || M > INT32_MAX || N > INT32_MAX || K > INT32_MAX) return 0;
+  if (opt_test_stall_us() != 0 || opt_a8w8_pair_tile() != 0) return 0;
+  return plan_a8w8(int(M), int(N), int(K), sm_count(), opt_a8w8_balanced()).balanced ? sk_workspace_bytes(sm_count()) : 0;
+}
 
 extern "C" int fnn_gemm_a8w8_plan(int64_t M, int64_t N, int64_t K, int* kernel, int* tile_n) {
   using namespace fnn;
@@ -915,8 +1184,8 @@ extern "C" int fnn_gemm_a8w8_plan(int64_t M, int64_t N, int64_t K, int* kernel, 
     *tile_n = 16;
     return FNN_OK;
   }
-  const A8W8Plan plan = plan_a8w8(int(M), int(N), sm_count());
-  *kernel = plan.pair ? 1 : 0;
+  const A8W8Plan plan = plan_a8w8(int(M), int(N), int(K > INT32_MAX ? INT32_MAX : K), sm_count(), opt_a8w8_balanced());
+  *kernel = plan.balanced ? 3 : plan.pair ? 1 : 0;
   *tile_n = plan.bn;
   return FNN_OK;
 }
@@ -926,8 +1195,6 @@ extern "C" int fnn_gemm_a8w8(const int8_t* a, int64_t lda, const int8_t* b, int6
                              int64_t ldo, int64_t M, int64_t N, int64_t K, int32_t* acc_out, int64_t ldacc,
                              void* workspace, size_t workspace_bytes, void* stream) {
   using namespace fnn;
-  (void)workspace;
-  (void)workspace_bytes;
   if (M < 0 || N < 0 || K < 0 || lda < K || ldb < K || ldo < N || (acc_out && ldacc < N))
     return fail(FNN_ERR_SHAPE, "gemm_a8w8: M=%lld N=%lld K=%lld lda=%lld ldb=%lld ldo=%lld", (long long)M,
                 (long long)N, (long long)K, (long long)lda, (long long)ldb, (long long)ldo);
@@ -944,6 +1211,6 @@ extern "C" int fnn_gemm_a8w8(const int8_t* a, int64_t lda, const int8_t* b, int6
   p.status = device_status_word();
   p.wait_ns = kWaitLimitNs; p.skip_kb = -1;
   cudaStream_t st = static_cast<cudaStream_t>(stream);
-  if (out_dtype == FNN_F16) return dispatch<__half>(a, lda, b, ldb, p, st);
-  return dispatch<__nv_bfloat16>(a, lda, b, ldb, p, st);
+  if (out_dtype == FNN_F16) return dispatch<__half>(a, lda, b, ldb, p, st, workspace, workspace_bytes);
+  return dispatch<__nv_bfloat16>(a, lda, b, ldb, p, st, workspace, workspace_bytes);
 }

@@ -68,11 +68,19 @@ typedef enum fnn_dtype {
  * FNN_OPT_A8W8_PAIR_TILE (default 0 = chosen from the problem shape; a tuning hook).  128, 160, 192, 224 or 256 forces
  * that output-tile width in fnn_gemm_a8w8 wherever the CTA-pair tensor-core kernel can run (more than 128 rows).  The
  * shape-to-tile table in the library was measured with it; results do not depend on the tile.
+ *
+ * FNN_OPT_A8W8_BALANCED (default 0).  The CTA-pair kernel of fnn_gemm_a8w8 has a K-balanced mode for shapes whose
+ * 256 x 256 tiles do not fill the last round of CTA pairs (for instance 64 tiles on 74 pairs): the (tile, K block)
+ * units are dealt out evenly, a pair that stops inside a tile leaves its int32 partial sums in the workspace and the
+ * pair that finishes the tile adds them (int32 additions: the accumulator stays exact whatever the order).  0 = used
+ * where the shape table expects at least 3 % from it and the caller passed the workspace, 1 = wherever it can run
+ * (more than 128 rows, a workspace; for tests), 2 = never.
  */
 typedef enum fnn_option {
   FNN_OPT_STATIC_WEIGHTS = 1,
   FNN_OPT_TEST_STALL_US = 2,
-  FNN_OPT_A8W8_PAIR_TILE = 3
+  FNN_OPT_A8W8_PAIR_TILE = 3,
+  FNN_OPT_A8W8_BALANCED = 4
 } fnn_option;
 
 /* Sets an option; FNN_ERR_UNSUPPORTED for an unknown one.  fnn_get_option returns the value, or -1 if unknown. */
@@ -132,7 +140,11 @@ int fnn_dynamic_quant(const void* x, int x_dtype, int64_t M, int64_t K, int64_t 
  *   acc_out    optional [M, N] int32 (ldacc): when not NULL the raw accumulator is
  *              written there as well (parity checks)
  *   workspace  scratch of at least fnn_gemm_a8w8_workspace_bytes(M, N, K) bytes,
- *              256-byte aligned; may be NULL when that function returns 0
+ *              256-byte aligned; may be NULL when that function returns 0.  Only the
+ *              K-balanced mode of the CTA-pair kernel uses it (FNN_OPT_A8W8_BALANCED); when it
+ *              is missing or too small that mode is not used and the result is the same.
+ *              Its contents need no initialisation and mean nothing afterwards; two calls
+ *              that may run at the same time (different streams) need different workspaces.
  *
  * Fast path (TMA + tcgen05): a, b 16-byte aligned and lda, ldb multiples of 16.
  * Anything else runs a slower generic kernel with the same results.
@@ -149,7 +161,8 @@ size_t fnn_gemm_a8w8_workspace_bytes(int64_t M, int64_t N, int64_t K);
 /*
  * Which kernel and output-tile width fnn_gemm_a8w8 picks for a problem with 16-byte-aligned operands on the current
  * device (148 SMs are assumed when there is none): *kernel = 0 single-CTA tensor-core kernel (tile 128 x *tile_n),
- * 1 CTA-pair tensor-core kernel (tile 256 x *tile_n), 2 the streaming decode kernel (16 output channels per step).
+ * 1 CTA-pair tensor-core kernel (tile 256 x *tile_n), 2 the streaming decode kernel (16 output channels per step),
+ * 3 the CTA-pair kernel in its K-balanced mode (taken only when the call passes the workspace).
  * This is the shape -> configuration table that takes the place of the reference's autotune cache
  * (flashnn/triton_kernels/triton_utils.py:84-151); its constants are measured (flashnn_b200/csrc/a8w8_plan.h).
  * Needs no GPU.

@@ -69,7 +69,11 @@ def test_gemm_a8w8_argument_errors(lib):
     assert call(lda=32) == 3                # lda < K
     assert call(ldo=8) == 3                 # ldo < N
     assert call(M=0) == 0 and call(N=0) == 0
-    assert lib.fnn_gemm_a8w8_workspace_bytes(4096, 4096, 4096) == 0
+    # scratch only where the K-balanced mode of the CTA-pair kernel is planned: 8192^3 fills its rounds of CTA pairs,
+    # 4096 x 2048 x 28672 (128 tiles on 74 pairs) does not; 16 KB of flags and two 256 x 256 int32 slots per pair of the 148 SMs
+    assert lib.fnn_gemm_a8w8_workspace_bytes(8192, 8192, 8192) == 0
+    assert lib.fnn_gemm_a8w8_workspace_bytes(16, 4096, 4096) == 0
+    assert lib.fnn_gemm_a8w8_workspace_bytes(4096, 2048, 28672) == 16384 + 148 * 256 * 256 * 4
 
 
 def test_gemm_weight_only_argument_errors(lib):

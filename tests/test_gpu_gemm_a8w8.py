@@ -163,3 +163,74 @@ def test_decode_streaming_kernel_exact(m, n, k, out_ty):
     b2[1::2] = 127
     out, acc = run(a2, b2, row.float(), col.float(), out_ty)
     assert torch.equal(acc, O.gemm_a8w8_acc_i32(a2, b2))
+
+
+# ---- the CTA-pair kernel with its K blocks dealt out evenly (partial sums handed from pair to pair) ----
+@pytest.fixture
+def balanced_mode():
+    from flashnn_b200 import _lib
+    _lib.set_option(_lib.OPT_A8W8_BALANCED, 1)
+    yield
+    _lib.set_option(_lib.OPT_A8W8_BALANCED, 0)
+
+
+# fewer tiles than pairs (every tile split over several pairs), a few more tiles than pairs, ragged M / N / K, short K
+# (units per pair below and above the K blocks of a tile), the narrow-shard shape of the down projection
+@pytest.mark.parametrize("m,n,k", [(256, 512, 4096), (300, 1000, 8896), (1000, 264, 7392), (2500, 2100, 1040),
+                                   (2049, 2560, 400), (4096, 1024, 7168), (1290, 4200, 2064), (129, 64, 256)])
+@pytest.mark.parametrize("out_ty", [torch.float16, torch.bfloat16])
+def test_balanced_mode_exact(balanced_mode, m, n, k, out_ty):
+    from flashnn_b200 import _lib
+    assert _lib.a8w8_plan(m, n, k)[0] == 3
+    a, b, row, col = make(m, n, k, seed=m + n + k + 1, lo=-128)
+    ref_acc = O.gemm_a8w8_acc_i32(a, b)
+    want = bits16(O.gemm_a8w8_from_acc(ref_acc, row, col, out_ty))
+    for _ in range(3):  # the hand-over flags are reused call after call
+        out, acc = run(a, b, row, col, out_ty)
+        assert torch.equal(acc, ref_acc)
+        assert torch.equal(bits16(out), want)
+
+
+def test_balanced_mode_replayed_from_a_cuda_graph(balanced_mode):
+    import flashnn_b200
+    m, n, k = 1024, 1024, 4096
+    a, b, row, col = make(m, n, k, seed=5)
+    want = bits16(O.gemm_a8w8(a, b, row, col, torch.bfloat16))
+    op = flashnn_b200.GemmA8W8(torch.bfloat16)
+    a, b, row, col = a.cuda(), b.cuda(), row.cuda(), col.cuda()
+    op(a, b, row, col)  # first call outside the capture (workspace allocation)
+    s = torch.cuda.Stream()
+    s.wait_stream(torch.cuda.current_stream())
+    with torch.cuda.stream(s):
+        op(a, b, row, col)
+        g = torch.cuda.CUDAGraph()
+        with torch.cuda.graph(g, stream=s):
+            out = op(a, b, row, col)
+    for _ in range(3):
+        out.zero_()
+        g.replay()
+        torch.cuda.synchronize()
+        assert torch.equal(bits16(out.cpu()), want)
+    from flashnn_b200 import _lib
+    assert _lib.device_status() == 0
+
+
+def test_balanced_mode_is_picked_for_narrow_shards_and_matches():
+    """Down projection of the 70B FFN on 1/4 of the columns: 128 tiles for 74 CTA pairs."""
+    from flashnn_b200 import _lib
+    m, n, k = 4096, 2048, 28672
+    assert _lib.a8w8_plan(m, n, k)[0] == 3
+    assert _lib.a8w8_plan(m, 8192, 8192)[0] == 1  # full waves: whole tiles
+    a, b, row, col = make(m, n, k, seed=9)
+    out, acc = run(a, b, row, col, torch.bfloat16)
+    rows = [0, 1, 127, 128, 255, 256, 1000, 2047, 2048, 4095]
+    ref_acc = O.gemm_a8w8_acc_i32(a[rows], b)
+    assert torch.equal(acc[rows], ref_acc)
+    assert torch.equal(bits16(out[rows]), bits16(O.gemm_a8w8_from_acc(ref_acc, row[rows], col, torch.bfloat16)))
+    # the whole accumulator against the same kernel without the hand-over
+    _lib.set_option(_lib.OPT_A8W8_BALANCED, 2)
+    try:
+        out2, acc2 = run(a, b, row, col, torch.bfloat16)
+    finally:
+        _lib.set_option(_lib.OPT_A8W8_BALANCED, 0)
+    assert torch.equal(acc, acc2) and torch.equal(bits16(out), bits16(out2))

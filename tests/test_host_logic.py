@@ -103,7 +103,15 @@ def test_a8w8_shape_to_tile_plan():
     assert _lib.a8w8_plan(4096, 57344, 8192) == (1, 256)
     assert _lib.a8w8_plan(4096, 7168, 8192) == (1, 224)     # 512 tiles = 6.92 waves instead of 448 = 6.05 -> 7
     assert _lib.a8w8_plan(4096, 1024, 28672) == (1, 256)    # 64 pair tiles in one wave, not 256 single-CTA tiles
-    assert _lib.a8w8_plan(764, 8192, 8192) == (1, 192)
+    assert _lib.a8w8_plan(4096, 2048, 28672) == (3, 256)    # 128 tiles = 1.73 rounds: the ragged round's K blocks are shared
+    assert _lib.a8w8_plan(4096, 4096, 28672) == (3, 256)    # 256 tiles = 3.46 rounds
+    assert _lib.a8w8_plan(764, 8192, 8192) == (1, 192)      # the hand-over would cost what the even split gains
+    assert _lib.a8w8_plan(4096, 4096, 4096)[0] == 1         # short K: the extra epilogues would not hide behind the MMAs
+    _lib.set_option(_lib.OPT_A8W8_BALANCED, 2)
+    try:
+        assert _lib.a8w8_plan(4096, 2048, 28672) == (1, 256)  # whole tiles: two rounds
+    finally:
+        _lib.set_option(_lib.OPT_A8W8_BALANCED, 0)
     assert _lib.a8w8_plan(256, 512, 4096) == (0, 64)        # too small for the pair kernel to fill the GPU
     assert _lib.a8w8_plan(64, 57344, 8192) == (0, 256)      # decode: the widest tile that still gives every SM work
     assert _lib.a8w8_plan(16, 4096, 4096) == (0, 64)
