@@ -31,7 +31,8 @@ namespace {
 constexpr int kTM = 128;        // tokens per CTA tile (256 per pair)
 constexpr int kTN = 256;        // channels per pair tile (128 converted per CTA)
 constexpr int kTK = 64;         // K per stage: 128 bytes of 16-bit operand
-constexpr int kPfThreads = 320; // 10 warps
+constexpr int kPfConvWarps = 8;   // converter warps of the per-channel kernel
+constexpr int kPfThreads = (6 + kPfConvWarps) * 32;  // TMA, MMA, four epilogue warps, the converters
 constexpr int kPfStages = 5;      // TMA ring: activations + raw weight bytes
 constexpr int kPfConvStages = 5;  // ring of converted weight tiles
 constexpr int kPfGroupM = 16;
@@ -161,14 +162,14 @@ __device__ __forceinline__ PfBars pf_bars(uint64_t* bars) {
 }
 
 // Thread 0 of each CTA: barrier counts.  `epi_arrivals` = epilogue warps of both CTAs that free an accumulator.
-__device__ __forceinline__ void pf_init_bars(const PfBars& b, int epi_arrivals, bool grp) {
+__device__ __forceinline__ void pf_init_bars(const PfBars& b, int epi_arrivals, bool grp, int conv_warps = 4) {
   for (int s = 0; s < kPfStages; ++s) {
     mbar_init(&b.raw_full[s], 1);
     mbar_init(&b.empty[s], 1);
   }
   for (int s = 0; s < kPfConvStages; ++s) {
-    mbar_init(&b.conv_full[s], 5);  // leader: its 4 converter warps + the peer's relay
-    mbar_init(&b.conv_done[s], 4);
+    mbar_init(&b.conv_full[s], conv_warps + 1);  // leader: its converter warps + the peer's relay
+    mbar_init(&b.conv_done[s], conv_warps);
     mbar_init(&b.conv_empty[s], 1);
   }
   for (int i = 0; i < 2; ++i) {
@@ -308,9 +309,9 @@ __device__ __forceinline__ void pf_relay(const PfBars& b, const PfParams& p, int
   }
 }
 
-// four converter warps of both CTAs (ct = 0..127): raw bytes of a K block -> exact 16-bit integers in the K-major
-// 128-byte-swizzled operand tile
-template <typename T, int BITS, int BN = kTN>
+// converter warps of both CTAs (CT threads, ct = 0..CT-1): raw bytes of a K block -> exact 16-bit integers in the
+// K-major 128-byte-swizzled operand tile
+template <typename T, int BITS, int BN = kTN, int CT = 128>
 __device__ __forceinline__ void pf_converters(uint8_t* smem, const PfBars& b, const PfParams& p, uint32_t rank, int pair_id,
                                               int num_pairs, int ct, volatile int* abort_flag) {
   using L = PfSmem<BITS>;
@@ -333,8 +334,8 @@ __device__ __forceinline__ void pf_converters(uint8_t* smem, const PfBars& b, co
       if (BITS == 8) {
         // 128 rows x 4 chunks of 16 bytes; chunk id -> (row = id / 4, c = id % 4): 16 k -> 32 bytes out
 #pragma unroll
-        for (int i = 0; i < 4; ++i) {
-          const int id = ct + i * 128;
+        for (int i = 0; i < 512 / CT; ++i) {
+          const int id = ct + i * CT;
           const uint32_t row = id >> 2, c = id & 3;
           if (BN < kTN && row >= BN / 2) continue;  // a narrower tile brings fewer weight rows
           const uint4 w = *reinterpret_cast<const uint4*>(raw + id * 16);
@@ -349,8 +350,8 @@ __device__ __forceinline__ void pf_converters(uint8_t* smem, const PfBars& b, co
       } else {
         // 64 packed rows x 4 chunks; packed row j carries channel rows 2j (low nibbles) and 2j+1 (high)
 #pragma unroll
-        for (int i = 0; i < 2; ++i) {
-          const int id = ct + i * 128;
+        for (int i = 0; i < 256 / CT; ++i) {
+          const int id = ct + i * CT;
           const uint32_t prow = id >> 2, c = id & 3;
           if (BN < kTN && prow >= BN / 4) continue;
           const uint4 w = *reinterpret_cast<const uint4*>(raw + id * 16);
@@ -375,7 +376,7 @@ __device__ __forceinline__ void pf_converters(uint8_t* smem, const PfBars& b, co
 }
 
 // ---------------------------------------------------------------------------------------------------------
-// Per-channel scales: ten warps (TMA, MMA, four epilogue, four converters); the accumulator of a tile is read
+// Per-channel scales: fourteen warps (TMA, MMA, four epilogue, eight converters); the accumulator of a tile is read
 // once, out = acc * s[n] - xsum[m] * s[n] zp[n] + bias[n].
 // ---------------------------------------------------------------------------------------------------------
 // BN: channels per pair tile (256, or narrower where that fills the last wave better; the shared-memory and TMEM
@@ -402,7 +403,7 @@ wo_umma_pair_kernel(const __grid_constant__ CUtensorMap tmap_x, const __grid_con
 
   if (threadIdx.x == 0) {
     *abort_flag = 0;
-    pf_init_bars(b, 8, false);
+    pf_init_bars(b, 8, false, kPfConvWarps);
     tma_prefetch_desc(&tmap_x);
     tma_prefetch_desc(&tmap_w);
   }
@@ -486,7 +487,7 @@ wo_umma_pair_kernel(const __grid_constant__ CUtensorMap tmap_x, const __grid_con
       if (lane == 0) mbar_arrive_cluster(map_to_cta(smem_u32(&b.tmem_empty[buf]), 0));
     }
   } else {
-    pf_converters<T, BITS, BN>(smem, b, p, rank, pair_id, num_pairs, threadIdx.x - 6 * 32, abort_flag);
+    pf_converters<T, BITS, BN, kPfConvWarps * 32>(smem, b, p, rank, pair_id, num_pairs, threadIdx.x - 6 * 32, abort_flag);
   }
 
   // -------------------------------- teardown --------------------------------
