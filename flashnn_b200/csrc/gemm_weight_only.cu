@@ -31,8 +31,13 @@ namespace {
 constexpr int kTM = 128;        // tokens per CTA tile (256 per pair)
 constexpr int kTN = 256;        // channels per pair tile (128 converted per CTA)
 constexpr int kTK = 64;         // K per stage: 128 bytes of 16-bit operand
-constexpr int kPfConvWarps = 8;   // converter warps of the per-channel kernel
-constexpr int kPfThreads = (6 + kPfConvWarps) * 32;  // TMA, MMA, four epilogue warps, the converters
+// Per-channel kernel: warps 0-3 TMA, MMA and two idle ones; 4-7 epilogue; 8-15 converters.  Whole warpgroups, so that
+// each role sizes its registers with setmaxnreg (40 / 200 / 72).  Eight converter warps: with four, a device-side
+// timeline showed them, not the MMAs, setting the pace (0.51 us per K block against 0.34 us); twelve or sixteen are
+// no faster than eight.
+constexpr int kPfConvWarps = 8;
+constexpr int kPfThreads = (8 + kPfConvWarps) * 32;
+constexpr int kPfConvRegs = 72;
 constexpr int kPfStages = 5;      // TMA ring: activations + raw weight bytes
 constexpr int kPfConvStages = 5;  // ring of converted weight tiles
 constexpr int kPfGroupM = 16;
@@ -334,8 +339,7 @@ __device__ __forceinline__ void pf_converters(uint8_t* smem, const PfBars& b, co
       if (BITS == 8) {
         // 128 rows x 4 chunks of 16 bytes; chunk id -> (row = id / 4, c = id % 4): 16 k -> 32 bytes out
 #pragma unroll
-        for (int i = 0; i < 512 / CT; ++i) {
-          const int id = ct + i * CT;
+        for (int id = ct; id < 512; id += CT) {
           const uint32_t row = id >> 2, c = id & 3;
           if (BN < kTN && row >= BN / 2) continue;  // a narrower tile brings fewer weight rows
           const uint4 w = *reinterpret_cast<const uint4*>(raw + id * 16);
@@ -350,8 +354,7 @@ __device__ __forceinline__ void pf_converters(uint8_t* smem, const PfBars& b, co
       } else {
         // 64 packed rows x 4 chunks; packed row j carries channel rows 2j (low nibbles) and 2j+1 (high)
 #pragma unroll
-        for (int i = 0; i < 256 / CT; ++i) {
-          const int id = ct + i * CT;
+        for (int id = ct; id < 256; id += CT) {
           const uint32_t prow = id >> 2, c = id & 3;
           if (BN < kTN && prow >= BN / 4) continue;
           const uint4 w = *reinterpret_cast<const uint4*>(raw + id * 16);
@@ -376,7 +379,7 @@ __device__ __forceinline__ void pf_converters(uint8_t* smem, const PfBars& b, co
 }
 
 // ---------------------------------------------------------------------------------------------------------
-// Per-channel scales: fourteen warps (TMA, MMA, four epilogue, eight converters); the accumulator of a tile is read
+// Per-channel scales: sixteen warps (TMA, MMA, two idle, four epilogue, eight converters); the accumulator of a tile is read
 // once, out = acc * s[n] - xsum[m] * s[n] zp[n] + bias[n].
 // ---------------------------------------------------------------------------------------------------------
 // BN: channels per pair tile (256, or narrower where that fills the last wave better; the shared-memory and TMEM
@@ -417,12 +420,16 @@ wo_umma_pair_kernel(const __grid_constant__ CUtensorMap tmap_x, const __grid_con
   tc_fence_after();
   const uint32_t tmem_base = *tmem_slot;
 
-  if (warp == 0) {
-    pf_producer<BITS, BN>(smem, b, &tmap_x, &tmap_w, p, rank, pair_id, num_pairs, abort_flag);
-  } else if (warp == 1) {
-    if (rank == 0) pf_mma<T, BITS, BN>(smem, b, p, tmem_base, pair_id, num_pairs, p.k_blocks, abort_flag);
-    else pf_relay(b, p, pair_id, num_pairs, abort_flag);
-  } else if (warp < 6) {
+  if (warp < 4) {
+    asm volatile("setmaxnreg.dec.sync.aligned.u32 40;");
+    if (warp == 0) {
+      pf_producer<BITS, BN>(smem, b, &tmap_x, &tmap_w, p, rank, pair_id, num_pairs, abort_flag);
+    } else if (warp == 1) {
+      if (rank == 0) pf_mma<T, BITS, BN>(smem, b, p, tmem_base, pair_id, num_pairs, p.k_blocks, abort_flag);
+      else pf_relay(b, p, pair_id, num_pairs, abort_flag);
+    }
+  } else if (warp < 8) {
+    asm volatile("setmaxnreg.inc.sync.aligned.u32 200;");
     // -------------------------------- epilogue (both CTAs) --------------------------------
     const int quarter = warp & 3;
     float* cs = vec_smem + quarter * 3 * kTN;  // scale, scale*zp, bias of this tile's channels (private copy)
@@ -487,7 +494,8 @@ wo_umma_pair_kernel(const __grid_constant__ CUtensorMap tmap_x, const __grid_con
       if (lane == 0) mbar_arrive_cluster(map_to_cta(smem_u32(&b.tmem_empty[buf]), 0));
     }
   } else {
-    pf_converters<T, BITS, BN, kPfConvWarps * 32>(smem, b, p, rank, pair_id, num_pairs, threadIdx.x - 6 * 32, abort_flag);
+    asm volatile("setmaxnreg.dec.sync.aligned.u32 %0;" ::"n"(kPfConvRegs));
+    pf_converters<T, BITS, BN, kPfConvWarps * 32>(smem, b, p, rank, pair_id, num_pairs, threadIdx.x - 8 * 32, abort_flag);
   }
 
   // -------------------------------- teardown --------------------------------
