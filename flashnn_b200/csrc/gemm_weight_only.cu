@@ -41,6 +41,7 @@ constexpr int kPfConvRegs = 72;
 constexpr int kPfStages = 5;      // TMA ring: activations + raw weight bytes
 constexpr int kPfConvStages = 5;  // ring of converted weight tiles
 constexpr int kPfGroupM = 16;
+constexpr int kPgScaleStages = 4;  // group-wise kernel: scale groups staged ahead of the epilogue
 
 struct PfParams {
   const void* scale;  // [N], or [K / group, N] for group-wise scales
@@ -62,9 +63,9 @@ template <int BITS> struct PfSmem {
   static constexpr int kWBytes = (kTN / 2) * kTK * 2;                                // 16 KB converted weights
   static constexpr int kStageBytes = kXBytes + kRawBytes;                            // one TMA stage
   static constexpr int kConvOff = kPfStages * kStageBytes;                           // converted-tile ring
-  static constexpr int kVecOff = kConvOff + kPfConvStages * kWBytes;                 // [4 warps][3][kTN] float (group-wise kernel: [3][2][kTN])
+  static constexpr int kVecOff = kConvOff + kPfConvStages * kWBytes;                 // [4 warps][3][kTN] float (group-wise kernel: scale ring [2][kPgScaleStages][kTN] + bias [2][kTN])
   static constexpr int kBarOff = kVecOff + 4 * 3 * kTN * 4;
-  static constexpr int kNumBars = 2 * kPfStages + 3 * kPfConvStages + 4 + 1 + 4;
+  static constexpr int kNumBars = 2 * kPfStages + 3 * kPfConvStages + 4 + 1 + 2 * kPgScaleStages;
   static constexpr int kTmemSlotOff = kBarOff + kNumBars * 8;
   static constexpr int kAbortOff = kTmemSlotOff + 8;
   static constexpr int kTotal = kAbortOff + 8;
@@ -147,10 +148,10 @@ __device__ __forceinline__ uint32_t sw128(uint32_t row, uint32_t kc) { return ro
 // ---------------------------------------------------------------------------------------------------------
 // Roles shared by the per-channel kernel and the group-wise kernel.  `bars` layout: raw_full[S], empty[S],
 // conv_full[C], conv_empty[C], conv_done[C], tmem_full[2], tmem_empty[2], drain, then (group-wise kernel only)
-// scale_full[2][2].
+// scale_full[kPgScaleStages], scale_empty[kPgScaleStages].
 // ---------------------------------------------------------------------------------------------------------
 struct PfBars {
-  uint64_t *raw_full, *empty, *conv_full, *conv_empty, *conv_done, *tmem_full, *tmem_empty, *drain, *scale_full;
+  uint64_t *raw_full, *empty, *conv_full, *conv_empty, *conv_done, *tmem_full, *tmem_empty, *drain, *scale_full, *scale_empty;
 };
 __device__ __forceinline__ PfBars pf_bars(uint64_t* bars) {
   PfBars b;
@@ -163,6 +164,7 @@ __device__ __forceinline__ PfBars pf_bars(uint64_t* bars) {
   b.tmem_empty = b.tmem_full + 2;
   b.drain = b.tmem_full + 4;
   b.scale_full = b.tmem_full + 5;
+  b.scale_empty = b.scale_full + kPgScaleStages;
   return b;
 }
 
@@ -183,7 +185,10 @@ __device__ __forceinline__ void pf_init_bars(const PfBars& b, int epi_arrivals, 
   }
   mbar_init(b.drain, 1);
   if (grp)
-    for (int i = 0; i < 4; ++i) mbar_init(&b.scale_full[i], 4);  // the four epilogue warps of one column half
+    for (int i = 0; i < kPgScaleStages; ++i) {
+      mbar_init(&b.scale_full[i], 2);   // the two staging warps, one per column half
+      mbar_init(&b.scale_empty[i], 8);  // the eight epilogue warps
+    }
   mbar_fence_init();
 }
 
@@ -579,6 +584,47 @@ wo_umma_pair_group_kernel(const __grid_constant__ CUtensorMap tmap_x, const __gr
     } else if (warp == 1) {
       if (rank == 0) pf_mma<T, BITS>(smem, b, p, tmem_base, pair_id, num_pairs, kb_per_group, abort_flag);
       else pf_relay(b, p, pair_id, num_pairs, abort_flag);
+    } else {
+      // ---- warps 2 and 3: stage the scales (and scale * zero-point, and with a tile's first group its bias) of the
+      // coming groups as fp32 in a ring of kPgScaleStages slots, one column half each, four columns per lane, so that
+      // the epilogue warps find them ready
+      const int half = warp - 2;
+      const int c0 = half * 128 + lane * 4;
+      float* sS = vec_smem;
+      float* sZ = sS + kPgScaleStages * kTN;
+      float* sB = sZ + kPgScaleStages * kTN;
+      const int groups = p.K / p.group;
+      int seg = 0;
+      bool ok = true;
+      for (int t = pair_id; t < num_tiles && ok; t += num_pairs) {
+        int mb, nb;
+        pf_tile_coords(t, p.tiles_m, p.tiles_n, mb, nb);
+        const int n0 = nb * kTN + c0;
+        for (int g = 0; g < groups; ++g, ++seg) {
+          const int slot = seg % kPgScaleStages;
+          const uint32_t ph = (seg / kPgScaleStages) & 1;
+          float sv[4], zv[4], bv[4];
+#pragma unroll
+          for (int j = 0; j < 4; ++j) {
+            const bool in = n0 + j < p.N;
+            const int64_t at = int64_t(g) * p.N + n0 + j;
+            sv[j] = in ? load_as_f32(p.scale, p.scale_dtype, at) : 0.f;
+            zv[j] = (HAS_ZP && in) ? sv[j] * load_as_f32(p.zp, p.scale_dtype, at) : 0.f;
+            bv[j] = (g == 0 && p.bias && in) ? load_as_f32(p.bias, p.bias_dtype, n0 + j) : 0.f;
+          }
+          ok = mbar_wait_bounded(&b.scale_empty[slot], ph ^ 1, abort_flag);
+          ok = __all_sync(0xffffffffu, ok);
+          if (!ok) {
+            if (lane == 0) pf_report(p.status, abort_flag, DEV_TIMEOUT_PRODUCER);
+            break;
+          }
+          *reinterpret_cast<float4*>(sS + slot * kTN + c0) = make_float4(sv[0], sv[1], sv[2], sv[3]);
+          if (HAS_ZP) *reinterpret_cast<float4*>(sZ + slot * kTN + c0) = make_float4(zv[0], zv[1], zv[2], zv[3]);
+          if (g == 0) *reinterpret_cast<float4*>(sB + slot * kTN + c0) = make_float4(bv[0], bv[1], bv[2], bv[3]);
+          __syncwarp();
+          if (lane == 0) mbar_arrive(&b.scale_full[slot]);
+        }
+      }
     }
   } else if (warp < 8) {
     asm volatile("setmaxnreg.dec.sync.aligned.u32 56;");
@@ -586,67 +632,51 @@ wo_umma_pair_group_kernel(const __grid_constant__ CUtensorMap tmap_x, const __gr
   } else {
     asm volatile("setmaxnreg.inc.sync.aligned.u32 208;");
     // -------------------------------- epilogue (both CTAs) --------------------------------
-    const int e = threadIdx.x - 8 * 32;  // 0..255: the tile column whose scale, zero-point and bias this thread stages
     const int quarter = warp & 3;
     const int half = (warp - 8) >> 2;
-    float* sS = vec_smem;            // [2][kTN] scale of the group in flight
-    float* sZ = sS + 2 * kTN;        // [2][kTN] scale * zero-point
-    float* sB = sZ + 2 * kTN;        // [2][kTN] bias, by tile parity
+    const float* sS = vec_smem;                       // [kPgScaleStages][kTN] scale of a group
+    const float* sZ = sS + kPgScaleStages * kTN;      // scale * zero-point
+    const float* sB = sZ + kPgScaleStages * kTN;      // bias, valid in the slot of a tile's first group
     T* out = reinterpret_cast<T*>(p.out);
     const bool vec_ok = (p.ldo % 8 == 0) && (reinterpret_cast<uintptr_t>(out) % 16 == 0);
     const int groups = p.K / p.group;
     uint64_t sum2[64];
 #pragma unroll
     for (int i = 0; i < 64; ++i) sum2[i] = 0ull;
-    // scale (and scale * zero-point) of column e for (tile column block nb, group g)
-    auto load_scale = [&](int nb, int g, float& s, float& z) {
-      const int ch = nb * kTN + e;
-      const bool in = ch < p.N;
-      const int64_t at = int64_t(g) * p.N + ch;
-      s = in ? load_as_f32(p.scale, p.scale_dtype, at) : 0.f;
-      z = (HAS_ZP && in) ? s * load_as_f32(p.zp, p.scale_dtype, at) : 0.f;
-    };
-    float ps = 0.f, pz = 0.f;  // prefetched for the segment about to start
-    if (pair_id < num_tiles) {
-      int mb0, nb0;
-      pf_tile_coords(pair_id, p.tiles_m, p.tiles_n, mb0, nb0);
-      load_scale(nb0, 0, ps, pz);
-    }
     int seg = 0, local = 0;
     bool ok = true;
     for (int t = pair_id; t < num_tiles && ok; t += num_pairs, ++local) {
       int mb, nb;
       pf_tile_coords(t, p.tiles_m, p.tiles_n, mb, nb);
-      int nb_next = -1;
-      if (t + num_pairs < num_tiles) {
-        int mbn;
-        pf_tile_coords(t + num_pairs, p.tiles_m, p.tiles_n, mbn, nb_next);
-      }
       const int row = mb * 256 + int(rank) * kTM + quarter * 32 + lane;
       const int n0 = nb * kTN;
-      sB[(local & 1) * kTN + e] = (p.bias && n0 + e < p.N) ? load_as_f32(p.bias, p.bias_dtype, n0 + e) : 0.f;
       for (int g = 0; g < groups; ++g, ++seg) {
         const int buf = seg & 1;
         const uint32_t seg_phase = (seg >> 1) & 1;
-        sS[buf * kTN + e] = ps;
-        if (HAS_ZP) sZ[buf * kTN + e] = pz;
-        __syncwarp();
-        if (lane == 0) mbar_arrive(&b.scale_full[buf * 2 + half]);
-        if (g + 1 < groups) load_scale(nb, g + 1, ps, pz);
-        else if (nb_next >= 0) load_scale(nb_next, 0, ps, pz);
+        const int slot = seg % kPgScaleStages;
+        const uint32_t slot_phase = (seg / kPgScaleStages) & 1;
         float nxg = 0.f;
         if (HAS_ZP && row < p.M) nxg = -p.xsum[int64_t(g) * p.M + row];
-        ok = mbar_wait_bounded(&b.scale_full[buf * 2 + half], seg_phase, abort_flag) &&
+        ok = mbar_wait_bounded(&b.scale_full[slot], slot_phase, abort_flag) &&
              mbar_wait_bounded(&b.tmem_full[buf], seg_phase, abort_flag);
         ok = __all_sync(0xffffffffu, ok);
         if (!ok) {
           if (lane == 0) pf_report(p.status, abort_flag, DEV_TIMEOUT_EPILOGUE);
           break;
         }
+        if (g == 0) {  // the sums of a tile start from its bias (they were left at zero)
+          const float4* b4 = reinterpret_cast<const float4*>(sB + slot * kTN + half * 128);
+#pragma unroll
+          for (int i = 0; i < 32; ++i) {
+            const float4 bv = b4[i];
+            asm("mov.b64 %0, {%1, %2};" : "=l"(sum2[2 * i]) : "f"(bv.x), "f"(bv.y));
+            asm("mov.b64 %0, {%1, %2};" : "=l"(sum2[2 * i + 1]) : "f"(bv.z), "f"(bv.w));
+          }
+        }
         tc_fence_after();
         const uint32_t taddr = tmem_base + (uint32_t(quarter * 32) << 16) + buf * kTN + half * 128;
-        const float4* s4 = reinterpret_cast<const float4*>(sS + buf * kTN + half * 128);
-        const float4* z4 = reinterpret_cast<const float4*>(sZ + buf * kTN + half * 128);
+        const float4* s4 = reinterpret_cast<const float4*>(sS + slot * kTN + half * 128);
+        const float4* z4 = reinterpret_cast<const float4*>(sZ + slot * kTN + half * 128);
 #pragma unroll
         for (int c = 0; c < 4; ++c) {
           uint32_t r[32];
@@ -667,11 +697,13 @@ wo_umma_pair_group_kernel(const __grid_constant__ CUtensorMap tmap_x, const __gr
         }
         tc_fence_before();
         __syncwarp();
-        if (lane == 0) mbar_arrive_cluster(map_to_cta(smem_u32(&b.tmem_empty[buf]), 0));
+        if (lane == 0) {
+          mbar_arrive_cluster(map_to_cta(smem_u32(&b.tmem_empty[buf]), 0));
+          mbar_arrive(&b.scale_empty[slot]);
+        }
       }
       if (!ok) break;
-      // the tile's sums are complete: add the bias, round once, store, and clear the sums for the next tile
-      const float* cb = sB + (local & 1) * kTN + half * 128;
+      // the tile's sums are complete: round once, store, and clear the sums for the next tile
       T* orow0 = out + int64_t(row) * p.ldo + n0 + half * 128;
 #pragma unroll
       for (int c = 0; c < 4; ++c) {
@@ -679,8 +711,6 @@ wo_umma_pair_group_kernel(const __grid_constant__ CUtensorMap tmap_x, const __gr
 #pragma unroll
         for (int j = 0; j < 32; j += 2) {
           unpack2(sum2[(c * 32 + j) >> 1], v[j], v[j + 1]);
-          v[j] += cb[c * 32 + j];
-          v[j + 1] += cb[c * 32 + j + 1];
           sum2[(c * 32 + j) >> 1] = 0ull;
         }
         const int col0 = n0 + half * 128 + c * 32;
