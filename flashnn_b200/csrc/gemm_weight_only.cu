@@ -65,7 +65,7 @@ template <int BITS> struct PfSmem {
   static constexpr int kConvOff = kPfStages * kStageBytes;                           // converted-tile ring
   static constexpr int kVecOff = kConvOff + kPfConvStages * kWBytes;                 // [4 warps][3][kTN] float (group-wise kernel: scale ring [2][kPgScaleStages][kTN] + bias [2][kTN])
   static constexpr int kBarOff = kVecOff + 4 * 3 * kTN * 4;
-  static constexpr int kNumBars = 2 * kPfStages + 3 * kPfConvStages + 4 + 1 + 2 * kPgScaleStages;
+  static constexpr int kNumBars = 2 * kPfStages + 3 * kPfConvStages + 8 + 1 + 2 * kPgScaleStages;
   static constexpr int kTmemSlotOff = kBarOff + kNumBars * 8;
   static constexpr int kAbortOff = kTmemSlotOff + 8;
   static constexpr int kTotal = kAbortOff + 8;
@@ -147,7 +147,7 @@ __device__ __forceinline__ uint32_t sw128(uint32_t row, uint32_t kc) { return ro
 
 // ---------------------------------------------------------------------------------------------------------
 // Roles shared by the per-channel kernel and the group-wise kernel.  `bars` layout: raw_full[S], empty[S],
-// conv_full[C], conv_empty[C], conv_done[C], tmem_full[2], tmem_empty[2], drain, then (group-wise kernel only)
+// conv_full[C], conv_empty[C], conv_done[C], tmem_full[4], tmem_empty[4], drain, then (group-wise kernel only)
 // scale_full[kPgScaleStages], scale_empty[kPgScaleStages].
 // ---------------------------------------------------------------------------------------------------------
 struct PfBars {
@@ -161,9 +161,9 @@ __device__ __forceinline__ PfBars pf_bars(uint64_t* bars) {
   b.conv_empty = b.conv_full + kPfConvStages;
   b.conv_done = b.conv_empty + kPfConvStages;  // peer CTA only: its four converter warps
   b.tmem_full = b.conv_done + kPfConvStages;
-  b.tmem_empty = b.tmem_full + 2;
-  b.drain = b.tmem_full + 4;
-  b.scale_full = b.tmem_full + 5;
+  b.tmem_empty = b.tmem_full + 4;
+  b.drain = b.tmem_full + 8;
+  b.scale_full = b.tmem_full + 9;
   b.scale_empty = b.scale_full + kPgScaleStages;
   return b;
 }
@@ -179,7 +179,7 @@ __device__ __forceinline__ void pf_init_bars(const PfBars& b, int epi_arrivals, 
     mbar_init(&b.conv_done[s], conv_warps);
     mbar_init(&b.conv_empty[s], 1);
   }
-  for (int i = 0; i < 2; ++i) {
+  for (int i = 0; i < 4; ++i) {  // up to four accumulators (512 TMEM columns / tile width)
     mbar_init(&b.tmem_full[i], 1);
     mbar_init(&b.tmem_empty[i], epi_arrivals);
   }
@@ -236,7 +236,7 @@ __device__ __forceinline__ void pf_producer(uint8_t* smem, const PfBars& b, cons
 // warp 1 of the leader CTA: issues the MMAs of both CTAs.  An accumulator (one of the two TMEM buffers) collects
 // `kb_per_acc` K blocks and is then handed to the epilogue: the whole K range for per-channel scales, one scale
 // group for group-wise scales.
-template <typename T, int BITS, int BN = kTN>
+template <typename T, int BITS, int BN = kTN, int NBUF = 2, int ACC_STRIDE = kTN>
 __device__ __forceinline__ void pf_mma(uint8_t* smem, const PfBars& b, const PfParams& p, uint32_t tmem_base, int pair_id,
                                        int num_pairs, int kb_per_acc, volatile int* abort_flag) {
   using L = PfSmem<BITS>;
@@ -250,8 +250,8 @@ __device__ __forceinline__ void pf_mma(uint8_t* smem, const PfBars& b, const PfP
   bool issued_any = false;
   for (int t = pair_id; t < num_tiles && ok; t += num_pairs) {
     for (int kb0 = 0; kb0 < p.k_blocks && ok; kb0 += kb_per_acc, ++seg) {
-      const int buf = seg & 1;
-      const uint32_t acc_phase = (seg >> 1) & 1;
+      const int buf = seg % NBUF;
+      const uint32_t acc_phase = (seg / NBUF) & 1;
       ok = mbar_wait_bounded(&b.tmem_empty[buf], acc_phase ^ 1, abort_flag);
       ok = __all_sync(0xffffffffu, ok);
       if (!ok) {
@@ -259,7 +259,7 @@ __device__ __forceinline__ void pf_mma(uint8_t* smem, const PfBars& b, const PfP
         break;
       }
       tc_fence_after();
-      const uint32_t tmem_d = tmem_base + buf * kTN;
+      const uint32_t tmem_d = tmem_base + buf * ACC_STRIDE;
       const int kb1 = min(kb0 + kb_per_acc, p.k_blocks);
       for (int kb = kb0; kb < kb1; ++kb) {
         ok = mbar_wait_bounded(&b.conv_full[cstage], cphase, abort_flag);
@@ -540,7 +540,9 @@ __device__ __forceinline__ void unpack2(uint64_t v, float& lo, float& hi) {
   asm("mov.b64 {%0, %1}, %2;" : "=f"(lo), "=f"(hi) : "l"(v));
 }
 
-template <typename T, int BITS, bool HAS_ZP>
+// BN: channels per pair tile, 256 or 128; the 512 TMEM columns hold NBUF = 512 / BN accumulators, so that many scale
+// groups are in flight between the MMA warp and the epilogue warps.
+template <typename T, int BITS, bool HAS_ZP, int BN>
 __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(kPgThreads, 1)
 wo_umma_pair_group_kernel(const __grid_constant__ CUtensorMap tmap_x, const __grid_constant__ CUtensorMap tmap_w,
                           const PfParams p) {
@@ -558,7 +560,9 @@ wo_umma_pair_group_kernel(const __grid_constant__ CUtensorMap tmap_x, const __gr
   const int pair_id = blockIdx.x >> 1;
   const int num_pairs = gridDim.x >> 1;
   const int num_tiles = p.tiles_m * p.tiles_n;
-  constexpr uint32_t kTmemCols = 2 * kTN;
+  constexpr uint32_t kTmemCols = 512;
+  constexpr int NBUF = 512 / BN;
+  constexpr int HC = BN / 2;  // columns of a tile that one epilogue thread folds (one column half)
 
   if (threadIdx.x == 0) {
     *abort_flag = 0;
@@ -580,16 +584,17 @@ wo_umma_pair_group_kernel(const __grid_constant__ CUtensorMap tmap_x, const __gr
   if (warp < 4) {
     asm volatile("setmaxnreg.dec.sync.aligned.u32 40;");
     if (warp == 0) {
-      pf_producer<BITS>(smem, b, &tmap_x, &tmap_w, p, rank, pair_id, num_pairs, abort_flag);
+      pf_producer<BITS, BN>(smem, b, &tmap_x, &tmap_w, p, rank, pair_id, num_pairs, abort_flag);
     } else if (warp == 1) {
-      if (rank == 0) pf_mma<T, BITS>(smem, b, p, tmem_base, pair_id, num_pairs, kb_per_group, abort_flag);
+      if (rank == 0) pf_mma<T, BITS, BN, NBUF, BN>(smem, b, p, tmem_base, pair_id, num_pairs, kb_per_group, abort_flag);
       else pf_relay(b, p, pair_id, num_pairs, abort_flag);
     } else {
       // ---- warps 2 and 3: stage the scales (and scale * zero-point, and with a tile's first group its bias) of the
-      // coming groups as fp32 in a ring of kPgScaleStages slots, one column half each, four columns per lane, so that
+      // coming groups as fp32 in a ring of kPgScaleStages slots, one column half each, CPL columns per lane, so that
       // the epilogue warps find them ready
+      constexpr int CPL = HC / 32;
       const int half = warp - 2;
-      const int c0 = half * 128 + lane * 4;
+      const int c0 = half * HC + lane * CPL;
       float* sS = vec_smem;
       float* sZ = sS + kPgScaleStages * kTN;
       float* sB = sZ + kPgScaleStages * kTN;
@@ -599,13 +604,13 @@ wo_umma_pair_group_kernel(const __grid_constant__ CUtensorMap tmap_x, const __gr
       for (int t = pair_id; t < num_tiles && ok; t += num_pairs) {
         int mb, nb;
         pf_tile_coords(t, p.tiles_m, p.tiles_n, mb, nb);
-        const int n0 = nb * kTN + c0;
+        const int n0 = nb * BN + c0;
         for (int g = 0; g < groups; ++g, ++seg) {
           const int slot = seg % kPgScaleStages;
           const uint32_t ph = (seg / kPgScaleStages) & 1;
-          float sv[4], zv[4], bv[4];
+          float sv[CPL], zv[CPL], bv[CPL];
 #pragma unroll
-          for (int j = 0; j < 4; ++j) {
+          for (int j = 0; j < CPL; ++j) {
             const bool in = n0 + j < p.N;
             const int64_t at = int64_t(g) * p.N + n0 + j;
             sv[j] = in ? load_as_f32(p.scale, p.scale_dtype, at) : 0.f;
@@ -618,9 +623,12 @@ wo_umma_pair_group_kernel(const __grid_constant__ CUtensorMap tmap_x, const __gr
             if (lane == 0) pf_report(p.status, abort_flag, DEV_TIMEOUT_PRODUCER);
             break;
           }
-          *reinterpret_cast<float4*>(sS + slot * kTN + c0) = make_float4(sv[0], sv[1], sv[2], sv[3]);
-          if (HAS_ZP) *reinterpret_cast<float4*>(sZ + slot * kTN + c0) = make_float4(zv[0], zv[1], zv[2], zv[3]);
-          if (g == 0) *reinterpret_cast<float4*>(sB + slot * kTN + c0) = make_float4(bv[0], bv[1], bv[2], bv[3]);
+#pragma unroll
+          for (int j = 0; j < CPL; ++j) {
+            sS[slot * kTN + c0 + j] = sv[j];
+            if (HAS_ZP) sZ[slot * kTN + c0 + j] = zv[j];
+            if (g == 0) sB[slot * kTN + c0 + j] = bv[j];
+          }
           __syncwarp();
           if (lane == 0) mbar_arrive(&b.scale_full[slot]);
         }
@@ -628,7 +636,7 @@ wo_umma_pair_group_kernel(const __grid_constant__ CUtensorMap tmap_x, const __gr
     }
   } else if (warp < 8) {
     asm volatile("setmaxnreg.dec.sync.aligned.u32 56;");
-    pf_converters<T, BITS>(smem, b, p, rank, pair_id, num_pairs, threadIdx.x - 4 * 32, abort_flag);
+    pf_converters<T, BITS, BN>(smem, b, p, rank, pair_id, num_pairs, threadIdx.x - 4 * 32, abort_flag);
   } else {
     asm volatile("setmaxnreg.inc.sync.aligned.u32 208;");
     // -------------------------------- epilogue (both CTAs) --------------------------------
@@ -640,19 +648,19 @@ wo_umma_pair_group_kernel(const __grid_constant__ CUtensorMap tmap_x, const __gr
     T* out = reinterpret_cast<T*>(p.out);
     const bool vec_ok = (p.ldo % 8 == 0) && (reinterpret_cast<uintptr_t>(out) % 16 == 0);
     const int groups = p.K / p.group;
-    uint64_t sum2[64];
+    uint64_t sum2[HC / 2];
 #pragma unroll
-    for (int i = 0; i < 64; ++i) sum2[i] = 0ull;
+    for (int i = 0; i < HC / 2; ++i) sum2[i] = 0ull;
     int seg = 0, local = 0;
     bool ok = true;
     for (int t = pair_id; t < num_tiles && ok; t += num_pairs, ++local) {
       int mb, nb;
       pf_tile_coords(t, p.tiles_m, p.tiles_n, mb, nb);
       const int row = mb * 256 + int(rank) * kTM + quarter * 32 + lane;
-      const int n0 = nb * kTN;
+      const int n0 = nb * BN;
       for (int g = 0; g < groups; ++g, ++seg) {
-        const int buf = seg & 1;
-        const uint32_t seg_phase = (seg >> 1) & 1;
+        const int buf = seg % NBUF;
+        const uint32_t seg_phase = (seg / NBUF) & 1;
         const int slot = seg % kPgScaleStages;
         const uint32_t slot_phase = (seg / kPgScaleStages) & 1;
         float nxg = 0.f;
@@ -665,20 +673,20 @@ wo_umma_pair_group_kernel(const __grid_constant__ CUtensorMap tmap_x, const __gr
           break;
         }
         if (g == 0) {  // the sums of a tile start from its bias (they were left at zero)
-          const float4* b4 = reinterpret_cast<const float4*>(sB + slot * kTN + half * 128);
+          const float4* b4 = reinterpret_cast<const float4*>(sB + slot * kTN + half * HC);
 #pragma unroll
-          for (int i = 0; i < 32; ++i) {
+          for (int i = 0; i < HC / 4; ++i) {
             const float4 bv = b4[i];
             asm("mov.b64 %0, {%1, %2};" : "=l"(sum2[2 * i]) : "f"(bv.x), "f"(bv.y));
             asm("mov.b64 %0, {%1, %2};" : "=l"(sum2[2 * i + 1]) : "f"(bv.z), "f"(bv.w));
           }
         }
         tc_fence_after();
-        const uint32_t taddr = tmem_base + (uint32_t(quarter * 32) << 16) + buf * kTN + half * 128;
-        const float4* s4 = reinterpret_cast<const float4*>(sS + slot * kTN + half * 128);
-        const float4* z4 = reinterpret_cast<const float4*>(sZ + slot * kTN + half * 128);
+        const uint32_t taddr = tmem_base + (uint32_t(quarter * 32) << 16) + buf * BN + half * HC;
+        const float4* s4 = reinterpret_cast<const float4*>(sS + slot * kTN + half * HC);
+        const float4* z4 = reinterpret_cast<const float4*>(sZ + slot * kTN + half * HC);
 #pragma unroll
-        for (int c = 0; c < 4; ++c) {
+        for (int c = 0; c < HC / 32; ++c) {
           uint32_t r[32];
           tmem_ld_32x32(taddr + c * 32, r);
           tc_wait_ld();
@@ -704,16 +712,16 @@ wo_umma_pair_group_kernel(const __grid_constant__ CUtensorMap tmap_x, const __gr
       }
       if (!ok) break;
       // the tile's sums are complete: round once, store, and clear the sums for the next tile
-      T* orow0 = out + int64_t(row) * p.ldo + n0 + half * 128;
+      T* orow0 = out + int64_t(row) * p.ldo + n0 + half * HC;
 #pragma unroll
-      for (int c = 0; c < 4; ++c) {
+      for (int c = 0; c < HC / 32; ++c) {
         float v[32];
 #pragma unroll
         for (int j = 0; j < 32; j += 2) {
           unpack2(sum2[(c * 32 + j) >> 1], v[j], v[j + 1]);
           sum2[(c * 32 + j) >> 1] = 0ull;
         }
-        const int col0 = n0 + half * 128 + c * 32;
+        const int col0 = n0 + half * HC + c * 32;
         if (row < p.M && col0 < p.N) {
           T* orow = orow0 + c * 32;
           if (col0 + 32 <= p.N && vec_ok) {
@@ -817,6 +825,30 @@ int launch_prefill_perch(const T* act, int64_t lda, const uint8_t* qw, PfParams 
   return check_cuda(cudaGetLastError(), "weight-only prefill launch");
 }
 
+// Tile width of the group-wise kernel.  128-wide tiles would keep four accumulators in flight instead of two, which
+// hides the hand-over of a group's accumulator, but a K block of a 128-wide tile gives the four converter warps half
+// the time for the same per-block barrier round: measured 676 against 865 TFLOP/s (A16W4, group 128, 2048 x 28672 x 8192).
+constexpr int kPgTile = 256;
+
+template <typename T, int BITS, bool HAS_ZP, int BN>
+int launch_prefill_group(const T* act, int64_t lda, const uint8_t* qw, PfParams p, cudaStream_t st) {
+  using L = PfSmem<BITS>;
+  static std::once_flag once[64];
+  static cudaError_t attr_err[64];  // per device, so that a failure is reported on every call and not only the first
+  if (int e = pf_configure(wo_umma_pair_group_kernel<T, BITS, HAS_ZP, BN>, L::kDynamicBytes, attr_err, once)) return e;
+  CUtensorMap tx, tw;
+  if (int e = make_tmap_2d(&tx, 2, act, p.M, p.K, lda * 2, kTK, kTM, true)) return e;
+  const int64_t w_rows = (BITS == 8) ? p.N : p.N / 2;
+  if (int e = make_tmap_2d(&tw, 1, qw, w_rows, p.K, p.K, kTK, (BITS == 8) ? BN / 2 : BN / 4, false)) return e;
+  p.tiles_m = (p.M + 255) / 256;
+  p.tiles_n = (p.N + BN - 1) / BN;
+  p.k_blocks = (p.K + kTK - 1) / kTK;
+  const int tiles = p.tiles_m * p.tiles_n;
+  const int pairs = tiles < sm_count() / 2 ? tiles : sm_count() / 2;
+  wo_umma_pair_group_kernel<T, BITS, HAS_ZP, BN><<<2 * pairs, kPgThreads, L::kDynamicBytes, st>>>(tx, tw, p);
+  return check_cuda(cudaGetLastError(), "weight-only prefill launch");
+}
+
 template <typename T, int BITS>
 int launch_prefill(const T* act, int64_t lda, const uint8_t* qw, PfParams p, float* xsum_ws, cudaStream_t st) {
   using L = PfSmem<BITS>;
@@ -836,24 +868,8 @@ int launch_prefill(const T* act, int64_t lda, const uint8_t* qw, PfParams p, flo
       default: return launch_prefill_perch<T, BITS, 256>(act, lda, qw, p, st);
     }
   }
-  // per device, so that a failure is reported on every call and not only the first
-  static std::once_flag once[2][64];
-  static cudaError_t attr_err[2][64];
-  const int which = p.zp ? 1 : 0;
-  if (which == 0) { if (int e = pf_configure(wo_umma_pair_group_kernel<T, BITS, false>, L::kDynamicBytes, attr_err[0], once[0])) return e; }
-  else { if (int e = pf_configure(wo_umma_pair_group_kernel<T, BITS, true>, L::kDynamicBytes, attr_err[1], once[1])) return e; }
-  CUtensorMap tx, tw;
-  if (int e = make_tmap_2d(&tx, 2, act, p.M, p.K, lda * 2, kTK, kTM, true)) return e;
-  const int64_t w_rows = (BITS == 8) ? p.N : p.N / 2;
-  if (int e = make_tmap_2d(&tw, 1, qw, w_rows, p.K, p.K, kTK, (BITS == 8) ? kTN / 2 : kTN / 4, false)) return e;
-  p.tiles_m = (p.M + 255) / 256;
-  p.tiles_n = (p.N + kTN - 1) / kTN;
-  p.k_blocks = (p.K + kTK - 1) / kTK;
-  const int tiles = p.tiles_m * p.tiles_n;
-  const int pairs = tiles < sm_count() / 2 ? tiles : sm_count() / 2;
-  if (which == 0) wo_umma_pair_group_kernel<T, BITS, false><<<2 * pairs, kPgThreads, L::kDynamicBytes, st>>>(tx, tw, p);
-  else wo_umma_pair_group_kernel<T, BITS, true><<<2 * pairs, kPgThreads, L::kDynamicBytes, st>>>(tx, tw, p);
-  return check_cuda(cudaGetLastError(), "weight-only prefill launch");
+  if (p.zp) return launch_prefill_group<T, BITS, true, kPgTile>(act, lda, qw, p, st);
+  return launch_prefill_group<T, BITS, false, kPgTile>(act, lda, qw, p, st);
 }
 
 }  // namespace
