@@ -36,6 +36,11 @@ constexpr int kTK = 64;         // K per stage: 128 bytes of 16-bit operand
 // timeline showed them, not the MMAs, setting the pace (0.51 us per K block against 0.34 us); twelve or sixteen are
 // no faster than eight.
 constexpr int kPfConvWarps = 8;
+// The converter warps take the K blocks in this many teams, in turn.  Measured: int4 weights (two iterations per thread
+// and block, four shared-memory stores each) gain 5 % from two teams of four warps (1319 -> 1390 TFLOP/s at
+// 2048 x 28672 x 8192), int8 weights are the same either way, the group-wise kernel's four warps lose 4 % as two teams.
+template <int BITS> constexpr int pf_conv_teams() { return BITS == 4 ? 2 : 1; }
+constexpr int kPgConvTeams = 1;
 constexpr int kPfThreads = (8 + kPfConvWarps) * 32;
 constexpr int kPfConvRegs = 72;
 constexpr int kPfStages = 5;      // TMA ring: activations + raw weight bytes
@@ -319,19 +324,27 @@ __device__ __forceinline__ void pf_relay(const PfBars& b, const PfParams& p, int
   }
 }
 
-// converter warps of both CTAs (CT threads, ct = 0..CT-1): raw bytes of a K block -> exact 16-bit integers in the
-// K-major 128-byte-swizzled operand tile
-template <typename T, int BITS, int BN = kTN, int CT = 128>
+// converter warps of both CTAs: raw bytes of a K block -> exact 16-bit integers in the K-major 128-byte-swizzled
+// operand tile.  The warps form TEAMS teams of CT threads (ct = 0..CT-1 within a team); the K blocks go to the teams
+// in turn, so a team has TEAMS blocks' time for one block's conversion and its fixed cost (two barrier waits, the
+// proxy fence, the arrive), which is what sets the pace when a block is short.
+template <typename T, int BITS, int BN = kTN, int CT = 128, int TEAMS = 1>
 __device__ __forceinline__ void pf_converters(uint8_t* smem, const PfBars& b, const PfParams& p, uint32_t rank, int pair_id,
-                                              int num_pairs, int ct, volatile int* abort_flag) {
+                                              int num_pairs, int ct, volatile int* abort_flag, int team = 0) {
   using L = PfSmem<BITS>;
   const int num_tiles = p.tiles_m * p.tiles_n;
   const int lane = ct & 31;
-  int stage = 0, cstage = 0;
+  int stage = 0, cstage = 0, turn = 0;  // ring positions of the current K block; whose turn it is
   uint32_t phase = 0, cphase = 0;
   bool ok = true;
+  auto advance = [&]() {
+    if (++stage == kPfStages) { stage = 0; phase ^= 1; }
+    if (++cstage == kPfConvStages) { cstage = 0; cphase ^= 1; }
+    if (++turn == TEAMS) turn = 0;
+  };
   for (int t = pair_id; t < num_tiles && ok; t += num_pairs) {
-    for (int kb = 0; kb < p.k_blocks; ++kb) {
+    for (int kb = 0; kb < p.k_blocks; ++kb, advance()) {
+      if (TEAMS > 1 && turn != team) continue;
       ok = mbar_wait_bounded(&b.conv_empty[cstage], cphase ^ 1, abort_flag) &&
            mbar_wait_bounded(&b.raw_full[stage], phase, abort_flag);
       ok = __all_sync(0xffffffffu, ok);
@@ -377,8 +390,6 @@ __device__ __forceinline__ void pf_converters(uint8_t* smem, const PfBars& b, co
       fence_proxy_async_smem();  // the tensor core reads these bytes through the async proxy
       __syncwarp();
       if (lane == 0) mbar_arrive(rank == 0 ? &b.conv_full[cstage] : &b.conv_done[cstage]);
-      if (++stage == kPfStages) { stage = 0; phase ^= 1; }
-      if (++cstage == kPfConvStages) { cstage = 0; cphase ^= 1; }
     }
   }
 }
@@ -411,7 +422,7 @@ wo_umma_pair_kernel(const __grid_constant__ CUtensorMap tmap_x, const __grid_con
 
   if (threadIdx.x == 0) {
     *abort_flag = 0;
-    pf_init_bars(b, 8, false, kPfConvWarps);
+    pf_init_bars(b, 8, false, kPfConvWarps / pf_conv_teams<BITS>());
     tma_prefetch_desc(&tmap_x);
     tma_prefetch_desc(&tmap_w);
   }
@@ -500,7 +511,10 @@ wo_umma_pair_kernel(const __grid_constant__ CUtensorMap tmap_x, const __grid_con
     }
   } else {
     asm volatile("setmaxnreg.dec.sync.aligned.u32 %0;" ::"n"(kPfConvRegs));
-    pf_converters<T, BITS, BN, kPfConvWarps * 32>(smem, b, p, rank, pair_id, num_pairs, threadIdx.x - 8 * 32, abort_flag);
+    constexpr int kTeamThreads = kPfConvWarps * 32 / pf_conv_teams<BITS>();
+    pf_converters<T, BITS, BN, kTeamThreads, pf_conv_teams<BITS>()>(smem, b, p, rank, pair_id, num_pairs,
+                                                           (threadIdx.x - 8 * 32) % kTeamThreads, abort_flag,
+                                                           (threadIdx.x - 8 * 32) / kTeamThreads);
   }
 
   // -------------------------------- teardown --------------------------------
@@ -566,7 +580,7 @@ wo_umma_pair_group_kernel(const __grid_constant__ CUtensorMap tmap_x, const __gr
 
   if (threadIdx.x == 0) {
     *abort_flag = 0;
-    pf_init_bars(b, 16, true);
+    pf_init_bars(b, 16, true, 4 / kPgConvTeams);
     tma_prefetch_desc(&tmap_x);
     tma_prefetch_desc(&tmap_w);
   }
@@ -636,7 +650,9 @@ wo_umma_pair_group_kernel(const __grid_constant__ CUtensorMap tmap_x, const __gr
     }
   } else if (warp < 8) {
     asm volatile("setmaxnreg.dec.sync.aligned.u32 56;");
-    pf_converters<T, BITS, BN>(smem, b, p, rank, pair_id, num_pairs, threadIdx.x - 4 * 32, abort_flag);
+    pf_converters<T, BITS, BN, 128 / kPgConvTeams, kPgConvTeams>(smem, b, p, rank, pair_id, num_pairs,
+                                                                 (threadIdx.x - 4 * 32) % (128 / kPgConvTeams), abort_flag,
+                                                                 (threadIdx.x - 4 * 32) / (128 / kPgConvTeams));
   } else {
     asm volatile("setmaxnreg.inc.sync.aligned.u32 208;");
     // -------------------------------- epilogue (both CTAs) --------------------------------
