@@ -15,8 +15,9 @@ HBM; `e2e` is the same step through the public Python API with pinned host
 buffers copied in and the outputs copied back inside the timed region.
 `--impl reference` times the reference's own CPU (torch) implementation of the
 same layer on the host cores, on rank 0 only: the unmodified reference classes
-when the reference tree is installed under baseline/_ref (or mounted at
-/root/reference), else the restatement in oracle/ (reported as kind "port").
+when the reference tree is installed under baseline/_ref (or the environment
+variable FLASHNN_REFERENCE names a checkout of it), else the restatement in
+oracle/ (reported as kind "port").
 """
 import argparse
 import json
@@ -54,8 +55,8 @@ def measured_peaks():
 
 def find_reference():
     """Directory that holds the reference project's own `flashnn` package, or None."""
-    for cand in (os.path.join(ROOT, "baseline", "_ref"), "/root/reference"):
-        if os.path.exists(os.path.join(cand, "flashnn", "quant_gemm.py")):
+    for cand in (os.path.join(ROOT, "baseline", "_ref"), os.environ.get("FLASHNN_REFERENCE", "")):
+        if cand and os.path.exists(os.path.join(cand, "flashnn", "quant_gemm.py")):
             return cand
     return None
 
@@ -64,7 +65,7 @@ def load_reference_cpu():
     """The unmodified reference with its torch backend selected: (module, None), or (None, reason)."""
     path = find_reference()
     if path is None:
-        return None, "no reference tree under baseline/_ref or /root/reference"
+        return None, "no reference tree under baseline/_ref (nor named by FLASHNN_REFERENCE)"
     try:
         for name in [n for n in sys.modules if n == "flashnn" or n.startswith("flashnn.")]:
             del sys.modules[name]
@@ -622,7 +623,7 @@ def reference_triton_figures(timeout_s=900):
     """The reference's own Triton kernels on this GPU (secondary baseline), timed by `bench.py --case ref_triton` in a
     child process so that a JIT failure or a crash of that code cannot take the benchmark down."""
     if find_reference() is None:
-        return dict(unavailable="no reference tree under baseline/_ref or /root/reference")
+        return dict(unavailable="no reference tree under baseline/_ref (nor named by FLASHNN_REFERENCE)")
     try:
         r = subprocess.run([sys.executable, os.path.abspath(__file__), "--case", "ref_triton"], capture_output=True, text=True,
                            timeout=timeout_s)

@@ -6,7 +6,7 @@ seeded inputs are the only thing that can pin the CPU oracle's restatement of th
     python tests/golden/make_moe_golden.py [--ref DIR] [--out DIR]
 
 DIR for --ref is a directory that holds the unmodified reference package `flashnn/` (default: baseline/_ref next to
-this repository's root, else /root/reference); --out defaults to tests/golden.  Every case stores its inputs and the
+this repository's root, else what the environment variable FLASHNN_REFERENCE names); --out defaults to tests/golden.  Every case stores its inputs and the
 reference's output; 16-bit floats are stored as their raw uint16 bits.  A case whose kernel fails to compile or run
 is recorded under `<case>/error` instead of being dropped silently.
 
@@ -40,8 +40,8 @@ def main():
     args = ap.parse_args()
     ref = args.ref
     if ref is None:
-        for cand in (os.path.join(ROOT, "baseline", "_ref"), "/root/reference"):
-            if os.path.exists(os.path.join(cand, "flashnn", "quant_gemm.py")):
+        for cand in (os.path.join(ROOT, "baseline", "_ref"), os.environ.get("FLASHNN_REFERENCE", "")):
+            if cand and os.path.exists(os.path.join(cand, "flashnn", "quant_gemm.py")):
                 ref = cand
                 break
     if ref is None:
