@@ -88,7 +88,7 @@ EncodeTiledFn encode_tiled_fn() {
 }  // namespace
 
 int make_tmap_2d(CUtensorMap* m, int elem_bytes, const void* base, int64_t rows, int64_t cols, int64_t pitch_bytes,
-                 int box_cols, int box_rows, bool swizzle128) {
+                 int box_cols, int box_rows, int swizzle) {
   EncodeTiledFn enc = encode_tiled_fn();
   if (!enc) return fail(FNN_ERR_CUDA, "cuTensorMapEncodeTiled is not available from this driver");
   const cuuint64_t dims[2] = {cuuint64_t(cols), cuuint64_t(rows)};
@@ -97,7 +97,7 @@ int make_tmap_2d(CUtensorMap* m, int elem_bytes, const void* base, int64_t rows,
   const cuuint32_t estr[2] = {1, 1};
   const CUtensorMapDataType dt = elem_bytes == 1 ? CU_TENSOR_MAP_DATA_TYPE_UINT8 : CU_TENSOR_MAP_DATA_TYPE_UINT16;
   const CUresult r = enc(m, dt, 2, const_cast<void*>(base), dims, strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE,
-                         swizzle128 ? CU_TENSOR_MAP_SWIZZLE_128B : CU_TENSOR_MAP_SWIZZLE_NONE,
+                         swizzle == 1 ? CU_TENSOR_MAP_SWIZZLE_128B : swizzle == 2 ? CU_TENSOR_MAP_SWIZZLE_64B : CU_TENSOR_MAP_SWIZZLE_NONE,
                          CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
   if (r != CUDA_SUCCESS) return fail(FNN_ERR_CUDA, "cuTensorMapEncodeTiled failed with CUresult %d", int(r));
   return FNN_OK;

@@ -44,6 +44,7 @@ struct A8W8Params {
   int M, N, K;
   int tiles_m, tiles_n, k_blocks;
   int* status;  // device status word
+  int out_tma;  // CTA-pair kernel: the output goes through shared memory and TMA stores (out and its pitch are 16-byte aligned)
   unsigned long long wait_ns;  // longest time one wait may take (single-CTA kernel; kWaitLimitNs unless a test shortened it)
   int skip_kb;                 // -1, or (test hook) the K block of a CTA's first tile whose loads are left out
   // Fused-MoE mode (kernel template flag MOE): A is the expert-sorted copy of the token rows [EM, K], B is the
@@ -100,26 +101,25 @@ __device__ __forceinline__ void report(int* status, volatile int* abort_flag, in
 // Epilogue of 32 accumulator columns of one output row: optional raw int32 copy, then
 // out = fl32(float(acc) * s) with s = row scale * column scale (rounded to the scales' dtype when
 // both scales share a 16-bit dtype), rounded once to OutT.
-template <typename OutT>
-__device__ __forceinline__ void store_chunk(const uint32_t (&r)[32], int row, int col0, float rs, const float* cs,
-                                            bool same16, const A8W8Params& p, bool vec_ok, bool acc_vec_ok) {
-  if (row >= p.M || col0 >= p.N) return;
-  const bool full = col0 + 32 <= p.N;
-  if (p.acc_out) {
-    int32_t* arow = p.acc_out + int64_t(row) * p.ldacc + col0;
-    if (full && acc_vec_ok) {
+__device__ __forceinline__ void store_acc_chunk(const uint32_t (&r)[32], int row, int col0, const A8W8Params& p,
+                                                bool acc_vec_ok) {
+  if (!p.acc_out || row >= p.M || col0 >= p.N) return;
+  int32_t* arow = p.acc_out + int64_t(row) * p.ldacc + col0;
+  if (col0 + 32 <= p.N && acc_vec_ok) {
 #pragma unroll
-      for (int j = 0; j < 32; j += 4)
-        *reinterpret_cast<uint4*>(arow + j) = make_uint4(r[j], r[j + 1], r[j + 2], r[j + 3]);
-    } else {
+    for (int j = 0; j < 32; j += 4)
+      *reinterpret_cast<uint4*>(arow + j) = make_uint4(r[j], r[j + 1], r[j + 2], r[j + 3]);
+  } else {
 #pragma unroll
-      for (int j = 0; j < 32; ++j)
-        if (col0 + j < p.N) arow[j] = int32_t(r[j]);
-    }
+    for (int j = 0; j < 32; ++j)
+      if (col0 + j < p.N) arow[j] = int32_t(r[j]);
   }
-  // s = fl32(row scale * column scale) (rounded to the scales' dtype when both share a 16-bit one), out = fl32(acc * s):
-  // four column scales per shared-memory read, two products per packed fp32 multiply
-  float v[32];
+}
+
+// s = fl32(row scale * column scale) (rounded to the scales' dtype when both share a 16-bit one), v = fl32(acc * s):
+// four column scales per shared-memory read, two products per packed fp32 multiply
+__device__ __forceinline__ void scale_chunk(const uint32_t (&r)[32], float rs, const float* cs, bool same16,
+                                            const A8W8Params& p, float (&v)[32]) {
   const uint64_t rs2 = pack_f32x2(rs, rs);
 #pragma unroll
   for (int j = 0; j < 32; j += 4) {
@@ -134,6 +134,16 @@ __device__ __forceinline__ void store_chunk(const uint32_t (&r)[32], int row, in
     unpack_f32x2(fmul2_rn(pack_f32x2(float(int32_t(r[j])), float(int32_t(r[j + 1]))), pack_f32x2(s0, s1)), v[j], v[j + 1]);
     unpack_f32x2(fmul2_rn(pack_f32x2(float(int32_t(r[j + 2])), float(int32_t(r[j + 3]))), pack_f32x2(s2, s3)), v[j + 2], v[j + 3]);
   }
+}
+
+template <typename OutT>
+__device__ __forceinline__ void store_chunk(const uint32_t (&r)[32], int row, int col0, float rs, const float* cs,
+                                            bool same16, const A8W8Params& p, bool vec_ok, bool acc_vec_ok) {
+  if (row >= p.M || col0 >= p.N) return;
+  const bool full = col0 + 32 <= p.N;
+  store_acc_chunk(r, row, col0, p, acc_vec_ok);
+  float v[32];
+  scale_chunk(r, rs, cs, same16, p, v);
   OutT* orow = reinterpret_cast<OutT*>(p.out) + int64_t(row) * p.ldo + col0;
   if (full && vec_ok) {
 #pragma unroll
@@ -505,7 +515,9 @@ template <int BN, int STAGES> struct PairSmem {
   static constexpr int kABytes = kBM * kBK;             // this CTA's 128 rows of A
   static constexpr int kBBytes = (kBN / 2) * kBK;       // this CTA's BN / 2 rows of B
   static constexpr int kStageBytes = kABytes + kBBytes;
-  static constexpr int kColScaleOff = STAGES * kStageBytes;  // [4][kBN] float
+  static constexpr int kOutOff = STAGES * kStageBytes;        // [4 epilogue warps][2][32 rows x 64 B] output staging
+  static constexpr int kOutBytes = 4 * 2 * 2048;
+  static constexpr int kColScaleOff = kOutOff + kOutBytes;    // [4][kBN] float
   static constexpr int kBarOff = kColScaleOff + 4 * kBN * 4;
   static constexpr int kNumBars = 2 * STAGES + 4 + 1;
   static constexpr int kTmemSlotOff = kBarOff + kNumBars * 8;
@@ -517,7 +529,7 @@ template <int BN, int STAGES> struct PairSmem {
 template <typename OutT, int BN, int STAGES, bool SK>
 __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(kThreads, 1)
 a8w8_umma_pair_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ CUtensorMap tmap_b,
-                      const A8W8Params p) {
+                      const __grid_constant__ CUtensorMap tmap_out, const A8W8Params p) {
   using L = PairSmem<BN, STAGES>;
   constexpr int kAccStride = 256;  // TMEM columns between the two accumulators (512 are allocated whatever BN is)
   extern __shared__ uint8_t smem_raw[];
@@ -553,6 +565,7 @@ a8w8_umma_pair_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_c
     mbar_fence_init();
     tma_prefetch_desc(&tmap_a);
     tma_prefetch_desc(&tmap_b);
+    if (p.out_tma) tma_prefetch_desc(&tmap_out);
   }
   if (warp == 1) {
     tmem_alloc_pair(tmem_slot, kTmemCols);
@@ -664,6 +677,8 @@ a8w8_umma_pair_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_c
     int local = 0;
     bool ok = true;
     PairWork<SK> w(p, pair_id, num_pairs);
+    uint8_t* out_stage = smem + L::kOutOff + quarter * 4096;            // this warp's two output staging buffers
+    int out_buf = 0;
     const int my_flag = int(rank) * 4 + quarter;                        // this warp's flag word within a pair's eight
     const int my_row = int(rank) * 128 + quarter * 32 + lane;           // this thread's row within a tile
     for (; ok && w.next(); ++local) {
@@ -755,7 +770,33 @@ a8w8_umma_pair_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_c
             }
           }
         }
-        store_chunk<OutT>(r, row, n0 + c * 32, rs, cs + c * 32, same16, p, vec_ok, acc_vec_ok);
+        if (p.out_tma) {
+          // The 32 x 32 block of outputs goes through shared memory and leaves as one TMA store: whole 64-byte row
+          // pieces instead of 16 bytes per lane and row.  Rows of 64 bytes in the 64-byte swizzle pattern (16-byte
+          // piece j of row l sits at piece j ^ ((l >> 1) & 3)), so the 32 lanes' stores spread over all banks; the
+          // store leaves out what lies beyond M or N.  Two buffers per warp: before one is written again, the store
+          // that read it two chunks ago has finished reading.
+          store_acc_chunk(r, row, n0 + c * 32, p, acc_vec_ok);
+          float v[32];
+          scale_chunk(r, rs, cs + c * 32, same16, p, v);
+          if (lane == 0) tma_store_wait_read<1>();
+          __syncwarp();
+          uint8_t* buf_out = out_stage + out_buf * 2048;
+#pragma unroll
+          for (int j = 0; j < 4; ++j)
+            *reinterpret_cast<uint4*>(buf_out + lane * 64 + ((j ^ ((lane >> 1) & 3)) << 4)) =
+                make_uint4(pack2<OutT>(v[8 * j], v[8 * j + 1]), pack2<OutT>(v[8 * j + 2], v[8 * j + 3]),
+                           pack2<OutT>(v[8 * j + 4], v[8 * j + 5]), pack2<OutT>(v[8 * j + 6], v[8 * j + 7]));
+          fence_proxy_async_smem();
+          __syncwarp();
+          if (lane == 0 && n0 + c * 32 < p.N && mb * 256 + int(rank) * 128 + quarter * 32 < p.M) {
+            tma_store_2d(&tmap_out, buf_out, n0 + c * 32, mb * 256 + int(rank) * 128 + quarter * 32);
+            tma_store_commit();
+          }
+          out_buf ^= 1;
+        } else {
+          store_chunk<OutT>(r, row, n0 + c * 32, rs, cs + c * 32, same16, p, vec_ok, acc_vec_ok);
+        }
       }
       tc_fence_before();
       __syncwarp();
@@ -770,6 +811,7 @@ a8w8_umma_pair_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_c
           *reinterpret_cast<volatile unsigned long long*>(p.sk_flags + slot_of(h) * 8 + my_flag) = 0ull;
       }
     }
+    if (lane == 0) tma_store_wait_all<0>();  // this warp's output stores have left shared memory and are complete
   }
 
   // -------------------------------- teardown --------------------------------
@@ -893,11 +935,11 @@ inline unsigned long long next_sk_epoch() {
 template <typename OutT, int BN, bool SK = false>
 int launch_pair(const int8_t* a, int64_t lda, const int8_t* b, int64_t ldb, A8W8Params p, cudaStream_t st,
                 void* workspace = nullptr) {
-  constexpr int kBudget = 212 * 1024;
+  constexpr int kBudget = 196 * 1024;  // for the operand ring; 16 KB more hold the output staging buffers
   constexpr int STAGES = kBudget / (kBM * kBK + (BN / 2) * kBK) < 8 ? kBudget / (kBM * kBK + (BN / 2) * kBK) : 8;
   using L = PairSmem<BN, STAGES>;
   static_assert(L::kDynamicBytes <= 227 * 1024, "shared memory budget");
-  static_assert(L::kStageBytes % 1024 == 0 && L::kABytes % 1024 == 0, "tiles must stay 1024-byte aligned");
+  static_assert(L::kStageBytes % 1024 == 0 && L::kABytes % 1024 == 0 && L::kOutOff % 1024 == 0, "tiles must stay 1024-byte aligned");
   static_assert(BN % 32 == 0 && BN <= 256, "pair tile width");
   auto kern = a8w8_umma_pair_kernel<OutT, BN, STAGES, SK>;
   static std::once_flag once[64];
@@ -909,9 +951,16 @@ int launch_pair(const int8_t* a, int64_t lda, const int8_t* b, int64_t ldb, A8W8
     attr_err[dev] = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, L::kDynamicBytes);
   });
   if (attr_err[dev] != cudaSuccess) return check_cuda(attr_err[dev], "cudaFuncSetAttribute(a8w8 pair)");
-  CUtensorMap ta, tb;
+  CUtensorMap ta, tb, tout;
   if (int e = make_tmap_i8(&ta, a, p.M, p.K, lda, kBM)) return e;
   if (int e = make_tmap_i8(&tb, b, p.N, p.K, ldb, BN / 2)) return e;
+  // output blocks of 32 rows x 32 columns (64 bytes per row) for the epilogue's TMA stores, where the output allows it
+  p.out_tma = (reinterpret_cast<uintptr_t>(p.out) % 16 == 0) && ((p.ldo * int64_t(sizeof(OutT))) % 16 == 0);
+  if (p.out_tma) {
+    if (int e = make_tmap_2d(&tout, int(sizeof(OutT)), p.out, p.M, p.N, p.ldo * int64_t(sizeof(OutT)), 32, 32, /*swizzle=*/2)) return e;
+  } else {
+    tout = ta;  // never used
+  }
   p.tiles_m = (p.M + 255) / 256;
   p.tiles_n = (p.N + BN - 1) / BN;
   p.k_blocks = (p.K + kBK - 1) / kBK;
@@ -930,7 +979,7 @@ int launch_pair(const int8_t* a, int64_t lda, const int8_t* b, int64_t ldb, A8W8
     p.sk_partials = reinterpret_cast<int32_t*>(static_cast<uint8_t*>(workspace) + kSkFlagBytes);
     p.sk_epoch = next_sk_epoch();
   }
-  kern<<<2 * pairs, kThreads, L::kDynamicBytes, st>>>(ta, tb, p);
+  kern<<<2 * pairs, kThreads, L::kDynamicBytes, st>>>(ta, tb, tout, p);
   return check_cuda(cudaGetLastError(), "a8w8 tcgen05 (CTA pair) launch");
 }
 
