@@ -923,7 +923,7 @@ def run_case(args):
         # Mixtral-8x7B-shaped expert layer (gate/up): E = 8, top-2, K = 4096 -> N = 28672, int8 weights
         from flashnn_b200.workloads import make_moe_case
         m, n, k = args.m or 64, args.n or 28672, args.k or 4096
-        e, top_k, bm = 8, 2, (16 if m <= 64 else 128)
+        e, top_k, bm = 8, 2, args.bm or (16 if m <= 64 else 128)
         c = {kk: v.to(device) for kk, v in make_moe_case(m, e, n, k, top_k, bm, seed=0).items()}
         out = torch.empty(m, top_k, n, dtype=torch.bfloat16, device=device)
         fn = lambda: flashnn_b200.fused_moe_a8w8_forward(c["a"], c["b"], out, c["alpha_row"], c["alpha_col"], c["topk_w"],
@@ -973,6 +973,7 @@ def main():
                     help="run one kernel only (profiling / A-B timing), the reference's Triton kernels, or the reference's shape sweep")
     ap.add_argument("--tile", type=int, default=0, help="with --case a8w8: force this CTA-pair tile width (tuning)")
     ap.add_argument("--balanced", type=int, default=0, help="with --case a8w8: 1 forces, 2 forbids the K-balanced mode of the CTA-pair kernel")
+    ap.add_argument("--bm", type=int, default=0, help="with --case moe: slots per block (default 16 up to 64 tokens, else 128)")
     ap.add_argument("--group", type=int, default=0, help="with --case wog: scale group size (-1: per channel)")
     ap.add_argument("--m", type=int)
     ap.add_argument("--n", type=int)

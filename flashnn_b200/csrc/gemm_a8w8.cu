@@ -427,16 +427,20 @@ a8w8_umma_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_consta
 // takes the head [0, sk_units) of tile i, so all heads advance through K in step, like whole tiles do (which is what
 // keeps the operand re-reads in L2); the remaining pairs walk their share of the tails and hand each piece over.
 // The whole rounds follow, for every pair alike, and hide the longer epilogue of a head behind their MMAs.
-template <bool SK> struct PairWork {
+template <bool SK, bool MOE = false> struct PairWork {
   int tile, kb0, kb1;  // the current piece: K blocks [kb0, kb1) of a tile
   int slot;            // workspace slot a tail piece is handed over in, -1 for any other piece
   bool head;           // head of a shared tile: its epilogue adds the tail pieces
   int next_plain, step, num_tiles, k_blocks;
   int pair, units, tail, pos, pos_end, next_slot;
+  int tiles_m, tiles_n, rows_in_use;  // fused MoE: row tiles past the slots in use are left out
   bool head_pending;
   __device__ __forceinline__ PairWork(const A8W8Params& p, int pair_id, int num_pairs) {
     k_blocks = p.k_blocks;
     num_tiles = p.tiles_m * p.tiles_n;
+    tiles_m = p.tiles_m;
+    tiles_n = p.tiles_n;
+    rows_in_use = MOE ? __ldg(p.num_post_padded) : 0;
     step = num_pairs;
     next_plain = pair_id;
     tile = kb0 = kb1 = 0;
@@ -479,11 +483,17 @@ template <bool SK> struct PairWork {
       slot = next_slot++;
       return true;
     }
-    tile = next_plain;
-    next_plain += step;
     kb0 = 0;
     kb1 = k_blocks;
-    return tile < num_tiles;
+    while (true) {
+      tile = next_plain;
+      next_plain += step;
+      if (tile >= num_tiles) return false;
+      if (!MOE) return true;
+      int mb, nb;
+      tile_coords(tile, tiles_m, tiles_n, mb, nb);
+      if (mb * 256 < rows_in_use) return true;
+    }
   }
 };
 
@@ -526,7 +536,9 @@ template <int BN, int STAGES> struct PairSmem {
   static constexpr int kDynamicBytes = kTotal + 1024;
 };
 
-template <typename OutT, int BN, int STAGES, bool SK>
+// MOE: fused-MoE mode for blocks of 256 sorted slots (A8W8Params, "Fused-MoE mode"): a pair tile is one block, whose
+// expert picks the weight rows and column scales; the epilogue scatters each slot's row to its (token, choice) index.
+template <typename OutT, int BN, int STAGES, bool SK, bool MOE = false>
 __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(kThreads, 1)
 a8w8_umma_pair_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ CUtensorMap tmap_b,
                       const __grid_constant__ CUtensorMap tmap_out, const A8W8Params p) {
@@ -584,10 +596,12 @@ a8w8_umma_pair_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_c
     uint32_t phase = 0;
     long long issued = 0;
     bool ok = true;
-    PairWork<SK> w(p, pair_id, num_pairs);
+    PairWork<SK, MOE> w(p, pair_id, num_pairs);
     while (ok && w.next()) {
       int mb, nb;
       tile_coords(w.tile, p.tiles_m, p.tiles_n, mb, nb);
+      // fused MoE: the tile's weights are rows [e * N + nb * BN, ...) of the expert stack
+      const int b_row = nb * BN + int(rank) * (BN / 2) + (MOE ? __ldg(p.expert_ids + (mb * 256) / p.block_m) * p.N : 0);
       for (int kb = w.kb0; kb < w.kb1; ++kb) {
         ok = mbar_wait_bounded(&empty_bar[stage], phase ^ 1, abort_flag);
         ok = __all_sync(0xffffffffu, ok);
@@ -600,7 +614,7 @@ a8w8_umma_pair_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_c
           const uint32_t full_in_leader = map_to_cta(smem_u32(&full_bar[stage]), 0);
           if (rank == 0) mbar_expect_tx(&full_bar[stage], 2 * L::kStageBytes);
           tma_load_2d_pair(sa, &tmap_a, full_in_leader, kb * kBK, mb * 256 + int(rank) * 128);
-          tma_load_2d_pair(sa + L::kABytes, &tmap_b, full_in_leader, kb * kBK, nb * BN + int(rank) * (BN / 2));
+          tma_load_2d_pair(sa + L::kABytes, &tmap_b, full_in_leader, kb * kBK, b_row);
           ++issued;
         }
         __syncwarp();
@@ -624,7 +638,7 @@ a8w8_umma_pair_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_c
       int local = 0;
       bool ok = true;
       bool issued_any = false;
-      PairWork<SK> w(p, pair_id, num_pairs);
+      PairWork<SK, MOE> w(p, pair_id, num_pairs);
       for (; ok && w.next(); ++local) {
         const int buf = local & 1;
         const uint32_t acc_phase = (local >> 1) & 1;
@@ -676,7 +690,7 @@ a8w8_umma_pair_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_c
     const bool acc_vec_ok = p.acc_out && (p.ldacc % 4 == 0) && (reinterpret_cast<uintptr_t>(p.acc_out) % 16 == 0);
     int local = 0;
     bool ok = true;
-    PairWork<SK> w(p, pair_id, num_pairs);
+    PairWork<SK, MOE> w(p, pair_id, num_pairs);
     uint8_t* out_stage = smem + L::kOutOff + quarter * 4096;            // this warp's two output staging buffers
     int out_buf = 0;
     const int my_flag = int(rank) * 4 + quarter;                        // this warp's flag word within a pair's eight
@@ -697,9 +711,21 @@ a8w8_umma_pair_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_c
       // slot of the piece of this tile that tail-sharing pair h computed: its pieces are of consecutive tiles
       auto slot_of = [&](int h) { return h * p.sk_slots + (w.tile - (h * p.sk_tail_units) / tail_blocks); };
       const int n0 = nb * BN;
+      const int64_t col_base = MOE ? int64_t(__ldg(p.expert_ids + (mb * 256) / p.block_m)) * p.col_stride_e : 0;
       for (int j = lane; j < BN; j += 32)
-        cs[j] = (n0 + j < p.N) ? load_as_f32(p.alpha_col, p.col_dtype, n0 + j) : 0.f;
-      const float rs = (row < p.M) ? load_as_f32(p.alpha_row, p.row_dtype, row) : 0.f;
+        cs[j] = (n0 + j < p.N) ? load_as_f32(p.alpha_col, p.col_dtype, col_base + n0 + j) : 0.f;
+      float rs = 0.f, rw = 1.f;
+      int64_t out_row = -1;  // fused MoE: the flat (token, choice) index this slot writes, or -1
+      if (MOE) {
+        const int flat = __ldg(p.sorted_ids + row);
+        if (flat >= 0 && flat < p.num_valid) {
+          out_row = flat;
+          rs = load_as_f32(p.alpha_row, p.row_dtype, flat / p.top_k);
+          if (p.mul_w) rw = load_as_f32(p.topk_w, p.topk_w_dtype, flat);
+        }
+      } else {
+        rs = (row < p.M) ? load_as_f32(p.alpha_row, p.row_dtype, row) : 0.f;
+      }
       __syncwarp();
 
       ok = mbar_wait_bounded(&tmem_full_bar[buf], acc_phase, abort_flag);
@@ -770,7 +796,9 @@ a8w8_umma_pair_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_c
             }
           }
         }
-        if (p.out_tma) {
+        if (MOE) {
+          if (out_row >= 0) store_chunk_moe<OutT>(r, out_row, n0 + c * 32, rs, rw, p.mul_w != 0, cs + c * 32, p, vec_ok);
+        } else if (p.out_tma) {
           // The 32 x 32 block of outputs goes through shared memory and leaves as one TMA store: whole 64-byte row
           // pieces instead of 16 bytes per lane and row.  Rows of 64 bytes in the 64-byte swizzle pattern (16-byte
           // piece j of row l sits at piece j ^ ((l >> 1) & 3)), so the 32 lanes' stores spread over all banks; the
@@ -1152,10 +1180,44 @@ int launch_moe_rows(const int8_t* a_sorted, int64_t EM, const int8_t* b, int64_t
   return launch_moe<OutT, BN, kBudget / ((kBM + BN) * kBK) < 8 ? kBudget / ((kBM + BN) * kBK) : 8, kBM>(a_sorted, EM, b, E, p, st);
 }
 
+// Blocks of 256 sorted slots (or a multiple): one block is one 256-row tile of the CTA-pair kernel.
+template <typename OutT>
+int launch_moe_pair(const int8_t* a_sorted, int64_t EM, const int8_t* b, int64_t E, A8W8Params p, cudaStream_t st) {
+  constexpr int BN = 256;
+  constexpr int kBudget = 196 * 1024;
+  constexpr int STAGES = kBudget / (kBM * kBK + (BN / 2) * kBK);
+  using L = PairSmem<BN, STAGES>;
+  static_assert(L::kDynamicBytes <= 227 * 1024, "shared memory budget");
+  auto kern = a8w8_umma_pair_kernel<OutT, BN, STAGES, false, true>;
+  static std::once_flag once[64];
+  static cudaError_t attr_err[64];  // per device, so that a failure is reported on every call and not only the first
+  int dev = 0;
+  cudaGetDevice(&dev);
+  dev &= 63;
+  std::call_once(once[dev], [&] {
+    attr_err[dev] = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, L::kDynamicBytes);
+  });
+  if (attr_err[dev] != cudaSuccess) return check_cuda(attr_err[dev], "cudaFuncSetAttribute(fused moe a8w8, CTA pair)");
+  CUtensorMap ta, tb;
+  if (int e = make_tmap_i8(&ta, a_sorted, EM, p.K, p.K, kBM)) return e;
+  if (int e = make_tmap_i8(&tb, b, E * p.N, p.K, p.K, BN / 2)) return e;
+  p.tiles_m = int(EM / 256);
+  p.tiles_n = (p.N + BN - 1) / BN;
+  p.k_blocks = (p.K + kBK - 1) / kBK;
+  p.out_tma = 0;
+  const int tiles = p.tiles_m * p.tiles_n;
+  const int pairs = tiles < sm_count() / 2 ? tiles : sm_count() / 2;
+  kern<<<2 * pairs, kThreads, L::kDynamicBytes, st>>>(ta, tb, ta, p);
+  return check_cuda(cudaGetLastError(), "fused moe a8w8 (CTA pair) launch");
+}
+
 template <typename OutT>
 int dispatch_moe(const int8_t* a_sorted, int64_t EM, const int8_t* b, int64_t E, const A8W8Params& p, cudaStream_t st) {
   // the widest tile that still gives every SM work; small problems stream the expert weights with 64-wide tiles
   const int sms = sm_count();
+  // blocks of 256 slots with enough tiles for every CTA pair: the CTA-pair kernel (a third less operand traffic per MMA)
+  if (p.block_m % 256 == 0 && (EM / 256) * ((p.N + 255) / 256) >= sms / 2)
+    return launch_moe_pair<OutT>(a_sorted, EM, b, E, p, st);
   const int64_t tiles_m = EM / p.tile_rows;
   if (tiles_m * ((p.N + 255) / 256) >= sms) return launch_moe_rows<OutT, 256>(a_sorted, EM, b, E, p, st);
   if (tiles_m * ((p.N + 127) / 128) >= sms) return launch_moe_rows<OutT, 128>(a_sorted, EM, b, E, p, st);

@@ -34,6 +34,22 @@ def test_matches_oracle(out_ty, m, e, n, k, top_k, bm, mul):
     assert torch.equal(out.view(torch.int16), ref.view(torch.int16))
 
 
+# blocks of 256 slots and enough tiles for every CTA pair: the CTA-pair kernel's fused-MoE mode (ragged N, an expert
+# count that leaves some experts with an odd number of half-filled blocks, with and without the routing weights)
+@pytest.mark.parametrize("out_ty", [torch.float16, torch.bfloat16])
+@pytest.mark.parametrize("m,e,n,k,top_k,mul", [(2000, 4, 1024, 512, 2, True), (1800, 6, 1008, 272, 2, False),
+                                               (4400, 8, 768, 128, 1, True)])
+def test_blocks_of_256_on_the_cta_pair_kernel(out_ty, m, e, n, k, top_k, mul):
+    bm = 256
+    c = make_moe_case(m, e, n, k, top_k, bm, seed=m + e + n)
+    assert (c["sorted_ids"].numel() // 256) * ((n + 255) // 256) >= 74
+    out = run(c, top_k, bm, mul, out_ty, m, n)
+    ref = O.fused_moe_a8w8(c["a"], c["b"], c["alpha_row"], c["alpha_col"], c["topk_w"], c["sorted_ids"], c["expert_ids"],
+                           c["npp"], m * top_k, mul, top_k, bm, out_ty, C=torch.full((m, top_k, n), 7.0, dtype=out_ty))
+    assert torch.equal(out.view(torch.int16), ref.view(torch.int16))
+
+
+
 def test_sixteen_bit_scales_and_dropped_tokens():
     """fp16 scales; some slots in use are padding-valued in the middle of a block (tokens dropped by the router)."""
     m, e, n, k, top_k, bm = 40, 4, 64, 256, 2, 16
