@@ -936,7 +936,7 @@ def run_case(args):
         # the same expert layer with packed-int4 weights and per-group (128) bf16 scales
         from flashnn_b200.workloads import make_moe_w4_case
         m, n, k = args.m or 64, args.n or 28672, args.k or 4096
-        e, top_k, bm = 8, 2, (16 if m <= 64 else 64)
+        e, top_k, bm = 8, 2, args.bm or (16 if m <= 64 else 64)
         c = {kk: (None if v is None else v.to(device)) for kk, v in
              make_moe_w4_case(m, e, n, k, top_k, bm, seed=0, dtype=torch.bfloat16, group=128).items() if kk != "w4"}
         out = torch.empty(m, top_k, n, dtype=torch.bfloat16, device=device)
@@ -973,7 +973,7 @@ def main():
                     help="run one kernel only (profiling / A-B timing), the reference's Triton kernels, or the reference's shape sweep")
     ap.add_argument("--tile", type=int, default=0, help="with --case a8w8: force this CTA-pair tile width (tuning)")
     ap.add_argument("--balanced", type=int, default=0, help="with --case a8w8: 1 forces, 2 forbids the K-balanced mode of the CTA-pair kernel")
-    ap.add_argument("--bm", type=int, default=0, help="with --case moe: slots per block (default 16 up to 64 tokens, else 128)")
+    ap.add_argument("--bm", type=int, default=0, help="with --case moe / moe4: slots per block (default 16 up to 64 tokens, else 128 / 64)")
     ap.add_argument("--group", type=int, default=0, help="with --case wog: scale group size (-1: per channel)")
     ap.add_argument("--m", type=int)
     ap.add_argument("--n", type=int)

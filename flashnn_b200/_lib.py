@@ -43,6 +43,11 @@ SIGNATURES = {
                                        _c.c_void_p, _c.c_void_p, _c.c_int, _c.c_int64, _c.c_void_p, _c.c_int,
                                        _c.c_void_p, _c.c_int64, _c.c_void_p, _c.c_void_p, _c.c_int64, _c.c_int, _c.c_int,
                                        _c.c_int, _c.c_void_p, _c.c_int, _c.c_int64, _c.c_void_p]),
+    "fnn_fused_moe_a16w4_ws": (_c.c_int, [_c.c_void_p, _c.c_int, _c.c_int64, _c.c_void_p, _c.c_int64, _c.c_int64, _c.c_int64,
+                                          _c.c_void_p, _c.c_void_p, _c.c_int, _c.c_int64, _c.c_void_p, _c.c_int,
+                                          _c.c_void_p, _c.c_int64, _c.c_void_p, _c.c_void_p, _c.c_int64, _c.c_int, _c.c_int,
+                                          _c.c_int, _c.c_void_p, _c.c_int, _c.c_int64, _c.c_void_p, _c.c_size_t, _c.c_void_p]),
+    "fnn_fused_moe_a16w4_workspace_bytes": (_c.c_size_t, [_c.c_int64, _c.c_int64, _c.c_int64, _c.c_int, _c.c_int]),
     "fnn_set_option": (_c.c_int, [_c.c_int, _c.c_int]),
     "fnn_get_option": (_c.c_int, [_c.c_int]),
     "fnn_rms_norm_dquant": (_c.c_int, [_c.c_void_p, _c.c_int, _c.c_int64, _c.c_int64, _c.c_int64, _c.c_void_p, _c.c_int,

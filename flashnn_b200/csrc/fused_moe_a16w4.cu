@@ -22,6 +22,7 @@
 
 #include "async_copy.cuh"
 #include "common.cuh"
+#include "weight_only.cuh"
 
 namespace fnn {
 namespace {
@@ -314,13 +315,14 @@ int dispatch_moe_w4(const MoeW4Params& p, cudaStream_t st) {
 }  // namespace
 }  // namespace fnn
 
-extern "C" int fnn_fused_moe_a16w4(const void* a, int a_dtype, int64_t lda, const void* b, int64_t E, int64_t N, int64_t K,
-                                   const void* scale, const void* zero_points, int scale_dtype, int64_t group_size,
-                                   const void* topk_weights, int topk_dtype, const int32_t* sorted_token_ids, int64_t EM,
-                                   const int32_t* expert_ids, const int32_t* num_tokens_post_padded,
-                                   int64_t num_valid_tokens, int top_k, int block_m, int mul_routed_weight, void* out,
-                                   int out_dtype, int64_t ldo, void* stream) {
-  using namespace fnn;
+namespace fnn {
+namespace {
+int fused_moe_a16w4_impl(const void* a, int a_dtype, int64_t lda, const void* b, int64_t E, int64_t N, int64_t K,
+                         const void* scale, const void* zero_points, int scale_dtype, int64_t group_size,
+                         const void* topk_weights, int topk_dtype, const int32_t* sorted_token_ids, int64_t EM,
+                         const int32_t* expert_ids, const int32_t* num_tokens_post_padded,
+                         int64_t num_valid_tokens, int top_k, int block_m, int mul_routed_weight, void* out,
+                         int out_dtype, int64_t ldo, void* workspace, size_t workspace_bytes, void* stream) {
   if (E <= 0 || N < 0 || K <= 0 || EM < 0 || lda < K || ldo < N || num_valid_tokens < 0 || top_k <= 0 || block_m <= 0 || group_size < 0)
     return fail(FNN_ERR_SHAPE, "fused_moe_a16w4: E=%lld N=%lld K=%lld EM=%lld lda=%lld ldo=%lld top_k=%d block_m=%d group=%lld",
                 (long long)E, (long long)N, (long long)K, (long long)EM, (long long)lda, (long long)ldo, top_k, block_m, (long long)group_size);
@@ -342,6 +344,16 @@ extern "C" int fnn_fused_moe_a16w4(const void* a, int a_dtype, int64_t lda, cons
     return fail(FNN_ERR_NULL_POINTER, "fused_moe_a16w4: null tensor pointer");
   if (K % 16 != 0 || reinterpret_cast<uintptr_t>(a) % 16 != 0 || lda % 8 != 0 || reinterpret_cast<uintptr_t>(b) % 16 != 0)
     return fail(FNN_ERR_ALIGNMENT, "fused_moe_a16w4: K must be a multiple of 16, lda of 8, and the operands 16-byte aligned");
+  cudaStream_t st = static_cast<cudaStream_t>(stream);
+  // Blocks of 256 slots (or a multiple) with a tile for every CTA pair and a workspace for the expert-sorted copy of the
+  // token rows: the tcgen05 prefill kernels of the weight-only GEMM in their fused-MoE mode.
+  if (workspace && block_m % 256 == 0 && (EM / 256) * ((N + 255) / 256) >= sm_count() / 2) {
+    const int r = weight_only_moe_prefill(a, a_dtype, lda, b, int(E), int(N), int(K), scale, zero_points, scale_dtype,
+                                          int(group_size), topk_weights, topk_dtype, sorted_token_ids, int(EM), expert_ids,
+                                          num_tokens_post_padded, int(num_valid_tokens), top_k, block_m,
+                                          mul_routed_weight ? 1 : 0, out, ldo, workspace, workspace_bytes, st);
+    if (r >= 0) return r;
+  }
   MoeW4Params p{};
   p.a = a; p.lda = lda; p.b = static_cast<const uint8_t*>(b); p.scale = scale; p.zp = zero_points; p.topk_w = topk_weights;
   p.sorted_ids = sorted_token_ids; p.expert_ids = expert_ids; p.npp = num_tokens_post_padded; p.out = out; p.ldo = ldo;
@@ -350,7 +362,6 @@ extern "C" int fnn_fused_moe_a16w4(const void* a, int a_dtype, int64_t lda, cons
   p.group = int(group_size); p.groups = group_size > 0 ? int(K / group_size) : 1;
   p.tile_rows = block_m < 64 ? block_m : 64;
   p.tiles_per_block = (block_m + p.tile_rows - 1) / p.tile_rows;
-  cudaStream_t st = static_cast<cudaStream_t>(stream);
 #define FNN_MOE_W4(T)                                                  \
   do {                                                                 \
     if (p.tile_rows <= 16) return dispatch_moe_w4<T, 16>(p, st);       \
@@ -360,4 +371,34 @@ extern "C" int fnn_fused_moe_a16w4(const void* a, int a_dtype, int64_t lda, cons
   if (a_dtype == FNN_F16) FNN_MOE_W4(__half);
   FNN_MOE_W4(__nv_bfloat16);
 #undef FNN_MOE_W4
+}
+}  // namespace
+}  // namespace fnn
+
+extern "C" int fnn_fused_moe_a16w4(const void* a, int a_dtype, int64_t lda, const void* b, int64_t E, int64_t N, int64_t K,
+                                   const void* scale, const void* zero_points, int scale_dtype, int64_t group_size,
+                                   const void* topk_weights, int topk_dtype, const int32_t* sorted_token_ids, int64_t EM,
+                                   const int32_t* expert_ids, const int32_t* num_tokens_post_padded,
+                                   int64_t num_valid_tokens, int top_k, int block_m, int mul_routed_weight, void* out,
+                                   int out_dtype, int64_t ldo, void* stream) {
+  return fnn::fused_moe_a16w4_impl(a, a_dtype, lda, b, E, N, K, scale, zero_points, scale_dtype, group_size, topk_weights,
+                                   topk_dtype, sorted_token_ids, EM, expert_ids, num_tokens_post_padded, num_valid_tokens,
+                                   top_k, block_m, mul_routed_weight, out, out_dtype, ldo, nullptr, 0, stream);
+}
+
+extern "C" size_t fnn_fused_moe_a16w4_workspace_bytes(int64_t EM, int64_t K, int64_t group_size, int has_zero_points,
+                                                      int block_m) {
+  if (EM <= 0 || K <= 0 || block_m <= 0 || block_m % 256 != 0) return 0;
+  return fnn::weight_only_moe_prefill_workspace(EM, K, group_size, has_zero_points != 0);
+}
+
+extern "C" int fnn_fused_moe_a16w4_ws(const void* a, int a_dtype, int64_t lda, const void* b, int64_t E, int64_t N, int64_t K,
+                                      const void* scale, const void* zero_points, int scale_dtype, int64_t group_size,
+                                      const void* topk_weights, int topk_dtype, const int32_t* sorted_token_ids, int64_t EM,
+                                      const int32_t* expert_ids, const int32_t* num_tokens_post_padded,
+                                      int64_t num_valid_tokens, int top_k, int block_m, int mul_routed_weight, void* out,
+                                      int out_dtype, int64_t ldo, void* workspace, size_t workspace_bytes, void* stream) {
+  return fnn::fused_moe_a16w4_impl(a, a_dtype, lda, b, E, N, K, scale, zero_points, scale_dtype, group_size, topk_weights,
+                                   topk_dtype, sorted_token_ids, EM, expert_ids, num_tokens_post_padded, num_valid_tokens,
+                                   top_k, block_m, mul_routed_weight, out, out_dtype, ldo, workspace, workspace_bytes, stream);
 }

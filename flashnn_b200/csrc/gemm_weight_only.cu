@@ -59,8 +59,30 @@ struct PfParams {
   int M, N, K;
   int group;  // 0: per-channel scales; else the K-group size (a multiple of the 64-wide K block)
   int tiles_m, tiles_n, k_blocks;
+  int moe;  // fused-MoE mode, see PfMoe
   int* status;
 };
+
+// Fused MoE (PfParams::moe != 0): the activations are the expert-sorted copy of the token rows [EM, K] (M = EM), a
+// 256-row tile is one block of sorted slots (block_m is a multiple of 256) whose expert picks the weight rows and the
+// scales ([E, N], or [E, N, K / group] for group-wise ones); the epilogue multiplies by the routing weight and scatters
+// each slot's row to its flat (token, choice) index.  Tiles past the slots in use are computed on whatever the copy
+// holds and never stored.  A kernel parameter of its own: the dense kernels' parameter block stays as small as it was
+// (growing it cost the group-wise kernel 4 % through local-memory copies of the block).
+struct PfMoe {
+  int num_experts, top_k, num_valid, mul_w, block_m, topk_dtype;
+  const int32_t* sorted_ids;
+  const int32_t* expert_ids;
+  const int32_t* npp;
+  const void* topk_w;
+};
+
+// Expert of the row tile mb, or -1 where the tile lies past the slots in use (or names no expert).
+__device__ __forceinline__ int pf_moe_expert(const PfMoe& m, int mb) {
+  if (mb * 256 >= __ldg(m.npp)) return -1;
+  const int e = __ldg(m.expert_ids + (mb * 256) / m.block_m);
+  return (e >= 0 && e < m.num_experts) ? e : -1;
+}
 
 template <int BITS> struct PfSmem {
   static constexpr int kXBytes = kTM * kTK * 2;                                      // 16 KB activations
@@ -198,10 +220,10 @@ __device__ __forceinline__ void pf_init_bars(const PfBars& b, int epi_arrivals, 
 }
 
 // warp 0 of both CTAs: TMA loads of this CTA's 128 activation rows and its raw weight bytes, one K block per stage
-template <int BITS, int BN = kTN>
+template <int BITS, int BN = kTN, bool MOE = false>
 __device__ __forceinline__ void pf_producer(uint8_t* smem, const PfBars& b, const CUtensorMap* tmap_x,
                                             const CUtensorMap* tmap_w, const PfParams& p, uint32_t rank, int pair_id,
-                                            int num_pairs, volatile int* abort_flag) {
+                                            int num_pairs, volatile int* abort_flag, const PfMoe* moe = nullptr) {
   using L = PfSmem<BITS>;
   const int num_tiles = p.tiles_m * p.tiles_n;
   const bool leader_lane = elect_one();
@@ -212,7 +234,11 @@ __device__ __forceinline__ void pf_producer(uint8_t* smem, const PfBars& b, cons
   for (int t = pair_id; t < num_tiles && ok; t += num_pairs) {
     int mb, nb;
     pf_tile_coords(t, p.tiles_m, p.tiles_n, mb, nb);
-    const int w_row = (BITS == 8) ? nb * BN + int(rank) * (BN / 2) : (nb * BN + int(rank) * (BN / 2)) / 2;
+    int w_row = (BITS == 8) ? nb * BN + int(rank) * (BN / 2) : (nb * BN + int(rank) * (BN / 2)) / 2;
+    if (MOE) {  // the expert's rows of the weight stack (a tile that is not in use reads expert 0's)
+      const int e = pf_moe_expert(*moe, mb);
+      w_row += (e < 0 ? 0 : e) * ((BITS == 8) ? p.N : p.N / 2);
+    }
     for (int kb = 0; kb < p.k_blocks; ++kb) {
       ok = mbar_wait_bounded(&b.empty[stage], phase ^ 1, abort_flag);
       ok = __all_sync(0xffffffffu, ok);
@@ -403,7 +429,7 @@ __device__ __forceinline__ void pf_converters(uint8_t* smem, const PfBars& b, co
 template <typename T, int BITS, int BN>
 __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(kPfThreads, 1)
 wo_umma_pair_kernel(const __grid_constant__ CUtensorMap tmap_x, const __grid_constant__ CUtensorMap tmap_w,
-                    const PfParams p) {
+                    const PfParams p, const __grid_constant__ PfMoe moe) {
   using L = PfSmem<BITS>;
   extern __shared__ uint8_t smem_raw[];
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
@@ -439,7 +465,8 @@ wo_umma_pair_kernel(const __grid_constant__ CUtensorMap tmap_x, const __grid_con
   if (warp < 4) {
     asm volatile("setmaxnreg.dec.sync.aligned.u32 40;");
     if (warp == 0) {
-      pf_producer<BITS, BN>(smem, b, &tmap_x, &tmap_w, p, rank, pair_id, num_pairs, abort_flag);
+      if (p.moe) pf_producer<BITS, BN, true>(smem, b, &tmap_x, &tmap_w, p, rank, pair_id, num_pairs, abort_flag, &moe);
+      else pf_producer<BITS, BN, false>(smem, b, &tmap_x, &tmap_w, p, rank, pair_id, num_pairs, abort_flag);
     } else if (warp == 1) {
       if (rank == 0) pf_mma<T, BITS, BN>(smem, b, p, tmem_base, pair_id, num_pairs, p.k_blocks, abort_flag);
       else pf_relay(b, p, pair_id, num_pairs, abort_flag);
@@ -462,14 +489,29 @@ wo_umma_pair_kernel(const __grid_constant__ CUtensorMap tmap_x, const __grid_con
       const uint32_t acc_phase = (local >> 1) & 1;
       const int row = mb * 256 + int(rank) * kTM + quarter * 32 + lane;
       const int n0 = nb * BN;
+      const int expert = p.moe ? pf_moe_expert(moe, mb) : 0;
+      const int64_t sbase = int64_t(expert < 0 ? 0 : expert) * p.N;  // fused MoE: the expert's scales
       for (int j = lane; j < BN; j += 32) {
-        const bool in = n0 + j < p.N;
-        const float s = in ? load_as_f32(p.scale, p.scale_dtype, n0 + j) : 0.f;
+        const bool in = n0 + j < p.N && expert >= 0;
+        const float s = in ? load_as_f32(p.scale, p.scale_dtype, sbase + n0 + j) : 0.f;
         cs[j] = s;
-        cz[j] = (in && p.zp) ? s * load_as_f32(p.zp, p.scale_dtype, n0 + j) : 0.f;
+        cz[j] = (in && p.zp) ? s * load_as_f32(p.zp, p.scale_dtype, sbase + n0 + j) : 0.f;
         cb[j] = (in && p.bias) ? load_as_f32(p.bias, p.bias_dtype, n0 + j) : 0.f;
       }
       const float xs = (p.zp && row < p.M) ? p.xsum[row] : 0.f;
+      // where this thread's row goes: its own row, or (fused MoE) the flat (token, choice) index of its slot
+      int64_t out_row = row < p.M ? row : -1;
+      float rw = 1.f;
+      if (p.moe) {
+        out_row = -1;
+        if (expert >= 0) {
+          const int flat = __ldg(moe.sorted_ids + row);
+          if (flat >= 0 && flat < moe.num_valid) {
+            out_row = flat;
+            if (moe.mul_w) rw = load_as_f32(moe.topk_w, moe.topk_dtype, flat);
+          }
+        }
+      }
       __syncwarp();
 
       ok = mbar_wait_bounded(&b.tmem_full[buf], acc_phase, abort_flag);
@@ -486,12 +528,12 @@ wo_umma_pair_kernel(const __grid_constant__ CUtensorMap tmap_x, const __grid_con
         tmem_ld_32x32(taddr + c * 32, r);
         tc_wait_ld();
         const int col0 = n0 + c * 32;
-        if (row < p.M && col0 < p.N) {
+        if (out_row >= 0 && col0 < p.N) {
           float v[32];
 #pragma unroll
           for (int j = 0; j < 32; ++j)
-            v[j] = fmaf(__uint_as_float(r[j]), cs[c * 32 + j], fmaf(-xs, cz[c * 32 + j], cb[c * 32 + j]));
-          T* orow = out + int64_t(row) * p.ldo + col0;
+            v[j] = rw * fmaf(__uint_as_float(r[j]), cs[c * 32 + j], fmaf(-xs, cz[c * 32 + j], cb[c * 32 + j]));
+          T* orow = out + out_row * p.ldo + col0;
           if (col0 + 32 <= p.N && vec_ok) {
 #pragma unroll
             for (int j = 0; j < 32; j += 8)
@@ -556,10 +598,10 @@ __device__ __forceinline__ void unpack2(uint64_t v, float& lo, float& hi) {
 
 // BN: channels per pair tile, 256 or 128; the 512 TMEM columns hold NBUF = 512 / BN accumulators, so that many scale
 // groups are in flight between the MMA warp and the epilogue warps.
-template <typename T, int BITS, bool HAS_ZP, int BN>
+template <typename T, int BITS, bool HAS_ZP, int BN, bool MOE>
 __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(kPgThreads, 1)
 wo_umma_pair_group_kernel(const __grid_constant__ CUtensorMap tmap_x, const __grid_constant__ CUtensorMap tmap_w,
-                          const PfParams p) {
+                          const PfParams p, const __grid_constant__ PfMoe moe) {
   using L = PfSmem<BITS>;
   extern __shared__ uint8_t smem_raw[];
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
@@ -598,7 +640,7 @@ wo_umma_pair_group_kernel(const __grid_constant__ CUtensorMap tmap_x, const __gr
   if (warp < 4) {
     asm volatile("setmaxnreg.dec.sync.aligned.u32 40;");
     if (warp == 0) {
-      pf_producer<BITS, BN>(smem, b, &tmap_x, &tmap_w, p, rank, pair_id, num_pairs, abort_flag);
+      pf_producer<BITS, BN, MOE>(smem, b, &tmap_x, &tmap_w, p, rank, pair_id, num_pairs, abort_flag, &moe);
     } else if (warp == 1) {
       if (rank == 0) pf_mma<T, BITS, BN, NBUF, BN>(smem, b, p, tmem_base, pair_id, num_pairs, kb_per_group, abort_flag);
       else pf_relay(b, p, pair_id, num_pairs, abort_flag);
@@ -619,14 +661,16 @@ wo_umma_pair_group_kernel(const __grid_constant__ CUtensorMap tmap_x, const __gr
         int mb, nb;
         pf_tile_coords(t, p.tiles_m, p.tiles_n, mb, nb);
         const int n0 = nb * BN + c0;
+        const int expert = MOE ? pf_moe_expert(moe, mb) : 0;
         for (int g = 0; g < groups; ++g, ++seg) {
           const int slot = seg % kPgScaleStages;
           const uint32_t ph = (seg / kPgScaleStages) & 1;
           float sv[CPL], zv[CPL], bv[CPL];
 #pragma unroll
           for (int j = 0; j < CPL; ++j) {
-            const bool in = n0 + j < p.N;
-            const int64_t at = int64_t(g) * p.N + n0 + j;
+            const bool in = n0 + j < p.N && expert >= 0;
+            // dense: [K / group, N]; fused MoE: [E, N, K / group]
+            const int64_t at = MOE ? (int64_t(expert) * p.N + n0 + j) * groups + g : int64_t(g) * p.N + n0 + j;
             sv[j] = in ? load_as_f32(p.scale, p.scale_dtype, at) : 0.f;
             zv[j] = (HAS_ZP && in) ? sv[j] * load_as_f32(p.zp, p.scale_dtype, at) : 0.f;
             bv[j] = (g == 0 && p.bias && in) ? load_as_f32(p.bias, p.bias_dtype, n0 + j) : 0.f;
@@ -674,6 +718,18 @@ wo_umma_pair_group_kernel(const __grid_constant__ CUtensorMap tmap_x, const __gr
       pf_tile_coords(t, p.tiles_m, p.tiles_n, mb, nb);
       const int row = mb * 256 + int(rank) * kTM + quarter * 32 + lane;
       const int n0 = nb * BN;
+      // fused MoE: the flat (token, choice) index this thread's slot writes (-1: none) and its routing weight
+      int moe_row = -1;
+      float rw = 1.f;
+      if (MOE) {
+        if (pf_moe_expert(moe, mb) >= 0) {
+          const int flat = __ldg(moe.sorted_ids + row);
+          if (flat >= 0 && flat < moe.num_valid) {
+            moe_row = flat;
+            if (moe.mul_w) rw = load_as_f32(moe.topk_w, moe.topk_dtype, flat);
+          }
+        }
+      }
       for (int g = 0; g < groups; ++g, ++seg) {
         const int buf = seg % NBUF;
         const uint32_t seg_phase = (seg / NBUF) & 1;
@@ -728,17 +784,22 @@ wo_umma_pair_group_kernel(const __grid_constant__ CUtensorMap tmap_x, const __gr
       }
       if (!ok) break;
       // the tile's sums are complete: round once, store, and clear the sums for the next tile
-      T* orow0 = out + int64_t(row) * p.ldo + n0 + half * HC;
+      const bool row_ok = MOE ? moe_row >= 0 : row < p.M;
+      T* orow0 = out + int64_t(MOE ? (moe_row < 0 ? 0 : moe_row) : row) * p.ldo + n0 + half * HC;
 #pragma unroll
       for (int c = 0; c < HC / 32; ++c) {
         float v[32];
 #pragma unroll
         for (int j = 0; j < 32; j += 2) {
           unpack2(sum2[(c * 32 + j) >> 1], v[j], v[j + 1]);
+          if (MOE) {
+            v[j] *= rw;
+            v[j + 1] *= rw;
+          }
           sum2[(c * 32 + j) >> 1] = 0ull;
         }
         const int col0 = n0 + half * HC + c * 32;
-        if (row < p.M && col0 < p.N) {
+        if (row_ok && col0 < p.N) {
           T* orow = orow0 + c * 32;
           if (col0 + 32 <= p.N && vec_ok) {
 #pragma unroll
@@ -823,21 +884,21 @@ inline int pf_pick_bn(int M, int N, int pairs) {
 }
 
 template <typename T, int BITS, int BN>
-int launch_prefill_perch(const T* act, int64_t lda, const uint8_t* qw, PfParams p, cudaStream_t st) {
+int launch_prefill_perch(const T* act, int64_t lda, const uint8_t* qw, PfParams p, const PfMoe& moe, cudaStream_t st) {
   using L = PfSmem<BITS>;
   static std::once_flag once[64];
   static cudaError_t attr_err[64];  // per device, so that a failure is reported on every call and not only the first
   if (int e = pf_configure(wo_umma_pair_kernel<T, BITS, BN>, L::kDynamicBytes, attr_err, once)) return e;
   CUtensorMap tx, tw;
   if (int e = make_tmap_2d(&tx, 2, act, p.M, p.K, lda * 2, kTK, kTM, true)) return e;
-  const int64_t w_rows = (BITS == 8) ? p.N : p.N / 2;
+  const int64_t w_rows = int64_t((BITS == 8) ? p.N : p.N / 2) * (p.moe ? moe.num_experts : 1);
   if (int e = make_tmap_2d(&tw, 1, qw, w_rows, p.K, p.K, kTK, (BITS == 8) ? BN / 2 : BN / 4, false)) return e;
   p.tiles_m = (p.M + 255) / 256;
   p.tiles_n = (p.N + BN - 1) / BN;
   p.k_blocks = (p.K + kTK - 1) / kTK;
   const int tiles = p.tiles_m * p.tiles_n;
   const int pairs = tiles < sm_count() / 2 ? tiles : sm_count() / 2;
-  wo_umma_pair_kernel<T, BITS, BN><<<2 * pairs, kPfThreads, L::kDynamicBytes, st>>>(tx, tw, p);
+  wo_umma_pair_kernel<T, BITS, BN><<<2 * pairs, kPfThreads, L::kDynamicBytes, st>>>(tx, tw, p, moe);
   return check_cuda(cudaGetLastError(), "weight-only prefill launch");
 }
 
@@ -846,27 +907,28 @@ int launch_prefill_perch(const T* act, int64_t lda, const uint8_t* qw, PfParams 
 // the time for the same per-block barrier round: measured 676 against 865 TFLOP/s (A16W4, group 128, 2048 x 28672 x 8192).
 constexpr int kPgTile = 256;
 
-template <typename T, int BITS, bool HAS_ZP, int BN>
-int launch_prefill_group(const T* act, int64_t lda, const uint8_t* qw, PfParams p, cudaStream_t st) {
+template <typename T, int BITS, bool HAS_ZP, int BN, bool MOE>
+int launch_prefill_group(const T* act, int64_t lda, const uint8_t* qw, PfParams p, const PfMoe& moe, cudaStream_t st) {
   using L = PfSmem<BITS>;
   static std::once_flag once[64];
   static cudaError_t attr_err[64];  // per device, so that a failure is reported on every call and not only the first
-  if (int e = pf_configure(wo_umma_pair_group_kernel<T, BITS, HAS_ZP, BN>, L::kDynamicBytes, attr_err, once)) return e;
+  if (int e = pf_configure(wo_umma_pair_group_kernel<T, BITS, HAS_ZP, BN, MOE>, L::kDynamicBytes, attr_err, once)) return e;
   CUtensorMap tx, tw;
   if (int e = make_tmap_2d(&tx, 2, act, p.M, p.K, lda * 2, kTK, kTM, true)) return e;
-  const int64_t w_rows = (BITS == 8) ? p.N : p.N / 2;
+  const int64_t w_rows = int64_t((BITS == 8) ? p.N : p.N / 2) * (p.moe ? moe.num_experts : 1);
   if (int e = make_tmap_2d(&tw, 1, qw, w_rows, p.K, p.K, kTK, (BITS == 8) ? BN / 2 : BN / 4, false)) return e;
   p.tiles_m = (p.M + 255) / 256;
   p.tiles_n = (p.N + BN - 1) / BN;
   p.k_blocks = (p.K + kTK - 1) / kTK;
   const int tiles = p.tiles_m * p.tiles_n;
   const int pairs = tiles < sm_count() / 2 ? tiles : sm_count() / 2;
-  wo_umma_pair_group_kernel<T, BITS, HAS_ZP, BN><<<2 * pairs, kPgThreads, L::kDynamicBytes, st>>>(tx, tw, p);
+  wo_umma_pair_group_kernel<T, BITS, HAS_ZP, BN, MOE><<<2 * pairs, kPgThreads, L::kDynamicBytes, st>>>(tx, tw, p, moe);
   return check_cuda(cudaGetLastError(), "weight-only prefill launch");
 }
 
 template <typename T, int BITS>
-int launch_prefill(const T* act, int64_t lda, const uint8_t* qw, PfParams p, float* xsum_ws, cudaStream_t st) {
+int launch_prefill(const T* act, int64_t lda, const uint8_t* qw, PfParams p, float* xsum_ws, cudaStream_t st,
+                   const PfMoe& moe = PfMoe{}) {
   using L = PfSmem<BITS>;
   static_assert(L::kDynamicBytes <= 227 * 1024, "shared memory budget");
   static_assert(L::kStageBytes % 1024 == 0 && L::kWBytes % 1024 == 0 && L::kConvOff % 1024 == 0, "tile alignment");
@@ -879,13 +941,17 @@ int launch_prefill(const T* act, int64_t lda, const uint8_t* qw, PfParams p, flo
   }
   if (p.group == 0) {
     switch (pf_pick_bn(p.M, p.N, sm_count() / 2)) {
-      case 224: return launch_prefill_perch<T, BITS, 224>(act, lda, qw, p, st);
-      case 192: return launch_prefill_perch<T, BITS, 192>(act, lda, qw, p, st);
-      default: return launch_prefill_perch<T, BITS, 256>(act, lda, qw, p, st);
+      case 224: return launch_prefill_perch<T, BITS, 224>(act, lda, qw, p, moe, st);
+      case 192: return launch_prefill_perch<T, BITS, 192>(act, lda, qw, p, moe, st);
+      default: return launch_prefill_perch<T, BITS, 256>(act, lda, qw, p, moe, st);
     }
   }
-  if (p.zp) return launch_prefill_group<T, BITS, true, kPgTile>(act, lda, qw, p, st);
-  return launch_prefill_group<T, BITS, false, kPgTile>(act, lda, qw, p, st);
+  if (BITS == 4 && p.moe) {  // fused MoE exists for packed int4 only
+    if (p.zp) return launch_prefill_group<T, 4, true, kPgTile, true>(act, lda, qw, p, moe, st);
+    return launch_prefill_group<T, 4, false, kPgTile, true>(act, lda, qw, p, moe, st);
+  }
+  if (p.zp) return launch_prefill_group<T, BITS, true, kPgTile, false>(act, lda, qw, p, moe, st);
+  return launch_prefill_group<T, BITS, false, kPgTile, false>(act, lda, qw, p, moe, st);
 }
 
 }  // namespace
@@ -918,6 +984,60 @@ int weight_only_prefill(const void* act, int act_dtype, int64_t lda, const void*
   }
   const __nv_bfloat16* a = static_cast<const __nv_bfloat16*>(act);
   return bits == 8 ? launch_prefill<__nv_bfloat16, 8>(a, lda, qw, p, xsum, st) : launch_prefill<__nv_bfloat16, 4>(a, lda, qw, p, xsum, st);
+}
+
+// Copies 16-bit token rows into expert-sorted order: slot s gets row sorted_ids[s] / top_k of A; slots that name no
+// token get zeros, slots past the ones in use are left alone.  One warp per slot, 16 bytes per lane and step.
+__global__ void moe_gather_rows16_kernel(const uint16_t* __restrict__ a, int64_t lda, const int32_t* __restrict__ sorted_ids,
+                                         const int32_t* __restrict__ npp, int num_valid, int top_k,
+                                         uint16_t* __restrict__ a_sorted, int K, int EM) {
+  const int slot = blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5);
+  if (slot >= EM || slot >= __ldg(npp)) return;
+  const int lane = threadIdx.x & 31;
+  const int flat = __ldg(sorted_ids + slot);
+  const bool valid = flat >= 0 && flat < num_valid;
+  const uint4* src = reinterpret_cast<const uint4*>(a + int64_t(valid ? flat / top_k : 0) * lda);
+  uint4* dst = reinterpret_cast<uint4*>(a_sorted + int64_t(slot) * K);
+  for (int i = lane; i < K / 8; i += 32) dst[i] = valid ? __ldg(src + i) : make_uint4(0, 0, 0, 0);
+}
+
+size_t weight_only_moe_prefill_workspace(int64_t EM, int64_t K, int64_t group, bool zp) {
+  size_t bytes = (size_t(EM) * size_t(K) * 2 + 255) / 256 * 256;
+  if (zp) bytes += (size_t(EM) * sizeof(float) * (group > 0 ? size_t(K / group) : 1) + 255) / 256 * 256;
+  return bytes;
+}
+
+// Fused MoE with packed-int4 expert weights on the prefill kernels: blocks of 256 sorted slots (or a multiple).
+// Returns -1 when the operands are outside what these kernels take (the caller then runs its own kernel).
+int weight_only_moe_prefill(const void* a, int a_dtype, int64_t lda, const void* b, int E, int N, int K, const void* scale,
+                            const void* zp, int scale_dtype, int group, const void* topk_w, int topk_dtype,
+                            const int32_t* sorted_ids, int EM, const int32_t* expert_ids, const int32_t* npp, int num_valid,
+                            int top_k, int block_m, int mul_w, void* out, int64_t ldo, void* workspace,
+                            size_t workspace_bytes, cudaStream_t st) {
+  if (block_m % 256 != 0 || EM % 256 != 0) return -1;
+  if (group > 0 && (group % kTK != 0 || K % group != 0)) return -1;
+  if (K % 16 != 0 || N % 2 != 0 || reinterpret_cast<uintptr_t>(b) % 16 != 0 || reinterpret_cast<uintptr_t>(a) % 16 != 0 || lda % 8 != 0)
+    return -1;
+  if (int64_t(E) * (N / 2) > INT32_MAX) return -1;
+  const size_t need = weight_only_moe_prefill_workspace(EM, K, group, zp != nullptr);
+  if (!workspace || workspace_bytes < need || reinterpret_cast<uintptr_t>(workspace) % 256 != 0) return -1;
+  uint16_t* a_sorted = static_cast<uint16_t*>(workspace);
+  float* xsum = zp ? reinterpret_cast<float*>(static_cast<uint8_t*>(workspace) + (size_t(EM) * size_t(K) * 2 + 255) / 256 * 256) : nullptr;
+  moe_gather_rows16_kernel<<<unsigned((EM + 7) / 8), 256, 0, st>>>(static_cast<const uint16_t*>(a), lda, sorted_ids, npp, num_valid,
+                                                                   top_k, a_sorted, K, EM);
+  if (int e = check_cuda(cudaGetLastError(), "fused moe a16w4 gather launch")) return e;
+  PfParams p{};
+  p.scale = scale; p.zp = zp; p.bias = nullptr; p.xsum = nullptr; p.out = out; p.ldo = ldo;
+  p.scale_dtype = scale_dtype; p.bias_dtype = FNN_F32; p.M = EM; p.N = N; p.K = K; p.group = group;
+  p.status = device_status_word();
+  p.moe = 1;
+  PfMoe moe{};
+  moe.num_experts = E; moe.top_k = top_k; moe.num_valid = num_valid; moe.mul_w = mul_w; moe.block_m = block_m;
+  moe.topk_dtype = topk_dtype; moe.sorted_ids = sorted_ids; moe.expert_ids = expert_ids; moe.npp = npp; moe.topk_w = topk_w;
+  const uint8_t* qw = static_cast<const uint8_t*>(b);
+  if (a_dtype == FNN_F16)
+    return launch_prefill<__half, 4>(reinterpret_cast<const __half*>(a_sorted), K, qw, p, xsum, st, moe);
+  return launch_prefill<__nv_bfloat16, 4>(reinterpret_cast<const __nv_bfloat16*>(a_sorted), K, qw, p, xsum, st, moe);
 }
 
 }  // namespace fnn

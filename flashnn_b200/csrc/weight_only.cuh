@@ -41,4 +41,14 @@ int gemv_a8w8_imma(const int8_t* a, int64_t lda, const int8_t* b, int64_t ldb, c
                    const void* alpha_col, int col_dtype, void* out, int out_dtype, int64_t ldo, int M, int N, int K,
                    int32_t* acc_out, int64_t ldacc, cudaStream_t st);
 
+// Fused MoE with packed-int4 expert weights on the prefill (tcgen05) kernels of gemm_weight_only.cu, for blocks of 256
+// sorted slots or a multiple.  Returns an fnn_status, or -1 when the shape, the alignment or the workspace is outside
+// what they take.  The workspace holds the expert-sorted copy of the token rows (and their row sums with zero-points).
+size_t weight_only_moe_prefill_workspace(int64_t EM, int64_t K, int64_t group, bool zp);
+int weight_only_moe_prefill(const void* a, int a_dtype, int64_t lda, const void* b, int E, int N, int K, const void* scale,
+                            const void* zp, int scale_dtype, int group, const void* topk_w, int topk_dtype,
+                            const int32_t* sorted_ids, int EM, const int32_t* expert_ids, const int32_t* npp, int num_valid,
+                            int top_k, int block_m, int mul_w, void* out, int64_t ldo, void* workspace,
+                            size_t workspace_bytes, cudaStream_t st);
+
 }  // namespace fnn

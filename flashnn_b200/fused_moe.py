@@ -84,9 +84,13 @@ def fused_moe_a16w4_forward(A, B, C, scale_b, zero_points, topk_weights, topk_id
         tw = tw.float()
     sid, eid, npp = _i32(sorted_token_ids), _i32(expert_ids), _i32(num_tokens_post_padded)
     with _on_device(A):
-        _lib.check(_lib.lib().fnn_fused_moe_a16w4(
+        L = _lib.lib()
+        ws_bytes = L.fnn_fused_moe_a16w4_workspace_bytes(sid.shape[0], K, group, int(zp is not None), int(BM))
+        ws = _workspace(A.device, ws_bytes) if ws_bytes else None
+        _lib.check(L.fnn_fused_moe_a16w4_ws(
             a2.data_ptr(), _DT[A.dtype], a2.stride(0), b.data_ptr(), E, N, K, scale.data_ptr(),
             zp.data_ptr() if zp is not None else None, _DT[scale.dtype], group, tw.data_ptr(), _DT[tw.dtype],
             sid.data_ptr(), sid.shape[0], eid.data_ptr(), npp.data_ptr(), topk_ids.numel(), int(top_k), int(BM),
-            int(bool(mul_routed_weight)), C.data_ptr(), _DT[C.dtype], C.stride(1), _stream(A)))
+            int(bool(mul_routed_weight)), C.data_ptr(), _DT[C.dtype], C.stride(1),
+            ws.data_ptr() if ws is not None else None, ws_bytes, _stream(A)))
     return C

@@ -227,6 +227,22 @@ int fnn_fused_moe_a16w4(const void* a, int a_dtype, int64_t lda, const void* b, 
                         int top_k, int block_m, int mul_routed_weight, void* out, int out_dtype, int64_t ldo, void* stream);
 
 /*
+ * The same operator with caller scratch.  With blocks of 256 sorted slots (block_m a multiple of 256), enough blocks to
+ * give every CTA pair a tile and a workspace of fnn_fused_moe_a16w4_workspace_bytes(...) bytes (256-byte aligned), the
+ * call runs on the tcgen05 prefill kernels of the weight-only GEMM in a fused-MoE mode: the token rows are first copied
+ * into expert-sorted order in the workspace (with zero-points also their row sums per scale group).  Any other call,
+ * and a call without the workspace, does exactly what fnn_fused_moe_a16w4 does.  The workspace function returns 0 for
+ * block sizes that never use one.  Same results contract (fp32 dequant-matmul bound).
+ */
+int fnn_fused_moe_a16w4_ws(const void* a, int a_dtype, int64_t lda, const void* b, int64_t E, int64_t N, int64_t K,
+                           const void* scale, const void* zero_points, int scale_dtype, int64_t group_size,
+                           const void* topk_weights, int topk_dtype, const int32_t* sorted_token_ids, int64_t EM,
+                           const int32_t* expert_ids, const int32_t* num_tokens_post_padded, int64_t num_valid_tokens,
+                           int top_k, int block_m, int mul_routed_weight, void* out, int out_dtype, int64_t ldo,
+                           void* workspace, size_t workspace_bytes, void* stream);
+size_t fnn_fused_moe_a16w4_workspace_bytes(int64_t EM, int64_t K, int64_t group_size, int has_zero_points, int block_m);
+
+/*
  * Weight-only GEMM / GEMV:  out = act . dequant(W)^T (+ bias), W int8 or packed int4.
  * Replaces `triton_gemm_a16w8_forward` (flashnn/triton_kernels/gemm_a16w8.py:275-338)
  * and `triton_gemm_a16w4_forward` (flashnn/triton_kernels/gemm_a16w4.py:336-406).

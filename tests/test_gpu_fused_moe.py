@@ -133,6 +133,22 @@ def test_a16w4_matches_the_fp32_dequant_oracle(dt, m, e, n, k, top_k, bm, mul, g
     check_w4(out, c, top_k, bm, mul, m, n)
 
 
+# blocks of 256 slots and enough tiles for every CTA pair: the tcgen05 prefill kernels in their fused-MoE mode
+# (per-channel and per-group scales, with and without zero-points, ragged N, an expert count that leaves padding tiles)
+@pytest.mark.parametrize("dt", [torch.float16, torch.bfloat16])
+@pytest.mark.parametrize("m,e,n,k,top_k,mul,group,use_zp", [
+    (2000, 4, 1024, 512, 2, True, 0, False), (1800, 6, 1056, 256, 2, False, 0, True), (2000, 4, 1024, 512, 2, True, 128, False),
+    (1800, 6, 1056, 512, 2, True, 64, True), (4400, 8, 768, 256, 1, True, 256, False)])
+def test_a16w4_blocks_of_256_on_the_prefill_kernels(dt, m, e, n, k, top_k, mul, group, use_zp):
+    bm = 256
+    c = make_moe_w4_case(m, e, n, k, top_k, bm, seed=m + e + n, dtype=dt, group=group, use_zp=use_zp)
+    assert (c["sorted_ids"].numel() // 256) * ((n + 255) // 256) >= 74
+    from flashnn_b200 import _lib
+    assert _lib.lib().fnn_fused_moe_a16w4_workspace_bytes(c["sorted_ids"].numel(), k, group, int(use_zp), bm) > 0
+    out = run_w4(c, top_k, bm, mul, m, n)
+    check_w4(out, c, top_k, bm, mul, m, n)
+
+
 def test_a16w4_dropped_tokens_and_fractional_zero_points():
     m, e, n, k, top_k, bm = 40, 4, 64, 256, 2, 16
     c = make_moe_w4_case(m, e, n, k, top_k, bm, seed=3, dtype=torch.float16, group=64, use_zp=True)
