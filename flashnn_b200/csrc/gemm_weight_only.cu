@@ -66,8 +66,8 @@ struct PfParams {
 // Fused MoE (PfParams::moe != 0): the activations are the expert-sorted copy of the token rows [EM, K] (M = EM), a
 // 256-row tile is one block of sorted slots (block_m is a multiple of 256) whose expert picks the weight rows and the
 // scales ([E, N], or [E, N, K / group] for group-wise ones); the epilogue multiplies by the routing weight and scatters
-// each slot's row to its flat (token, choice) index.  Tiles past the slots in use are computed on whatever the copy
-// holds and never stored.  A kernel parameter of its own: the dense kernels' parameter block stays as small as it was
+// each slot's row to its flat (token, choice) index.  Row tiles past the slots in use are left out by every role
+// alike.  A kernel parameter of its own: the dense kernels' parameter block stays as small as it was
 // (growing it cost the group-wise kernel 4 % through local-memory copies of the block).
 struct PfMoe {
   int num_experts, top_k, num_valid, mul_w, block_m, topk_dtype;
@@ -219,6 +219,14 @@ __device__ __forceinline__ void pf_init_bars(const PfBars& b, int epi_arrivals, 
   mbar_fence_init();
 }
 
+// Fused MoE: is the row tile of tile t in use?  (Every role leaves out the same tiles, so the rings stay in step.)
+__device__ __forceinline__ bool pf_tile_in_use(const PfMoe* moe, const PfParams& p, int t) {
+  if (!moe) return true;
+  int mb, nb;
+  pf_tile_coords(t, p.tiles_m, p.tiles_n, mb, nb);
+  return pf_moe_expert(*moe, mb) >= 0;
+}
+
 // warp 0 of both CTAs: TMA loads of this CTA's 128 activation rows and its raw weight bytes, one K block per stage
 template <int BITS, int BN = kTN, bool MOE = false>
 __device__ __forceinline__ void pf_producer(uint8_t* smem, const PfBars& b, const CUtensorMap* tmap_x,
@@ -235,9 +243,10 @@ __device__ __forceinline__ void pf_producer(uint8_t* smem, const PfBars& b, cons
     int mb, nb;
     pf_tile_coords(t, p.tiles_m, p.tiles_n, mb, nb);
     int w_row = (BITS == 8) ? nb * BN + int(rank) * (BN / 2) : (nb * BN + int(rank) * (BN / 2)) / 2;
-    if (MOE) {  // the expert's rows of the weight stack (a tile that is not in use reads expert 0's)
+    if (MOE) {  // the expert's rows of the weight stack; a tile that is not in use is left out
       const int e = pf_moe_expert(*moe, mb);
-      w_row += (e < 0 ? 0 : e) * ((BITS == 8) ? p.N : p.N / 2);
+      if (e < 0) continue;
+      w_row += e * ((BITS == 8) ? p.N : p.N / 2);
     }
     for (int kb = 0; kb < p.k_blocks; ++kb) {
       ok = mbar_wait_bounded(&b.empty[stage], phase ^ 1, abort_flag);
@@ -269,7 +278,7 @@ __device__ __forceinline__ void pf_producer(uint8_t* smem, const PfBars& b, cons
 // group for group-wise scales.
 template <typename T, int BITS, int BN = kTN, int NBUF = 2, int ACC_STRIDE = kTN>
 __device__ __forceinline__ void pf_mma(uint8_t* smem, const PfBars& b, const PfParams& p, uint32_t tmem_base, int pair_id,
-                                       int num_pairs, int kb_per_acc, volatile int* abort_flag) {
+                                       int num_pairs, int kb_per_acc, volatile int* abort_flag, const PfMoe* moe = nullptr) {
   using L = PfSmem<BITS>;
   constexpr uint32_t idesc = umma_idesc(/*f32*/ 1, std::is_same<T, __half>::value ? 0u : 1u, 256, BN);
   const int num_tiles = p.tiles_m * p.tiles_n;
@@ -280,6 +289,7 @@ __device__ __forceinline__ void pf_mma(uint8_t* smem, const PfBars& b, const PfP
   bool ok = true;
   bool issued_any = false;
   for (int t = pair_id; t < num_tiles && ok; t += num_pairs) {
+    if (!pf_tile_in_use(moe, p, t)) continue;
     for (int kb0 = 0; kb0 < p.k_blocks && ok; kb0 += kb_per_acc, ++seg) {
       const int buf = seg % NBUF;
       const uint32_t acc_phase = (seg / NBUF) & 1;
@@ -329,13 +339,14 @@ __device__ __forceinline__ void pf_mma(uint8_t* smem, const PfBars& b, const PfP
 // warp 1 of the peer CTA: relays "this CTA's converted tile is ready" to the leader's barrier, one remote arrive per
 // K block, so the converter warps themselves only ever signal locally
 __device__ __forceinline__ void pf_relay(const PfBars& b, const PfParams& p, int pair_id, int num_pairs,
-                                         volatile int* abort_flag) {
+                                         volatile int* abort_flag, const PfMoe* moe = nullptr) {
   const int num_tiles = p.tiles_m * p.tiles_n;
   const bool leader_lane = elect_one();
   int cstage = 0;
   uint32_t cphase = 0;
   bool ok = true;
   for (int t = pair_id; t < num_tiles && ok; t += num_pairs) {
+    if (!pf_tile_in_use(moe, p, t)) continue;
     for (int kb = 0; kb < p.k_blocks; ++kb) {
       ok = mbar_wait_bounded(&b.conv_done[cstage], cphase, abort_flag);
       ok = __all_sync(0xffffffffu, ok);
@@ -356,7 +367,8 @@ __device__ __forceinline__ void pf_relay(const PfBars& b, const PfParams& p, int
 // proxy fence, the arrive), which is what sets the pace when a block is short.
 template <typename T, int BITS, int BN = kTN, int CT = 128, int TEAMS = 1>
 __device__ __forceinline__ void pf_converters(uint8_t* smem, const PfBars& b, const PfParams& p, uint32_t rank, int pair_id,
-                                              int num_pairs, int ct, volatile int* abort_flag, int team = 0) {
+                                              int num_pairs, int ct, volatile int* abort_flag, int team = 0,
+                                              const PfMoe* moe = nullptr) {
   using L = PfSmem<BITS>;
   const int num_tiles = p.tiles_m * p.tiles_n;
   const int lane = ct & 31;
@@ -369,6 +381,7 @@ __device__ __forceinline__ void pf_converters(uint8_t* smem, const PfBars& b, co
     if (++turn == TEAMS) turn = 0;
   };
   for (int t = pair_id; t < num_tiles && ok; t += num_pairs) {
+    if (!pf_tile_in_use(moe, p, t)) continue;
     for (int kb = 0; kb < p.k_blocks; ++kb, advance()) {
       if (TEAMS > 1 && turn != team) continue;
       ok = mbar_wait_bounded(&b.conv_empty[cstage], cphase ^ 1, abort_flag) &&
@@ -468,8 +481,9 @@ wo_umma_pair_kernel(const __grid_constant__ CUtensorMap tmap_x, const __grid_con
       if (p.moe) pf_producer<BITS, BN, true>(smem, b, &tmap_x, &tmap_w, p, rank, pair_id, num_pairs, abort_flag, &moe);
       else pf_producer<BITS, BN, false>(smem, b, &tmap_x, &tmap_w, p, rank, pair_id, num_pairs, abort_flag);
     } else if (warp == 1) {
-      if (rank == 0) pf_mma<T, BITS, BN>(smem, b, p, tmem_base, pair_id, num_pairs, p.k_blocks, abort_flag);
-      else pf_relay(b, p, pair_id, num_pairs, abort_flag);
+      const PfMoe* in_use = p.moe ? &moe : nullptr;
+      if (rank == 0) pf_mma<T, BITS, BN>(smem, b, p, tmem_base, pair_id, num_pairs, p.k_blocks, abort_flag, in_use);
+      else pf_relay(b, p, pair_id, num_pairs, abort_flag, in_use);
     }
   } else if (warp < 8) {
     asm volatile("setmaxnreg.inc.sync.aligned.u32 200;");
@@ -482,14 +496,16 @@ wo_umma_pair_kernel(const __grid_constant__ CUtensorMap tmap_x, const __grid_con
     const bool vec_ok = (p.ldo % 8 == 0) && (reinterpret_cast<uintptr_t>(out) % 16 == 0);
     int local = 0;
     bool ok = true;
-    for (int t = pair_id; t < num_tiles && ok; t += num_pairs, ++local) {
+    for (int t = pair_id; t < num_tiles && ok; t += num_pairs) {
       int mb, nb;
       pf_tile_coords(t, p.tiles_m, p.tiles_n, mb, nb);
+      const int expert = p.moe ? pf_moe_expert(moe, mb) : 0;
+      if (expert < 0) continue;  // fused MoE: a row tile past the slots in use
       const int buf = local & 1;
       const uint32_t acc_phase = (local >> 1) & 1;
+      ++local;
       const int row = mb * 256 + int(rank) * kTM + quarter * 32 + lane;
       const int n0 = nb * BN;
-      const int expert = p.moe ? pf_moe_expert(moe, mb) : 0;
       const int64_t sbase = int64_t(expert < 0 ? 0 : expert) * p.N;  // fused MoE: the expert's scales
       for (int j = lane; j < BN; j += 32) {
         const bool in = n0 + j < p.N && expert >= 0;
@@ -556,7 +572,7 @@ wo_umma_pair_kernel(const __grid_constant__ CUtensorMap tmap_x, const __grid_con
     constexpr int kTeamThreads = kPfConvWarps * 32 / pf_conv_teams<BITS>();
     pf_converters<T, BITS, BN, kTeamThreads, pf_conv_teams<BITS>()>(smem, b, p, rank, pair_id, num_pairs,
                                                            (threadIdx.x - 8 * 32) % kTeamThreads, abort_flag,
-                                                           (threadIdx.x - 8 * 32) / kTeamThreads);
+                                                           (threadIdx.x - 8 * 32) / kTeamThreads, p.moe ? &moe : nullptr);
   }
 
   // -------------------------------- teardown --------------------------------
@@ -642,8 +658,8 @@ wo_umma_pair_group_kernel(const __grid_constant__ CUtensorMap tmap_x, const __gr
     if (warp == 0) {
       pf_producer<BITS, BN, MOE>(smem, b, &tmap_x, &tmap_w, p, rank, pair_id, num_pairs, abort_flag, &moe);
     } else if (warp == 1) {
-      if (rank == 0) pf_mma<T, BITS, BN, NBUF, BN>(smem, b, p, tmem_base, pair_id, num_pairs, kb_per_group, abort_flag);
-      else pf_relay(b, p, pair_id, num_pairs, abort_flag);
+      if (rank == 0) pf_mma<T, BITS, BN, NBUF, BN>(smem, b, p, tmem_base, pair_id, num_pairs, kb_per_group, abort_flag, MOE ? &moe : nullptr);
+      else pf_relay(b, p, pair_id, num_pairs, abort_flag, MOE ? &moe : nullptr);
     } else {
       // ---- warps 2 and 3: stage the scales (and scale * zero-point, and with a tile's first group its bias) of the
       // coming groups as fp32 in a ring of kPgScaleStages slots, one column half each, CPL columns per lane, so that
@@ -662,6 +678,7 @@ wo_umma_pair_group_kernel(const __grid_constant__ CUtensorMap tmap_x, const __gr
         pf_tile_coords(t, p.tiles_m, p.tiles_n, mb, nb);
         const int n0 = nb * BN + c0;
         const int expert = MOE ? pf_moe_expert(moe, mb) : 0;
+        if (expert < 0) continue;
         for (int g = 0; g < groups; ++g, ++seg) {
           const int slot = seg % kPgScaleStages;
           const uint32_t ph = (seg / kPgScaleStages) & 1;
@@ -696,7 +713,7 @@ wo_umma_pair_group_kernel(const __grid_constant__ CUtensorMap tmap_x, const __gr
     asm volatile("setmaxnreg.dec.sync.aligned.u32 56;");
     pf_converters<T, BITS, BN, 128 / kPgConvTeams, kPgConvTeams>(smem, b, p, rank, pair_id, num_pairs,
                                                                  (threadIdx.x - 4 * 32) % (128 / kPgConvTeams), abort_flag,
-                                                                 (threadIdx.x - 4 * 32) / (128 / kPgConvTeams));
+                                                                 (threadIdx.x - 4 * 32) / (128 / kPgConvTeams), MOE ? &moe : nullptr);
   } else {
     asm volatile("setmaxnreg.inc.sync.aligned.u32 208;");
     // -------------------------------- epilogue (both CTAs) --------------------------------
@@ -722,12 +739,11 @@ wo_umma_pair_group_kernel(const __grid_constant__ CUtensorMap tmap_x, const __gr
       int moe_row = -1;
       float rw = 1.f;
       if (MOE) {
-        if (pf_moe_expert(moe, mb) >= 0) {
-          const int flat = __ldg(moe.sorted_ids + row);
-          if (flat >= 0 && flat < moe.num_valid) {
-            moe_row = flat;
-            if (moe.mul_w) rw = load_as_f32(moe.topk_w, moe.topk_dtype, flat);
-          }
+        if (pf_moe_expert(moe, mb) < 0) continue;  // a row tile past the slots in use
+        const int flat = __ldg(moe.sorted_ids + row);
+        if (flat >= 0 && flat < moe.num_valid) {
+          moe_row = flat;
+          if (moe.mul_w) rw = load_as_f32(moe.topk_w, moe.topk_dtype, flat);
         }
       }
       for (int g = 0; g < groups; ++g, ++seg) {
