@@ -186,7 +186,8 @@ int fnn_gemm_a8w8_plan(int64_t M, int64_t N, int64_t K, int* kernel, int* tile_n
  *                     to a multiple of block_m with values >= num_valid_tokens
  *   expert_ids        [EM / block_m] int32;  num_tokens_post_padded [1] int32 (device memory)
  *   out               [M * top_k, N] f16 or bf16, ldo
- *   block_m           at most 128, or a multiple of 128
+ *   block_m           at most 128, or a multiple of 128; a multiple of 256 with enough blocks to give every CTA pair a
+ *                     tile runs on the CTA-pair kernel (prefill-sized batches: 11-15 % faster than blocks of 128)
  *   workspace         fnn_fused_moe_a8w8_workspace_bytes(EM, K) bytes, 256-byte aligned (the expert-sorted copy of
  *                     the token rows)
  */
