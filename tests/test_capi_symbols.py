@@ -95,3 +95,25 @@ def test_gemm_weight_only_argument_errors(lib):
 
 def test_device_status_needs_an_output_pointer(lib):
     assert lib.fnn_device_status(None) == 1
+
+
+def test_fused_moe_a16w4_workspace_and_argument_errors(lib):
+    # scratch only for blocks of 256 slots (the prefill kernels): the expert-sorted 16-bit copy of the token rows,
+    # plus their row sums per scale group when zero-points are given
+    ws = lib.fnn_fused_moe_a16w4_workspace_bytes
+    assert ws(4096, 4096, 128, 0, 64) == 0 and ws(4096, 4096, 128, 0, 128) == 0
+    assert ws(4096, 4096, 128, 0, 256) == 4096 * 4096 * 2
+    assert ws(4096, 4096, 128, 1, 256) == 4096 * 4096 * 2 + 4096 * 4 * 32
+    assert ws(4096, 4096, 0, 1, 512) == 4096 * 4096 * 2 + 4096 * 4
+    f = lib.fnn_fused_moe_a16w4_ws
+
+    def call(N=64, K=128, EM=256, bm=256, group=0, adt=_lib.BF16, odt=_lib.BF16, top_k=2):
+        return f(None, adt, K, None, 4, N, K, None, None, _lib.BF16, group, None, _lib.F32, None, EM, None, None, 64, top_k, bm, 1,
+                 None, odt, N, None, 0, None)
+
+    assert call() == 1                # null tensors
+    assert call(N=63) == 3            # packed int4 needs an even N
+    assert call(EM=200) == 3          # slots not a multiple of block_m
+    assert call(bm=100, EM=200) == 5  # block size
+    assert call(group=96) == 5        # group size
+    assert call(odt=_lib.F16) == 2    # output dtype must equal the token dtype
