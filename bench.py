@@ -879,6 +879,8 @@ def run_case(args):
             _lib.set_option(_lib.OPT_A8W8_PAIR_TILE, args.tile)
         if args.balanced:
             _lib.set_option(_lib.OPT_A8W8_BALANCED, args.balanced)
+        if args.epilogue_warps:
+            _lib.set_option(_lib.OPT_A8W8_EPILOGUE_WARPS, args.epilogue_warps)
     elif name == "gemv":
         m, n, k = args.m or 1, args.n or 28672, args.k or 8192
         w = W.a16w4_decode(m, n, k)
@@ -973,6 +975,7 @@ def main():
                     help="run one kernel only (profiling / A-B timing), the reference's Triton kernels, or the reference's shape sweep")
     ap.add_argument("--tile", type=int, default=0, help="with --case a8w8: force this CTA-pair tile width (tuning)")
     ap.add_argument("--balanced", type=int, default=0, help="with --case a8w8: 1 forces, 2 forbids the K-balanced mode of the CTA-pair kernel")
+    ap.add_argument("--epilogue-warps", type=int, default=0, help="with --case a8w8: 4 keeps four epilogue warps per CTA for every K")
     ap.add_argument("--bm", type=int, default=0, help="with --case moe / moe4: slots per block (default 16 up to 64 tokens, else 128 / 64)")
     ap.add_argument("--group", type=int, default=0, help="with --case wog: scale group size (-1: per channel)")
     ap.add_argument("--m", type=int)

@@ -106,6 +106,7 @@ OPT_STATIC_WEIGHTS = 1
 OPT_TEST_STALL_US = 2  # test hook, see include/flashnn_b200.h
 OPT_A8W8_PAIR_TILE = 3  # tuning hook
 OPT_A8W8_BALANCED = 4  # 0 by shape, 1 always where possible, 2 never
+OPT_A8W8_EPILOGUE_WARPS = 5  # tuning hook: 4 keeps four epilogue warps per CTA for every K
 
 
 def set_option(option: int, value: int) -> None:

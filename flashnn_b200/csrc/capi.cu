@@ -58,6 +58,8 @@ std::atomic<int> g_opt_a8w8_pair_tile{0};
 std::atomic<int> g_opt_a8w8_balanced{0};
 }
 int opt_a8w8_balanced() { return g_opt_a8w8_balanced.load(std::memory_order_relaxed); }
+namespace { std::atomic<int> g_opt_a8w8_epilogue_warps{0}; }
+int opt_a8w8_epilogue_warps() { return g_opt_a8w8_epilogue_warps.load(std::memory_order_relaxed); }
 int opt_a8w8_pair_tile() { return g_opt_a8w8_pair_tile.load(std::memory_order_relaxed); }
 bool opt_static_weights() { return g_opt_static_weights.load(std::memory_order_relaxed) != 0; }
 int opt_test_stall_us() { return g_opt_test_stall_us.load(std::memory_order_relaxed); }
@@ -129,6 +131,12 @@ extern "C" int fnn_set_option(int option, int value) {
     fnn::g_opt_a8w8_pair_tile.store(value, std::memory_order_relaxed);
     return FNN_OK;
   }
+  if (option == FNN_OPT_A8W8_EPILOGUE_WARPS) {
+    if (value != 0 && value != 4)
+      return fnn::fail(FNN_ERR_UNSUPPORTED, "fnn_set_option: FNN_OPT_A8W8_EPILOGUE_WARPS takes 0 (by shape) or 4 (got %d)", value);
+    fnn::g_opt_a8w8_epilogue_warps.store(value, std::memory_order_relaxed);
+    return FNN_OK;
+  }
   if (option == FNN_OPT_A8W8_BALANCED) {
     if (value < 0 || value > 2)
       return fnn::fail(FNN_ERR_UNSUPPORTED, "fnn_set_option: FNN_OPT_A8W8_BALANCED takes 0 (by shape), 1 (always) or 2 (never) (got %d)", value);
@@ -143,6 +151,7 @@ extern "C" int fnn_get_option(int option) {
   if (option == FNN_OPT_TEST_STALL_US) return fnn::g_opt_test_stall_us.load(std::memory_order_relaxed);
   if (option == FNN_OPT_A8W8_PAIR_TILE) return fnn::g_opt_a8w8_pair_tile.load(std::memory_order_relaxed);
   if (option == FNN_OPT_A8W8_BALANCED) return fnn::g_opt_a8w8_balanced.load(std::memory_order_relaxed);
+  if (option == FNN_OPT_A8W8_EPILOGUE_WARPS) return fnn::g_opt_a8w8_epilogue_warps.load(std::memory_order_relaxed);
   return -1;
 }
 

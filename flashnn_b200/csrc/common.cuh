@@ -23,6 +23,7 @@ bool opt_static_weights();  // FNN_OPT_STATIC_WEIGHTS
 int opt_test_stall_us();    // FNN_OPT_TEST_STALL_US (0 unless a test set it)
 int opt_a8w8_pair_tile();   // FNN_OPT_A8W8_PAIR_TILE (0 = chosen from the shape)
 int opt_a8w8_balanced();    // FNN_OPT_A8W8_BALANCED (0 = by shape, 1 = always where possible, 2 = never)
+int opt_a8w8_epilogue_warps();  // FNN_OPT_A8W8_EPILOGUE_WARPS (0 = by shape, 4 = always four)
 // 2-D tiled tensor map over a row-major [rows, cols] matrix of 1- or 2-byte elements (row pitch in bytes);
 // the box is box_cols x box_rows elements, out-of-range elements read as zero (and are not written by a store).
 // swizzle: 0 none, 1 the 128-byte pattern, 2 the 64-byte pattern.

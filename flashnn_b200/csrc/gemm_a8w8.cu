@@ -520,15 +520,15 @@ __device__ __forceinline__ bool flag_wait_bounded(const unsigned long long* f, u
   }
 }
 
-template <int BN, int STAGES> struct PairSmem {
+template <int BN, int STAGES, int EPI = 4> struct PairSmem {
   static constexpr int kBN = BN;                        // output columns of a pair tile (a multiple of 32, at most 256)
   static constexpr int kABytes = kBM * kBK;             // this CTA's 128 rows of A
   static constexpr int kBBytes = (kBN / 2) * kBK;       // this CTA's BN / 2 rows of B
   static constexpr int kStageBytes = kABytes + kBBytes;
-  static constexpr int kOutOff = STAGES * kStageBytes;        // [4 epilogue warps][2][32 rows x 64 B] output staging
-  static constexpr int kOutBytes = 4 * 2 * 2048;
-  static constexpr int kColScaleOff = kOutOff + kOutBytes;    // [4][kBN] float
-  static constexpr int kBarOff = kColScaleOff + 4 * kBN * 4;
+  static constexpr int kOutOff = STAGES * kStageBytes;        // [EPI epilogue warps][2][32 rows x 64 B] output staging
+  static constexpr int kOutBytes = EPI * 2 * 2048;
+  static constexpr int kColScaleOff = kOutOff + kOutBytes;    // [EPI][kBN] float
+  static constexpr int kBarOff = kColScaleOff + EPI * kBN * 4;
   static constexpr int kNumBars = 2 * STAGES + 4 + 1;
   static constexpr int kTmemSlotOff = kBarOff + kNumBars * 8;
   static constexpr int kAbortOff = kTmemSlotOff + 8;
@@ -538,11 +538,14 @@ template <int BN, int STAGES> struct PairSmem {
 
 // MOE: fused-MoE mode for blocks of 256 sorted slots (A8W8Params, "Fused-MoE mode"): a pair tile is one block, whose
 // expert picks the weight rows and column scales; the epilogue scatters each slot's row to its (token, choice) index.
-template <typename OutT, int BN, int STAGES, bool SK, bool MOE = false>
-__global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(kThreads, 1)
+// EPI: epilogue warps per CTA, 4 or 8.  With 8, two warps share a TMEM lane quarter and split a tile's column chunks:
+// for short K, where a tile's MMAs take less time than four warps need to write it out.
+template <typename OutT, int BN, int STAGES, bool SK, bool MOE = false, int EPI = 4>
+__global__ void __cluster_dims__(2, 1, 1) __launch_bounds__((2 + EPI) * 32, 1)
 a8w8_umma_pair_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ CUtensorMap tmap_b,
                       const __grid_constant__ CUtensorMap tmap_out, const A8W8Params p) {
-  using L = PairSmem<BN, STAGES>;
+  using L = PairSmem<BN, STAGES, EPI>;
+  static_assert(EPI == 4 || (EPI == 8 && !SK && !MOE), "eight epilogue warps exist for the plain mode only");
   constexpr int kAccStride = 256;  // TMEM columns between the two accumulators (512 are allocated whatever BN is)
   extern __shared__ uint8_t smem_raw[];
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
@@ -571,7 +574,7 @@ a8w8_umma_pair_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_c
     }
     for (int b = 0; b < 2; ++b) {
       mbar_init(&tmem_full_bar[b], 1);
-      mbar_init(&tmem_empty_bar[b], 8);
+      mbar_init(&tmem_empty_bar[b], 2 * EPI);
     }
     mbar_init(drain_bar, 1);
     mbar_fence_init();
@@ -684,14 +687,18 @@ a8w8_umma_pair_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_c
   } else {
     // -------------------------------- epilogue (both CTAs) --------------------------------
     const int quarter = warp & 3;
-    float* cs = col_scale_smem + quarter * BN;  // this warp's private copy
+    const int ewarp = warp - 2;                  // 0 .. EPI-1
+    constexpr int NC = BN / 32;                  // column chunks of a tile
+    const int c_begin = (EPI == 8 && ewarp >= 4) ? (NC + 1) / 2 : 0;  // with eight warps the second four take the upper chunks
+    const int c_end = (EPI == 8 && ewarp < 4) ? (NC + 1) / 2 : NC;
+    float* cs = col_scale_smem + ewarp * BN;  // this warp's private copy
     const bool same16 = (p.row_dtype == p.col_dtype) && (p.row_dtype != FNN_F32);
     const bool vec_ok = (p.ldo % 8 == 0) && (reinterpret_cast<uintptr_t>(p.out) % 16 == 0);
     const bool acc_vec_ok = p.acc_out && (p.ldacc % 4 == 0) && (reinterpret_cast<uintptr_t>(p.acc_out) % 16 == 0);
     int local = 0;
     bool ok = true;
     PairWork<SK, MOE> w(p, pair_id, num_pairs);
-    uint8_t* out_stage = smem + L::kOutOff + quarter * 4096;            // this warp's two output staging buffers
+    uint8_t* out_stage = smem + L::kOutOff + ewarp * 4096;              // this warp's two output staging buffers
     int out_buf = 0;
     const int my_flag = int(rank) * 4 + quarter;                        // this warp's flag word within a pair's eight
     const int my_row = int(rank) * 128 + quarter * 32 + lane;           // this thread's row within a tile
@@ -712,7 +719,7 @@ a8w8_umma_pair_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_c
       auto slot_of = [&](int h) { return h * p.sk_slots + (w.tile - (h * p.sk_tail_units) / tail_blocks); };
       const int n0 = nb * BN;
       const int64_t col_base = MOE ? int64_t(__ldg(p.expert_ids + (mb * 256) / p.block_m)) * p.col_stride_e : 0;
-      for (int j = lane; j < BN; j += 32)
+      for (int j = c_begin * 32 + lane; j < c_end * 32; j += 32)
         cs[j] = (n0 + j < p.N) ? load_as_f32(p.alpha_col, p.col_dtype, col_base + n0 + j) : 0.f;
       float rs = 0.f, rw = 1.f;
       int64_t out_row = -1;  // fused MoE: the flat (token, choice) index this slot writes, or -1
@@ -761,7 +768,7 @@ a8w8_umma_pair_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_c
         for (int j = 0; j < 8; ++j) ahead[j] = __ldcg(src + j * 32);  // written by another SM in this launch: read through L2
       }
 #pragma unroll 1
-      for (int c = 0; c < BN / 32; ++c) {
+      for (int c = c_begin; c < c_end; ++c) {
         uint32_t r[32];
         tmem_ld_32x32(taddr + c * 32, r);
         uint4 cur[8];
@@ -960,16 +967,17 @@ inline unsigned long long next_sk_epoch() {
   return e;
 }
 
-template <typename OutT, int BN, bool SK = false>
+template <typename OutT, int BN, bool SK = false, int EPI = 4>
 int launch_pair(const int8_t* a, int64_t lda, const int8_t* b, int64_t ldb, A8W8Params p, cudaStream_t st,
                 void* workspace = nullptr) {
-  constexpr int kBudget = 196 * 1024;  // for the operand ring; 16 KB more hold the output staging buffers
+  // for the operand ring; the output staging buffers and the column scales of the epilogue warps take the rest
+  constexpr int kBudget = (EPI == 4 ? 196 : 174) * 1024;
   constexpr int STAGES = kBudget / (kBM * kBK + (BN / 2) * kBK) < 8 ? kBudget / (kBM * kBK + (BN / 2) * kBK) : 8;
-  using L = PairSmem<BN, STAGES>;
+  using L = PairSmem<BN, STAGES, EPI>;
   static_assert(L::kDynamicBytes <= 227 * 1024, "shared memory budget");
   static_assert(L::kStageBytes % 1024 == 0 && L::kABytes % 1024 == 0 && L::kOutOff % 1024 == 0, "tiles must stay 1024-byte aligned");
   static_assert(BN % 32 == 0 && BN <= 256, "pair tile width");
-  auto kern = a8w8_umma_pair_kernel<OutT, BN, STAGES, SK>;
+  auto kern = a8w8_umma_pair_kernel<OutT, BN, STAGES, SK, false, EPI>;
   static std::once_flag once[64];
   static cudaError_t attr_err[64];  // per device, so that a failure is reported on every call and not only the first
   int dev = 0;
@@ -1007,7 +1015,7 @@ int launch_pair(const int8_t* a, int64_t lda, const int8_t* b, int64_t ldb, A8W8
     p.sk_partials = reinterpret_cast<int32_t*>(static_cast<uint8_t*>(workspace) + kSkFlagBytes);
     p.sk_epoch = next_sk_epoch();
   }
-  kern<<<2 * pairs, kThreads, L::kDynamicBytes, st>>>(ta, tb, tout, p);
+  kern<<<2 * pairs, (2 + EPI) * 32, L::kDynamicBytes, st>>>(ta, tb, tout, p);
   return check_cuda(cudaGetLastError(), "a8w8 tcgen05 (CTA pair) launch");
 }
 
@@ -1022,6 +1030,11 @@ int launch_pair(const int8_t* a, int64_t lda, const int8_t* b, int64_t ldb, A8W8
 // operand traffic; it wins where the problem is too small to give every CTA pair a tile.  Problems of at
 // most 128 rows are bound by the weight stream instead and keep their own rule.
 // ---------------------------------------------------------------------------
+// Up to this K the CTA-pair kernel runs with eight epilogue warps per CTA (and one operand stage fewer, which is what
+// it costs from K = 3328 up).  Measured, four -> eight warps: K = 1664 2037 -> 3055 TOPS, 2048 2097 -> 2741,
+// 3328 3344 -> 3281, 4096 3470 -> 3279.
+constexpr int kEpi8MaxK = 2560;
+
 struct A8W8Plan {
   bool pair;
   int bn;
@@ -1114,6 +1127,16 @@ int dispatch(const int8_t* a, int64_t lda, const int8_t* b, int64_t ldb, const A
     if (p.M > kBM) plan = A8W8Plan{true, forced, 0.0};
   }
   if (plan.balanced) return launch_pair<OutT, 256, true>(a, lda, b, ldb, p, st, workspace);
+  if (plan.pair && p.K <= kEpi8MaxK && opt_a8w8_epilogue_warps() != 4) {
+    // short K: a tile's MMAs take less time than four warps need to write it out; eight epilogue warps per CTA
+    switch (plan.bn) {
+      case 256: return launch_pair<OutT, 256, false, 8>(a, lda, b, ldb, p, st);
+      case 224: return launch_pair<OutT, 224, false, 8>(a, lda, b, ldb, p, st);
+      case 192: return launch_pair<OutT, 192, false, 8>(a, lda, b, ldb, p, st);
+      case 160: return launch_pair<OutT, 160, false, 8>(a, lda, b, ldb, p, st);
+      default: return launch_pair<OutT, 128, false, 8>(a, lda, b, ldb, p, st);
+    }
+  }
   if (plan.pair) {
     switch (plan.bn) {
       case 256: return launch_pair<OutT, 256>(a, lda, b, ldb, p, st);

@@ -75,12 +75,16 @@ typedef enum fnn_dtype {
  * pair that finishes the tile adds them (int32 additions: the accumulator stays exact whatever the order).  0 = used
  * where the shape table expects at least 3 % from it and the caller passed the workspace, 1 = wherever it can run
  * (more than 128 rows, a workspace; for tests), 2 = never.
+ *
+ * FNN_OPT_A8W8_EPILOGUE_WARPS (default 0; a tuning hook).  The CTA-pair kernel runs with eight epilogue warps per CTA
+ * for K up to 2560, where a tile's MMAs take less time than four warps need to write it out; 4 keeps four everywhere.
  */
 typedef enum fnn_option {
   FNN_OPT_STATIC_WEIGHTS = 1,
   FNN_OPT_TEST_STALL_US = 2,
   FNN_OPT_A8W8_PAIR_TILE = 3,
-  FNN_OPT_A8W8_BALANCED = 4
+  FNN_OPT_A8W8_BALANCED = 4,
+  FNN_OPT_A8W8_EPILOGUE_WARPS = 5
 } fnn_option;
 
 /* Sets an option; FNN_ERR_UNSUPPORTED for an unknown one.  fnn_get_option returns the value, or -1 if unknown. */
