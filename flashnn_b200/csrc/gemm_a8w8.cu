@@ -526,7 +526,8 @@ template <int BN, int STAGES, int EPI = 4> struct PairSmem {
   static constexpr int kBBytes = (kBN / 2) * kBK;       // this CTA's BN / 2 rows of B
   static constexpr int kStageBytes = kABytes + kBBytes;
   static constexpr int kOutOff = STAGES * kStageBytes;        // [EPI epilogue warps][2][32 rows x 64 B] output staging
-  static constexpr int kOutBytes = EPI * 2 * 2048;
+  static constexpr int kOutBufs = EPI == 4 ? 2 : 1;           // staging buffers per epilogue warp
+  static constexpr int kOutBytes = EPI * kOutBufs * 2048;
   static constexpr int kColScaleOff = kOutOff + kOutBytes;    // [EPI][kBN] float
   static constexpr int kBarOff = kColScaleOff + EPI * kBN * 4;
   static constexpr int kNumBars = 2 * STAGES + 4 + 1;
@@ -538,8 +539,8 @@ template <int BN, int STAGES, int EPI = 4> struct PairSmem {
 
 // MOE: fused-MoE mode for blocks of 256 sorted slots (A8W8Params, "Fused-MoE mode"): a pair tile is one block, whose
 // expert picks the weight rows and column scales; the epilogue scatters each slot's row to its (token, choice) index.
-// EPI: epilogue warps per CTA, 4 or 8.  With 8, two warps share a TMEM lane quarter and split a tile's column chunks:
-// for short K, where a tile's MMAs take less time than four warps need to write it out.
+// EPI: epilogue warps per CTA, 4 or 8.  With 8 (the plain mode's default), two warps share a TMEM lane quarter and
+// split a tile's column chunks, and each has one output staging buffer instead of two.
 template <typename OutT, int BN, int STAGES, bool SK, bool MOE = false, int EPI = 4>
 __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__((2 + EPI) * 32, 1)
 a8w8_umma_pair_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ CUtensorMap tmap_b,
@@ -698,7 +699,7 @@ a8w8_umma_pair_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_c
     int local = 0;
     bool ok = true;
     PairWork<SK, MOE> w(p, pair_id, num_pairs);
-    uint8_t* out_stage = smem + L::kOutOff + ewarp * 4096;              // this warp's two output staging buffers
+    uint8_t* out_stage = smem + L::kOutOff + ewarp * (L::kOutBufs * 2048);  // this warp's output staging buffer(s)
     int out_buf = 0;
     const int my_flag = int(rank) * 4 + quarter;                        // this warp's flag word within a pair's eight
     const int my_row = int(rank) * 128 + quarter * 32 + lane;           // this thread's row within a tile
@@ -814,7 +815,7 @@ a8w8_umma_pair_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_c
           store_acc_chunk(r, row, n0 + c * 32, p, acc_vec_ok);
           float v[32];
           scale_chunk(r, rs, cs + c * 32, same16, p, v);
-          if (lane == 0) tma_store_wait_read<1>();
+          if (lane == 0) tma_store_wait_read<L::kOutBufs - 1>();
           __syncwarp();
           uint8_t* buf_out = out_stage + out_buf * 2048;
 #pragma unroll
@@ -828,7 +829,7 @@ a8w8_umma_pair_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_c
             tma_store_2d(&tmap_out, buf_out, n0 + c * 32, mb * 256 + int(rank) * 128 + quarter * 32);
             tma_store_commit();
           }
-          out_buf ^= 1;
+          if (L::kOutBufs == 2) out_buf ^= 1;
         } else {
           store_chunk<OutT>(r, row, n0 + c * 32, rs, cs + c * 32, same16, p, vec_ok, acc_vec_ok);
         }
@@ -971,7 +972,7 @@ template <typename OutT, int BN, bool SK = false, int EPI = 4>
 int launch_pair(const int8_t* a, int64_t lda, const int8_t* b, int64_t ldb, A8W8Params p, cudaStream_t st,
                 void* workspace = nullptr) {
   // for the operand ring; the output staging buffers and the column scales of the epilogue warps take the rest
-  constexpr int kBudget = (EPI == 4 ? 196 : 174) * 1024;
+  constexpr int kBudget = (EPI == 4 ? 196 : 194) * 1024;
   constexpr int STAGES = kBudget / (kBM * kBK + (BN / 2) * kBK) < 8 ? kBudget / (kBM * kBK + (BN / 2) * kBK) : 8;
   using L = PairSmem<BN, STAGES, EPI>;
   static_assert(L::kDynamicBytes <= 227 * 1024, "shared memory budget");
@@ -1030,11 +1031,6 @@ int launch_pair(const int8_t* a, int64_t lda, const int8_t* b, int64_t ldb, A8W8
 // operand traffic; it wins where the problem is too small to give every CTA pair a tile.  Problems of at
 // most 128 rows are bound by the weight stream instead and keep their own rule.
 // ---------------------------------------------------------------------------
-// Up to this K the CTA-pair kernel runs with eight epilogue warps per CTA (and one operand stage fewer, which is what
-// it costs from K = 3328 up).  Measured, four -> eight warps: K = 1664 2037 -> 3055 TOPS, 2048 2097 -> 2741,
-// 3328 3344 -> 3281, 4096 3470 -> 3279.
-constexpr int kEpi8MaxK = 2560;
-
 struct A8W8Plan {
   bool pair;
   int bn;
@@ -1127,8 +1123,10 @@ int dispatch(const int8_t* a, int64_t lda, const int8_t* b, int64_t ldb, const A
     if (p.M > kBM) plan = A8W8Plan{true, forced, 0.0};
   }
   if (plan.balanced) return launch_pair<OutT, 256, true>(a, lda, b, ldb, p, st, workspace);
-  if (plan.pair && p.K <= kEpi8MaxK && opt_a8w8_epilogue_warps() != 4) {
-    // short K: a tile's MMAs take less time than four warps need to write it out; eight epilogue warps per CTA
+  if (plan.pair && opt_a8w8_epilogue_warps() != 4) {
+    // Eight epilogue warps per CTA (one output staging buffer each, so the operand ring keeps its depth).  With short K
+    // a tile's MMAs take less time than four warps need to write it out: measured four -> eight warps, K = 1664
+    // 2037 -> 3003 TOPS, 2048 2051 -> 2766, 3328 3273 -> 3344, 4096 3322 -> 3370, 8192 the same.
     switch (plan.bn) {
       case 256: return launch_pair<OutT, 256, false, 8>(a, lda, b, ldb, p, st);
       case 224: return launch_pair<OutT, 224, false, 8>(a, lda, b, ldb, p, st);

@@ -77,7 +77,7 @@ typedef enum fnn_dtype {
  * (more than 128 rows, a workspace; for tests), 2 = never.
  *
  * FNN_OPT_A8W8_EPILOGUE_WARPS (default 0; a tuning hook).  The CTA-pair kernel runs with eight epilogue warps per CTA
- * for K up to 2560, where a tile's MMAs take less time than four warps need to write it out; 4 keeps four everywhere.
+ * (with short K a tile's MMAs take less time than four warps need to write it out); 4 runs it with four.
  */
 typedef enum fnn_option {
   FNN_OPT_STATIC_WEIGHTS = 1,
