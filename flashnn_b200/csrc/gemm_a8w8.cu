@@ -1072,11 +1072,19 @@ A8W8Plan plan_a8w8(int M, int N, int sms) {
   A8W8Plan best{false, 64, 1e30};
   const int tiles_m1 = (M + kBM - 1) / kBM;
   if (M <= kBM) {
-    // one row of tiles (decode shapes): bound by the weight stream, not by the tensor pipe; the widest tile that
-    // still gives every SM work keeps the most bytes in flight per CTA
-    if (((N + 255) / 256) >= sms) return A8W8Plan{false, 256, 0.0};
-    if (((N + 127) / 128) >= sms) return A8W8Plan{false, 128, 0.0};
-    return A8W8Plan{false, 64, 0.0};
+    // one row of tiles (decode shapes): bound by the weight stream, not by the tensor pipe.  The persistent CTAs walk
+    // the tiles in rounds, so the time goes with rounds x tile width; ties keep the wider tile (more bytes in flight per
+    // CTA), and 64-wide tiles carry a measured 20 % penalty (64 x 57344 x 8192: 0.098 ms with 256-wide tiles in two
+    // rounds, 0.115 ms with 64-wide ones in seven; 64 x 14336 x 8192: 0.037 ms with 128-wide tiles in one round,
+    // 0.041 ms with 64-wide ones in two).
+    int best_bn = 256;
+    double best_cost = 1e30;
+    for (int bn : {256, 128, 64}) {
+      const long long tiles = (N + bn - 1) / bn;
+      const double cost = double((tiles + sms - 1) / sms) * bn * (bn == 64 ? 1.2 : 1.0);
+      if (cost < best_cost) { best_cost = cost; best_bn = bn; }
+    }
+    return A8W8Plan{false, best_bn, 0.0};
   }
   for (int bn : {256, 128, 64}) {
     const long long tiles = 1ll * tiles_m1 * ((N + bn - 1) / bn);
